@@ -1,0 +1,216 @@
+/* catgrad_b200 — C ABI of the B200 tensor backend for catgrad's interpreter.
+ *
+ * One entry point per method of `trait Backend`
+ * (catgrad/src/interpreter/backend/mod.rs:24-122), with the trait's names, so that a Rust shim
+ * `impl Backend for B200Backend` is a table of one-line FFI calls.  Conventions of the trait are kept
+ * (mod.rs:18-23): the operands of one op share a dtype, nothing broadcasts implicitly, reductions keep
+ * the rank.  Where the reference panics (ndarray.rs:27,34,365,444,485,530; candle.rs:1272-1274) or
+ * returns BackendError::ShapeError (mod.rs:129-132), these functions return a status and leave a
+ * message in cg_last_error(); nothing traps on the device.
+ *
+ * Plain pointers and sizes only.  Tensors are opaque reference-counted handles; every function that
+ * returns a tensor returns a NEW handle the caller releases with cg_release().  Inputs are never
+ * mutated and are not consumed (a Rust shim releases its `TaggedTensor` arguments when they drop).
+ *
+ * One cg_ctx = one device + one stream, used from one thread at a time.  Only cg_to_vec, cg_to_bool,
+ * cg_compare, cg_format and cg_synchronize wait for the device.
+ */
+#ifndef CATGRAD_B200_H
+#define CATGRAD_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cg_ctx cg_ctx;
+typedef struct cg_tensor cg_tensor;
+typedef struct cg_term cg_term;
+typedef struct cg_builder cg_builder;
+typedef struct cg_params cg_params;
+typedef struct cg_llama cg_llama;
+
+/* enum Dtype, catgrad/src/category/core.rs:23-29 (same order) */
+typedef enum { CG_F32 = 0, CG_F16 = 1, CG_BF16 = 2, CG_F8E4M3 = 3, CG_U32 = 4 } cg_dtype;
+
+typedef enum {
+  CG_OK = 0,
+  CG_ERR_SHAPE_MISMATCH = 1,    /* "Shape mismatch in operation" (candle.rs:1272-1274) */
+  CG_ERR_DTYPE_MISMATCH = 2,    /* InterpreterError::TypeError (tensor_op.rs:254-256) */
+  CG_ERR_UNSUPPORTED_DTYPE = 3, /* e.g. sin of a u32 tensor (ndarray.rs:361-367) */
+  CG_ERR_OOM = 4,
+  CG_ERR_CUDA = 5,
+  CG_ERR_TIMEOUT = 6,
+  CG_ERR_BAD_HANDLE = 7,
+  CG_ERR_SHAPE = 8,             /* BackendError::ShapeError (mod.rs:129-132) */
+  CG_ERR_INVALID_ARG = 9,
+  CG_ERR_INTERP = 10            /* InterpreterError::{ArityError,MultipleRead,MultipleWrite,Load,...} */
+} cg_status;
+
+#define CG_MAX_RANK 8
+
+/* ---- context ------------------------------------------------------------------------------ */
+/* Creates a context on CUDA device `device` (replaces `CandleBackend::new_accel`/`NdArrayBackend`,
+ * examples/llama/main.rs:199-210).  Fails with CG_ERR_CUDA when no device is usable: there is no
+ * CPU fallback. */
+cg_status cg_init(int device, cg_ctx** out);
+void cg_destroy(cg_ctx* ctx);
+/* Message of the last failing call on this context (or, with ctx == NULL, of the last failing call
+ * that had no context).  Valid until the next call on the same context/thread. */
+const char* cg_last_error(cg_ctx* ctx);
+cg_status cg_synchronize(cg_ctx* ctx);
+/* Name of the implementation behind the handle ("b200"). */
+const char* cg_backend_name(cg_ctx* ctx);
+
+/* ---- tensor handles (BackendTensorOps::shape, mod.rs:124-126; TaggedTensor::dtype, types.rs:18-60) */
+void cg_retain(cg_tensor* t);
+void cg_release(cg_tensor* t);
+int cg_rank(const cg_tensor* t);
+cg_status cg_shape(const cg_tensor* t, uint64_t* dims /* CG_MAX_RANK */, int* rank);
+cg_dtype cg_dtype_of(const cg_tensor* t);
+/* 1 if the handle is a contiguous row-major buffer (views made by transpose/slice/broadcast are not) */
+int cg_is_contiguous(const cg_tensor* t);
+/* Device address of element 0 and strides in elements (for zero-copy interop; not part of the trait). */
+void* cg_data_ptr(const cg_tensor* t);
+cg_status cg_strides(const cg_tensor* t, int64_t* strides /* CG_MAX_RANK */, int* rank);
+
+/* ---- constructors (mod.rs:28-58) ---------------------------------------------------------- */
+cg_status cg_zeros(cg_ctx*, const uint64_t* dims, int rank, cg_dtype dtype, cg_tensor** out);
+/* `data` is host memory, n elements; n != product(dims) -> CG_ERR_SHAPE (BackendError::ShapeError) */
+cg_status cg_from_vec_f32(cg_ctx*, const float* data, uint64_t n, const uint64_t* dims, int rank, cg_tensor** out);
+cg_status cg_from_vec_f16(cg_ctx*, const uint16_t* data, uint64_t n, const uint64_t* dims, int rank, cg_tensor** out);
+cg_status cg_from_vec_bf16(cg_ctx*, const uint16_t* data, uint64_t n, const uint64_t* dims, int rank, cg_tensor** out);
+cg_status cg_from_vec_fp8(cg_ctx*, const uint8_t* data, uint64_t n, const uint64_t* dims, int rank, cg_tensor** out);
+cg_status cg_from_vec_u32(cg_ctx*, const uint32_t* data, uint64_t n, const uint64_t* dims, int rank, cg_tensor** out);
+cg_status cg_arange(cg_ctx*, uint64_t end, cg_tensor** out);                  /* mod.rs:111 */
+
+/* ---- ops (mod.rs:60-110) ------------------------------------------------------------------- */
+cg_status cg_cast(cg_ctx*, const cg_tensor* x, cg_dtype target, cg_tensor** out);
+cg_status cg_matmul(cg_ctx*, const cg_tensor* lhs, const cg_tensor* rhs, cg_tensor** out);
+cg_status cg_add(cg_ctx*, const cg_tensor* a, const cg_tensor* b, cg_tensor** out);
+cg_status cg_sub(cg_ctx*, const cg_tensor* a, const cg_tensor* b, cg_tensor** out);
+cg_status cg_mul(cg_ctx*, const cg_tensor* a, const cg_tensor* b, cg_tensor** out);
+cg_status cg_div(cg_ctx*, const cg_tensor* a, const cg_tensor* b, cg_tensor** out);
+cg_status cg_pow(cg_ctx*, const cg_tensor* a, const cg_tensor* b, cg_tensor** out);
+cg_status cg_lt(cg_ctx*, const cg_tensor* a, const cg_tensor* b, cg_tensor** out);
+cg_status cg_gt(cg_ctx*, const cg_tensor* a, const cg_tensor* b, cg_tensor** out);
+cg_status cg_gte(cg_ctx*, const cg_tensor* a, const cg_tensor* b, cg_tensor** out);
+cg_status cg_lte(cg_ctx*, const cg_tensor* a, const cg_tensor* b, cg_tensor** out);
+cg_status cg_eq(cg_ctx*, const cg_tensor* a, const cg_tensor* b, cg_tensor** out);
+cg_status cg_where_cond(cg_ctx*, const cg_tensor* mask, const cg_tensor* x, const cg_tensor* y, cg_tensor** out);
+cg_status cg_sin(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+cg_status cg_cos(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+cg_status cg_exp(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+cg_status cg_log(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+cg_status cg_floor(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+cg_status cg_round(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+cg_status cg_neg(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+cg_status cg_broadcast(cg_ctx*, const cg_tensor* x, const uint64_t* dims, int rank, cg_tensor** out);
+cg_status cg_reshape(cg_ctx*, const cg_tensor* x, const uint64_t* dims, int rank, cg_tensor** out);
+cg_status cg_transpose(cg_ctx*, const cg_tensor* x, uint64_t dim0, uint64_t dim1, cg_tensor** out);
+cg_status cg_max(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+cg_status cg_sum(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+cg_status cg_argmax(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+cg_status cg_topk(cg_ctx*, const cg_tensor* x, uint64_t k, cg_tensor** out_values, cg_tensor** out_indices);
+cg_status cg_compare(cg_ctx*, const cg_tensor* a, const cg_tensor* b, int* out_equal);
+cg_status cg_concat(cg_ctx*, const cg_tensor* x, const cg_tensor* y, uint64_t dim, cg_tensor** out);
+cg_status cg_index(cg_ctx*, const cg_tensor* x, uint64_t dim, const cg_tensor* indices, cg_tensor** out);
+cg_status cg_slice(cg_ctx*, const cg_tensor* x, uint64_t dim, uint64_t start, uint64_t len, cg_tensor** out);
+cg_status cg_to_bool(cg_ctx*, const cg_tensor* x, int* out);                  /* mod.rs:113 */
+/* Row-major contents to host memory, element type = the tensor's dtype (mod.rs:115, TaggedVec). */
+cg_status cg_to_vec(cg_ctx*, const cg_tensor* x, void* dst, uint64_t cap_bytes);
+/* Backend::format_tensor (mod.rs:117-125); writes a NUL-terminated string, truncated to cap. */
+cg_status cg_format(cg_ctx*, const cg_tensor* x, char* buf, uint64_t cap);
+
+/* ---- terms and the interpreter ------------------------------------------------------------
+ * A restatement of catgrad's core IR (category/core.rs:104-290) and of the evaluator
+ * (abstract_interpreter/eval.rs:18-187; interpreter/interpreter.rs:29-108; tensor_op.rs:9-275).
+ * Node types and op kinds are the integer values of `cg::NodeType` / `cg::OpKind` / `cg::ScalarOp`
+ * (catgrad_b200/csrc/host/ir.h), mirrored in catgrad_b200/ir.py. */
+cg_status cg_builder_new(cg_builder** out);
+void cg_builder_free(cg_builder* b);
+/* Adds a term input of node type `node_type`; returns its variable id in *out_var. */
+cg_status cg_builder_source(cg_builder* b, int node_type, int* out_var);
+/* Adds one operation.  `str` is the Probe label or the Load path ("a.b.c"); then_term/else_term are
+ * used by If (core.rs:112) and copied.  Variables may be used any number of times: the Copy edges the
+ * evaluator needs are inserted by cg_builder_finish. */
+cg_status cg_builder_op(cg_builder* b, int op_kind, int scalar_op, uint64_t nat, int dtype, float f32, uint32_t u32,
+                        const char* str, const cg_term* then_term, const cg_term* else_term, const int* inputs,
+                        int n_inputs, const int* output_types, int n_outputs, int* out_vars);
+cg_status cg_builder_finish(cg_builder* b, const int* targets, int n_targets, cg_term** out);
+void cg_term_free(cg_term* t);
+/* counts[0..3] = nodes, edges, tensor-op edges, layers of the parallel SSA order (ssa/mod.rs:24-76) */
+cg_status cg_term_stats(const cg_term* t, uint64_t counts[4]);
+
+/* LlamaConfig (catgrad-llm-models/src/models/llama.rs:9-27), fields the Llama term reads. */
+typedef struct {
+  uint64_t hidden_size, intermediate_size, num_hidden_layers, num_attention_heads, num_key_value_heads, vocab_size;
+  float rope_theta, rms_norm_eps;
+  int tie_word_embeddings;
+} cg_llama_config;
+/* The term of LlamaModel::def (llama.rs:393-401): inputs x [B,S] u32, in_k, in_v [L,B,Hkv,T,D],
+ * max_positions (nat); outputs ids [B,S,1] u32, out_k, out_v [L,B,Hkv,T+S,D].  tap_logits != 0 adds the
+ * lm_head output as a 4th output. */
+cg_status cg_llama_term(const cg_llama_config* cfg, int tap_logits, cg_term** out);
+
+/* Parameters<B> (interpreter/parameters.rs): path -> tensor; Load(path) clones the handle. */
+cg_status cg_params_new(cg_params** out);
+void cg_params_free(cg_params* p);
+cg_status cg_params_set(cg_params* p, const char* path, const cg_tensor* t);
+
+/* Value<B> (interpreter/types.rs:10-16) crossing the ABI. */
+typedef enum { CG_VALUE_NAT = 1, CG_VALUE_DTYPE = 2, CG_VALUE_SHAPE = 3, CG_VALUE_TENSOR = 4 } cg_value_kind;
+typedef struct {
+  int kind;              /* cg_value_kind */
+  uint64_t nat;          /* CG_VALUE_NAT */
+  int dtype;             /* CG_VALUE_DTYPE */
+  uint64_t dims[CG_MAX_RANK];
+  int rank;              /* CG_VALUE_SHAPE */
+  cg_tensor* tensor;     /* CG_VALUE_TENSOR; outputs are new handles */
+} cg_value;
+/* Interpreter::run (interpreter.rs:33-36).  The schedule of a term is computed on its first run and
+ * kept with the term. */
+cg_status cg_interp_run(cg_ctx*, const cg_term* term, const cg_params* params, const cg_value* inputs, int n_inputs,
+                        cg_value* outputs, int cap_outputs, int* n_outputs);
+
+/* ---- fused Llama runner (B200 only; not part of the trait) ---------------------------------
+ * Executes the Llama term above as a fixed plan of fused kernels with a device-resident KV cache
+ * instead of one kernel per IR edge.  It replaces the per-token `run_interpreter` loop of
+ * examples/llama/main.rs:876-1043 (generate_stream): same inputs (token ids), same outputs (greedy ids),
+ * with the rounding points of the term kept (bf16 at every op output the graph types as bf16). */
+/* Parameters are looked up by their safetensors names (llama.rs Load paths).  dtype: CG_F32 or CG_BF16. */
+cg_status cg_llama_create(cg_ctx*, const cg_llama_config* cfg, cg_dtype dtype, const cg_params* params,
+                          uint64_t max_batch, uint64_t max_positions, cg_llama** out);
+void cg_llama_free(cg_llama* m);
+/* Clears the KV cache (context length 0) for a new batch of `batch` sequences. */
+cg_status cg_llama_reset(cg_llama* m, uint64_t batch);
+/* Runs one step of the term on `ids` (host memory, [batch, seq] u32, row-major) at the current context
+ * length, appends K/V to the cache, and leaves the greedy id of the LAST position of every sequence on
+ * the device (the element the reference runner reads, main.rs:1031-1037).  With out_ids != NULL they are
+ * also copied to host ([batch] u32), which synchronises. */
+cg_status cg_llama_forward(cg_llama* m, const uint32_t* ids, uint64_t batch, uint64_t seq, uint32_t* out_ids);
+/* `steps` greedy decode steps, each consuming the ids the previous step left on the device (no host
+ * round trip per token; EOS is ignored as in the reference's --bench loop, main.rs:919).  Writes
+ * [batch, steps] u32 to out_ids (host) at the end. */
+cg_status cg_llama_decode(cg_llama* m, uint64_t steps, uint32_t* out_ids);
+/* Copies the logits of the last forward/decode step ([batch, vocab], last position only) to host as f32. */
+cg_status cg_llama_last_logits(cg_llama* m, float* dst, uint64_t cap_elems);
+/* Current context length T. */
+uint64_t cg_llama_context_len(const cg_llama* m);
+/* Number of kernel launches issued by this runner since creation (graph replays count their nodes). */
+uint64_t cg_llama_launch_count(const cg_llama* m);
+
+/* ---- timing and allocator introspection ---------------------------------------------------- */
+/* CUDA events on the context's stream (the stream every kernel of this library is launched on). */
+cg_status cg_event_record(cg_ctx*, int slot /* 0..63 */);
+cg_status cg_event_elapsed_ms(cg_ctx*, int slot_start, int slot_end, float* out_ms);
+/* bytes currently handed out / cached by the context's caching allocator, and launch counter */
+cg_status cg_ctx_stats(cg_ctx*, uint64_t stats[4] /* live bytes, cached bytes, cudaMalloc calls, kernel launches */);
+/* Writes `bytes` of device memory on the context's stream (used by benchmarks to evict L2). */
+cg_status cg_flush_l2(cg_ctx*, uint64_t bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
