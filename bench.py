@@ -1,0 +1,305 @@
+"""Benchmark of the hot path: greedy Llama decoding (and prefill) through the C ABI.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|c3|c4|tiny]
+
+One "step" is one decode step of the whole batch (one new token per sequence).
+  N = 1  : Llama-3.2-1B shape, bf16, batch 1, 512-token prompt, then K timed decode steps (baseline config 3).
+           The batch-sharded workload (config 4: 256 sequences x 128 prompt tokens) is timed too and reported
+           under "c4" so that the N>1 runs have their single-GPU point.
+  N > 1  : config 4: the 256 sequences are split evenly over the ranks (one process per GPU, no collective on
+           the data path; the generated ids are gathered once at the end).  Total work is fixed: strong scaling.
+`value` is decode tokens/s with everything resident on the device (CUDA-graph replay, ids fed back on the
+device); `e2e` is the same loop driven like the reference's runner, one host round trip per token: the token
+ids are copied host->device, the step runs, the new ids are read back (examples/llama/main.rs:1016-1037).
+Weights are synthetic (N(0,0.02), seed 0), prompts are uniform random ids (seed 1); the 2.47 GB of weights read
+per step exceed the 126 MB L2, so no flush is needed between steps.
+
+`--impl reference` times the CPU restatement of the reference's ndarray path (oracle/ndarray_ref.cc,
+single-threaded like the reference's tensor ops) on a bounded sample of the same workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import catgrad_b200 as cb  # noqa: E402
+
+HBM_NOMINAL_GBS = 8000.0
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device, self.rows, self.proc = device, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def event_ms(be, a, b):
+    out = ctypes.c_float()
+    be._check(be._ns.event_elapsed_ms(be._ctx, a, b, ctypes.byref(out)))
+    return out.value
+
+
+def build_model(be, cfg, dtype):
+    t0 = time.time()
+    w = cb.random_weights(cfg, seed=0)
+    params = cb.upload_weights(be, w, dtype)
+    be.synchronize()
+    return params, w, time.time() - t0
+
+
+def decode_bytes(cfg, batch, ctx_len):
+    """Algorithmic HBM bytes of one decode step: every weight once (the tied head counted once, the embedding
+    rows actually gathered are negligible) + the KV cache read + the new KV rows written."""
+    n_weights = cfg.num_params()
+    kv_per_tok = 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim * 2
+    return 2 * n_weights + batch * kv_per_tok * ctx_len + batch * kv_per_tok
+
+
+def run_decode_workload(be, cfg, params, batch, prompt_len, steps, warmup, dev_index, e2e_steps=None, name=""):
+    """Prefill, then W warm-up + K timed decode steps (device-resident), then the same through host round trips."""
+    P = prompt_len + 2 * (warmup + steps) + 16
+    runner = cb.LlamaRunner(be, cfg, params, cb.Dtype.BF16, max_batch=batch, max_positions=P)
+    prompts = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(batch, prompt_len), dtype=np.uint32)
+    res = {}
+    # ---- prefill (reported beside the headline) ----
+    pre_ms = []
+    for i in range(3):
+        runner.reset(batch)
+        be._ns.event_record(be._ctx, 0)
+        runner.forward(prompts, read=False)
+        be._ns.event_record(be._ctx, 1)
+        be.synchronize()
+        pre_ms.append(event_ms(be, 0, 1))
+    res["prefill_ms"] = min(pre_ms[1:])
+    res["prefill_tok_s"] = batch * prompt_len / (res["prefill_ms"] / 1e3)
+    # ---- device-resident decode ----
+    runner.decode(max(warmup, 3))
+    l0 = runner.launch_count
+    ctx0 = runner.context_len
+    sampler = ClockSampler(dev_index)
+    sampler.start()
+    be.synchronize()
+    be._ns.event_record(be._ctx, 2)
+    ids = runner.decode(steps)
+    be._ns.event_record(be._ctx, 3)
+    be.synchronize()
+    res["clocks"] = sampler.stop()
+    res["ms"] = event_ms(be, 2, 3)
+    res["launches"] = runner.launch_count - l0
+    res["ctx_mid"] = ctx0 + steps / 2
+    res["ids_checksum"] = int(ids.astype(np.uint64).sum())
+    # ---- end to end: one host round trip per token, like the reference runner ----
+    k = e2e_steps or steps
+    tok = ids[:, -1].copy().reshape(batch, 1)
+    for _ in range(3):
+        tok = runner.forward(tok).reshape(batch, 1)
+    t0 = time.perf_counter()
+    for _ in range(k):
+        tok = runner.forward(tok).reshape(batch, 1)
+    res["e2e_ms"] = (time.perf_counter() - t0) * 1e3
+    res["e2e_steps"] = k
+    res["batch"] = batch
+    del runner
+    return res
+
+
+def cpu_baseline_sample(cfg, weights_f32, prompt_len=8, steps=2):
+    """The oracle (CPU restatement of the reference's ndarray path, 1 thread) on a bounded sample of the workload:
+    a short prefill, then `steps` decode steps through the op-by-op interpreter, f32 (the ndarray backend has no
+    bf16).  Returns decode tokens/s."""
+    so = os.path.join(ROOT, "oracle", "_build", "libndarray_ref.so")
+    if not os.path.exists(so):
+        subprocess.run(["make", "-C", os.path.join(ROOT, "oracle")], check=True, capture_output=True)
+    oracle = cb.Backend(_cdll=ctypes.CDLL(so), _prefix="ref_")
+    params = cb.upload_weights(oracle, weights_f32, cb.Dtype.F32)
+    term = cb.llama_term(oracle, cfg)
+    interp = cb.Interpreter(oracle, params)
+    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(1, prompt_len), dtype=np.uint32)
+    in_k, in_v = cb.empty_state_cache(oracle, cfg, 1, cb.Dtype.F32)
+    x = ids
+    times = []
+    for i in range(steps + 1):
+        t0 = time.perf_counter()
+        r = interp.run(term, [oracle.ndarray_from_vec_u32(x, x.shape), in_k, in_v, prompt_len + steps + 1])
+        last = oracle.to_numpy(r[0])[:, -1, 0]
+        times.append(time.perf_counter() - t0)
+        in_k, in_v = r[1], r[2]
+        x = last.reshape(1, 1).astype(np.uint32)
+    dec = times[1:]
+    return {"value": len(dec) / sum(dec), "unit": "tok/s", "cores": 1, "kind": "port",
+            "sample": f"oracle/ndarray_ref (1 thread, f32): prefill of {prompt_len} tokens ({times[0]:.1f} s) then "
+                      f"{steps} decode steps of the same model ({sum(dec):.1f} s)",
+            "prefill_tok_s": prompt_len / times[0]}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "c3", "c4", "tiny"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-c4", action="store_true", help="N=1 only: do not time the batch-sharded workload as well")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = cb.TINY if args.workload == "tiny" else cb.LLAMA_1B
+    model_name = "tiny-llama" if args.workload == "tiny" else "Llama-3.2-1B shape"
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        w = cb.random_weights(cfg, seed=0)
+        base = cpu_baseline_sample(cfg, w, prompt_len=8, steps=max(1, min(args.steps, 2)))
+        line = {"impl": "reference", "metric": "decode tokens/s", "value": base["value"], "unit": "tok/s",
+                "n_gpus": args.gpus, "steps": max(1, min(args.steps, 2)), "warmup": 0,
+                "ms_per_step": 1e3 / base["value"], "higher_is_better": True, "scaling": "weak" if args.gpus == 1 else "strong",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"{model_name}, batch 1, greedy decode on the host CPU (ndarray-path restatement)"},
+                "cpu_baseline": base,
+                "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    be = cb.Backend(local_rank)
+    params, w, load_s = build_model(be, cfg, cb.Dtype.BF16)
+    hbm_peak, _, peak_src = measured_peaks()
+
+    single = world == 1
+    workload = args.workload if args.workload != "auto" else ("c3" if single else "c4")
+    if workload in ("c3", "tiny"):
+        batch_total, prompt_len = 1, (512 if workload == "c3" else 64)
+    else:
+        batch_total, prompt_len = 256, 128
+    assert batch_total % world == 0
+    batch = batch_total // world
+
+    if dist is not None:
+        dist.barrier()
+    r = run_decode_workload(be, cfg, params, batch, prompt_len, args.steps, args.warmup, local_rank)
+    ms, e2e_ms, pre_ms = r["ms"], r["e2e_ms"], r["prefill_ms"]
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms, e2e_ms, pre_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)      # max over ranks
+        ms, e2e_ms, pre_ms = [float(v) for v in t.tolist()]
+        gathered = [torch.zeros(1, dtype=torch.int64, device="cuda") for _ in range(world)]
+        dist.all_gather(gathered, torch.tensor([r["ids_checksum"] % (1 << 62)], device="cuda"))  # the final gather
+        dist.barrier()
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    tok_per_step = batch_total
+    value = tok_per_step * args.steps / (ms / 1e3)
+    e2e_value = tok_per_step * r["e2e_steps"] / (e2e_ms / 1e3)
+    bytes_step = decode_bytes(cfg, batch, r["ctx_mid"])
+    achieved = bytes_step / (ms / args.steps / 1e3) / 1e9
+    line = {
+        "metric": "decode tokens/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak" if single else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{model_name} bf16, {batch_total} sequence(s) x {prompt_len}-token prompt, greedy decode, "
+                               f"context {int(r['ctx_mid'] - args.steps / 2)}..{int(r['ctx_mid'] + args.steps / 2)}",
+                   "global_batch": batch_total, "prompt_len": prompt_len, "parallelism": f"batch-sharded x{world}",
+                   "l2": "inputs larger than L2 (2.47 GB of weights per step vs 126 MB)"},
+        "prefill": {"tok_s": batch_total * prompt_len / (pre_ms / 1e3), "ms": pre_ms,
+                    "note": "lm_head on the last position of each sequence only"},
+        "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4 * batch, "d2h_bytes_per_step": 4 * batch,
+                "steps": r["e2e_steps"], "how": "cg_llama_forward per token with host id buffers (copy in, step, copy out)"},
+        "gpu_launches": r["launches"],
+        "clocks": r["clocks"],
+        "roofline": {"bound": "hbm", "kernel": "decode step (gemv_fused_kernel streams the weights)",
+                     "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "peak_source": peak_src, "frac_of_8TBs_nominal": achieved / HBM_NOMINAL_GBS,
+                     "bytes_per_step": bytes_step, "traffic": None},
+        "load_s": load_s,
+    }
+    if single and workload == "c3" and not args.skip_c4:
+        # the batch-sharded workload on one GPU: the N=1 point of the scaling runs
+        c4_steps = min(args.steps, 64)
+        r4 = run_decode_workload(be, cfg, params, 256, 128, c4_steps, args.warmup, local_rank, e2e_steps=8)
+        line["c4"] = {"decode_tok_s": 256 * c4_steps / (r4["ms"] / 1e3), "ms_per_step": r4["ms"] / c4_steps,
+                      "prefill_tok_s": r4["prefill_tok_s"], "e2e_tok_s": 256 * r4["e2e_steps"] / (r4["e2e_ms"] / 1e3),
+                      "workload": "256 sequences x 128-token prompt on one GPU"}
+    if single and not args.no_cpu_baseline:
+        del params
+        wf = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+        line["cpu_baseline"] = cpu_baseline_sample(cfg, wf, prompt_len=8, steps=2)
+        line["cpu_baseline"]["host"] = {"nproc": os.cpu_count()}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,676 @@
+// The fused Llama runner behind cg_llama_* (include/catgrad_b200.h).
+//
+// It executes the Llama term (llama_term.cc, i.e. catgrad-llm-models/src/models/llama.rs:144-385) as a fixed
+// plan instead of ~140 interpreter edges per layer:
+//   * the plan is built once per model (the reference re-lowers and re-schedules the term on every token,
+//     interpreter.rs:33-36 + ssa/mod.rs:24-76);
+//   * every `linear` reads W[out,in] in place (no transpose/broadcast copy, nn/mod.rs:182-204);
+//   * the KV cache lives on the device with spare capacity and is appended in place; the functional
+//     slice/concat/re-stack of helpers/cache.rs:13-75 never runs; repeat_kv is an index computation;
+//   * RoPE tables and all literals are computed once at creation (cache.rs:86-103 rebuilds them per step);
+//   * the context length is a device-side scalar, so one captured CUDA graph replays for every decode step;
+//   * greedy ids stay on the device between steps (the reference reads them back per token, main.rs:1031-1037).
+// Observable behaviour kept: ids of the last position per sequence; K/V contents; rounding points (see
+// llama_kernels.cuh).  The lm_head runs on the last position of each sequence only: the reference computes it
+// for all S positions (llama.rs:217-225) and its runner reads only the last element.
+#include <cmath>
+#include <cstring>
+
+#include "../kernels/elementwise.h"
+#include "../kernels/gemm_tcgen05.h"
+#include "../kernels/llama_kernels.cuh"
+#include "../kernels/matmul.h"
+#include "c_api_internal.h"
+#include "cuda_backend.h"
+
+using namespace cg;
+
+namespace {
+
+struct LayerW {
+  const void *in_norm, *q, *k, *v, *o, *post_norm, *gate, *up, *down;
+};
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace
+
+struct cg_llama {
+  CudaBackend* be = nullptr;
+  cg_ctx* ctx = nullptr;
+  LlamaConfig cfg;
+  Dtype dt = Dtype::BF16;
+  size_t es = 2;
+  int64_t max_batch = 0, P = 0;
+  std::vector<Tensor> keep;  // parameter tensors kept alive
+  std::vector<LayerW> layers;
+  const void *embed = nullptr, *final_norm = nullptr, *head = nullptr;
+
+  // persistent device state
+  Tensor kc, vc;              // [L, Bmax, nkv, P, hd]
+  Tensor cos_t, sin_t;        // [P, hd/2] f32
+  Tensor words;               // int32: [0] ctx_len, [1] step_no
+  Tensor ids_in, ids_cur, ids_new, ids_out;  // u32: prompt ids [M], current [B], argmax result [B], record [steps*B]
+  Tensor logits;              // [Bmax, V]
+  int64_t out_cap_steps = 0;
+  // activation buffers sized for `cap_tokens` tokens
+  int64_t cap_tokens = 0;
+  Tensor x, xn, qkv, attn, h, g, u, tmp, scores, attn_bhsd;
+  int64_t batch = 0;
+  int64_t host_ctx_len = 0;   // mirror of words[0] (all steps are issued by this object)
+  uint64_t launches = 0;
+
+  cudaGraphExec_t graph = nullptr;
+  int64_t graph_batch = -1;
+  uint64_t graph_nodes = 0;
+
+  ~cg_llama() {
+    if (graph) cudaGraphExecDestroy(graph);
+  }
+};
+
+namespace {
+
+template <class T>
+struct Plan {
+  cg_llama& m;
+  cudaStream_t st;
+  int sm;
+  explicit Plan(cg_llama& mm) : m(mm), st(mm.be->stream()), sm(mm.be->sm_count()) {}
+
+  void launched(const char* what) {
+    ++m.launches;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) throw Error(ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+  }
+
+  static int mt_for(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16; }
+  static bool gemv_ok(int64_t M, int64_t K) {
+    return M <= 16 && (size_t)mt_for(M) * K * sizeof(T) <= 160 * 1024 && K % (16 / sizeof(T)) == 0;
+  }
+
+  template <int MT, int PRO, int EPI>
+  void gemv_launch(const cgk::GemvArgs& a) {
+    size_t smem = (size_t)MT * a.K * sizeof(T);
+    auto kern = cgk::gemv_fused_kernel<T, MT, PRO, EPI>;
+    static size_t smem_set = 0;  // per instantiation: raise the dynamic shared-memory limit once per size class
+    if (smem > 48 * 1024 && smem > smem_set) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      smem_set = smem;
+    }
+    int pairs = EPI == cgk::EPI_SILU_MUL ? a.N : (a.N + 1) / 2;
+    int ctas_per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
+    int grid = std::min((pairs + 7) / 8, sm * ctas_per_sm);
+    kern<<<grid, 256, smem, st>>>(a);
+    launched("gemv");
+  }
+  template <int PRO, int EPI>
+  void gemv_mt(const cgk::GemvArgs& a) {
+    switch (mt_for(a.M)) {
+      case 1: gemv_launch<1, PRO, EPI>(a); break;
+      case 2: gemv_launch<2, PRO, EPI>(a); break;
+      case 4: gemv_launch<4, PRO, EPI>(a); break;
+      case 8: gemv_launch<8, PRO, EPI>(a); break;
+      default: gemv_launch<16, PRO, EPI>(a); break;
+    }
+  }
+  void gemv(int pro, int epi, const cgk::GemvArgs& a) {
+    if (pro == cgk::PRO_NORM) {
+      if (epi == cgk::EPI_STORE) gemv_mt<cgk::PRO_NORM, cgk::EPI_STORE>(a);
+      else if (epi == cgk::EPI_SILU_MUL) gemv_mt<cgk::PRO_NORM, cgk::EPI_SILU_MUL>(a);
+      else gemv_mt<cgk::PRO_NORM, cgk::EPI_RESIDUAL>(a);
+    } else {
+      if (epi == cgk::EPI_STORE) gemv_mt<cgk::PRO_NONE, cgk::EPI_STORE>(a);
+      else if (epi == cgk::EPI_SILU_MUL) gemv_mt<cgk::PRO_NONE, cgk::EPI_SILU_MUL>(a);
+      else gemv_mt<cgk::PRO_NONE, cgk::EPI_RESIDUAL>(a);
+    }
+  }
+
+  // out[M,N] (row pitch ldo... contiguous) = xin[M,K] (row pitch ldx) @ W[N,K]^T
+  void gemm(const void* xin, int64_t ldx, const void* W, void* out, int64_t M, int64_t N, int64_t K) {
+    cgk::View4 bt;
+    std::memset(&bt, 0, sizeof(bt));
+    bt.rank = 0;
+    bt.total = 1;
+    if (std::is_same<T, __nv_bfloat16>::value &&
+        cgk::tcgen05_gemm_applicable(bt, 1, xin, W, M, N, K, ldx, 1, 1, K)) {
+      cgk::launch_tcgen05_gemm(bt, 1, xin, W, out, M, N, K, ldx, K, m.be->dev_err(), sm, st);
+      launched("gemm(tcgen05)");
+      return;
+    }
+    cgk::launch_matmul((int)m.dt, bt, 1, xin, W, out, M, N, K, ldx, 1, 1, K, sm, st);
+    launched("gemm");
+  }
+
+  int grid_for(long long items) {
+    long long blocks = (items + 255) / 256, cap = (long long)sm * 8;
+    return (int)std::max<long long>(1, std::min(blocks, cap));
+  }
+
+  void rmsnorm(const void* in, const void* gain, void* out, int64_t rows, int64_t H, int64_t row_mul, int64_t row_off) {
+    cgk::rmsnorm_kernel<T><<<(int)rows, 256, 0, st>>>((const T*)in, (const T*)gain, (T*)out, (int)H, m.cfg.rms_norm_eps,
+                                                      row_mul, row_off);
+    launched("rmsnorm");
+  }
+  void add_inplace(void* xx, const void* y, int64_t n) {
+    cgk::add_inplace_kernel<T><<<grid_for(n / (16 / sizeof(T))), 256, 0, st>>>((T*)xx, (const T*)y, n);
+    launched("add");
+  }
+
+  // One evaluation of the term on M = B*S tokens whose ids are in `ids` (device).
+  void step(const unsigned* ids, int64_t B, int64_t S) {
+    const LlamaConfig& c = m.cfg;
+    const int64_t H = c.hidden_size, F = c.intermediate_size, nh = c.num_attention_heads, nkv = c.num_key_value_heads,
+                  hd = c.head_dim(), V = c.vocab_size, L = c.num_hidden_layers;
+    const int64_t M = B * S, NQ = nh * hd, NKV = nkv * hd, NQKV = NQ + 2 * NKV;
+    int* ctx_len = (int*)m.words.raw();
+    unsigned* err = m.be->dev_err();
+    T* x = (T*)m.x.raw();
+
+    cgk::embed_kernel<T><<<grid_for(M * (H / (16 / sizeof(T)))), 256, 0, st>>>(ids, (const T*)m.embed, x, (int)M, (int)H,
+                                                                             (int)V, err);
+    launched("embed");
+
+    const float scale = cgk_host_round((float)std::sqrt((float)hd));
+    for (int64_t l = 0; l < L; ++l) {
+      const LayerW& w = m.layers[l];
+      // ---- attention block ----
+      T* qkv = (T*)m.qkv.raw();
+      if (gemv_ok(M, H)) {
+        cgk::GemvArgs a{};
+        a.w[0] = w.q; a.w[1] = w.k; a.w[2] = w.v;
+        a.n_end[0] = (int)NQ; a.n_end[1] = (int)(NQ + NKV); a.n_end[2] = (int)NQKV;
+        a.x = x; a.x_row_stride = H; a.gain = w.in_norm; a.eps = c.rms_norm_eps;
+        a.out = qkv; a.M = (int)M; a.N = (int)NQKV; a.K = (int)H;
+        gemv(cgk::PRO_NORM, cgk::EPI_STORE, a);
+      } else {
+        rmsnorm(x, w.in_norm, m.xn.raw(), M, H, 1, 0);
+        // q | k | v packed per buffer: [M,NQ] then [M,NKV] then [M,NKV]
+        gemm(m.xn.raw(), H, w.q, qkv, M, NQ, H);
+        gemm(m.xn.raw(), H, w.k, qkv + M * NQ, M, NKV, H);
+        gemm(m.xn.raw(), H, w.v, qkv + M * (NQ + NKV), M, NKV, H);
+      }
+      const bool packed_rows = gemv_ok(M, H);  // rows interleave q|k|v (pitch NQKV) vs three dense matrices
+      T* q = qkv;
+      T* k = packed_rows ? qkv + NQ : qkv + M * NQ;
+      T* v = packed_rows ? qkv + NQ + NKV : qkv + M * (NQ + NKV);
+      const int64_t qs = packed_rows ? NQKV : NQ, ks = packed_rows ? NQKV : NKV;
+      T* kcl = (T*)m.kc.raw() + l * m.max_batch * nkv * m.P * hd;
+      T* vcl = (T*)m.vc.raw() + l * m.max_batch * nkv * m.P * hd;
+      {
+        cgk::RopeArgs r{};
+        r.q = q; r.q_row_stride = qs; r.k = k; r.k_row_stride = ks; r.v = v; r.v_row_stride = ks;
+        r.kc = kcl; r.vc = vcl; r.cos_t = (const float*)m.cos_t.raw(); r.sin_t = (const float*)m.sin_t.raw();
+        r.ctx_len = ctx_len; r.B = (int)B; r.S = (int)S; r.nh = (int)nh; r.nkv = (int)nkv; r.HD = (int)hd; r.P = (int)m.P;
+        cgk::rope_append_kernel<T><<<(int)M, 256, 0, st>>>(r, err);
+        launched("rope_append");
+      }
+      T* attn = (T*)m.attn.raw();
+      if (S == 1) {
+        cgk::AttnArgs a{};
+        a.q = q; a.q_row_stride = qs; a.kc = kcl; a.vc = vcl; a.out = attn; a.out_row_stride = NQ;
+        a.ctx_len = ctx_len; a.nh = (int)nh; a.nkv = (int)nkv; a.P = (int)m.P; a.scale = scale;
+        constexpr int VEC = 16 / sizeof(T);
+        size_t smem = (size_t)m.P * 4 + (size_t)(256 / (hd / VEC)) * hd * 4;
+        dim3 grid((unsigned)nh, (unsigned)B);
+        if (hd == 64) {
+          auto kern = cgk::attn_decode_kernel<T, 64>;
+          static size_t smem_set = 0;
+          if (smem > 48 * 1024 && smem > smem_set) {
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            smem_set = smem;
+          }
+          kern<<<grid, 256, smem, st>>>(a);
+        } else {
+          auto kern = cgk::attn_decode_kernel<T, 128>;
+          static size_t smem_set = 0;
+          if (smem > 48 * 1024 && smem > smem_set) {
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            smem_set = smem;
+          }
+          kern<<<grid, 256, smem, st>>>(a);
+        }
+        launched("attn_decode");
+      } else {
+        prefill_attention(q, qs, kcl, vcl, attn, B, S);
+      }
+      // ---- o_proj + residual ----
+      if (gemv_ok(M, NQ)) {
+        cgk::GemvArgs a{};
+        a.w[0] = w.o; a.n_end[0] = a.n_end[1] = a.n_end[2] = (int)H;
+        a.x = attn; a.x_row_stride = NQ; a.out = x; a.res = x; a.M = (int)M; a.N = (int)H; a.K = (int)NQ;
+        gemv(cgk::PRO_NONE, cgk::EPI_RESIDUAL, a);
+      } else {
+        gemm(attn, NQ, w.o, m.tmp.raw(), M, H, NQ);
+        add_inplace(x, m.tmp.raw(), M * H);
+      }
+      // ---- MLP ----
+      T* hbuf = (T*)m.h.raw();
+      if (gemv_ok(M, H)) {
+        cgk::GemvArgs a{};
+        a.w[0] = w.gate; a.w[1] = w.up; a.n_end[0] = a.n_end[1] = a.n_end[2] = (int)F;
+        a.x = x; a.x_row_stride = H; a.gain = w.post_norm; a.eps = c.rms_norm_eps;
+        a.out = hbuf; a.M = (int)M; a.N = (int)F; a.K = (int)H;
+        gemv(cgk::PRO_NORM, cgk::EPI_SILU_MUL, a);
+      } else {
+        rmsnorm(x, w.post_norm, m.xn.raw(), M, H, 1, 0);
+        gemm(m.xn.raw(), H, w.gate, m.g.raw(), M, F, H);
+        gemm(m.xn.raw(), H, w.up, m.u.raw(), M, F, H);
+        cgk::silu_mul_kernel<T><<<grid_for(M * F / (16 / sizeof(T))), 256, 0, st>>>((const T*)m.g.raw(), (const T*)m.u.raw(),
+                                                                                  hbuf, M * F);
+        launched("silu_mul");
+      }
+      if (gemv_ok(M, F)) {
+        cgk::GemvArgs a{};
+        a.w[0] = w.down; a.n_end[0] = a.n_end[1] = a.n_end[2] = (int)H;
+        a.x = hbuf; a.x_row_stride = F; a.out = x; a.res = x; a.M = (int)M; a.N = (int)H; a.K = (int)F;
+        gemv(cgk::PRO_NONE, cgk::EPI_RESIDUAL, a);
+      } else {
+        gemm(hbuf, F, w.down, m.tmp.raw(), M, H, F);
+        add_inplace(x, m.tmp.raw(), M * H);
+      }
+    }
+    // ---- final norm + lm_head on the last position of each sequence, argmax ----
+    T* logits = (T*)m.logits.raw();
+    if (gemv_ok(B, H)) {
+      cgk::GemvArgs a{};
+      a.w[0] = m.head; a.n_end[0] = a.n_end[1] = a.n_end[2] = (int)V;
+      a.x = x + (S - 1) * H; a.x_row_stride = S * H; a.gain = m.final_norm; a.eps = c.rms_norm_eps;
+      a.out = logits; a.M = (int)B; a.N = (int)V; a.K = (int)H;
+      gemv(cgk::PRO_NORM, cgk::EPI_STORE, a);
+    } else {
+      rmsnorm(x, m.final_norm, m.xn.raw(), B, H, S, S - 1);
+      gemm(m.xn.raw(), H, m.head, logits, B, V, H);
+    }
+    {
+      cgk::View4 outer;
+      std::memset(&outer, 0, sizeof(outer));
+      outer.rank = 1;
+      outer.total = B;
+      outer.shape[0] = B;
+      outer.sa[0] = V;
+      cgk::launch_reduce(cgk::R_ARGMAX, (int)m.dt, outer, B, V, 1, logits, m.ids_new.raw(), sm, st);
+      launched("argmax");
+    }
+    cgk::advance_kernel<<<1, 256, 0, st>>>((const unsigned*)m.ids_new.raw(), (unsigned*)m.ids_cur.raw(),
+                                           (unsigned*)m.ids_out.raw(), ctx_len, ctx_len + 1, (int)B, (int)S,
+                                           (int)m.out_cap_steps);
+    launched("advance");
+  }
+
+  // round sqrt(hd) through T like `cast(constant(sqrt(hd)), dtype(attn))` (llama.rs:331-332)
+  static float cgk_host_round(float v) {
+    if (std::is_same<T, float>::value) return v;
+    uint32_t u;
+    std::memcpy(&u, &v, 4);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    u &= 0xffff0000u;
+    float r;
+    std::memcpy(&r, &u, 4);
+    return r;
+  }
+
+  // Prefill attention through batched matmuls over views (no repeat_kv copy, no K transpose copy):
+  // scores[b,kvh,r] = Q[b,:,kvh*rep+r,:] x K[b,kvh]^T ; softmax ; out = P x V[b,kvh].
+  void prefill_attention(T* q, int64_t qs, T* kcl, T* vcl, T* attn_out, int64_t B, int64_t S) {
+    const LlamaConfig& c = m.cfg;
+    const int64_t nh = c.num_attention_heads, nkv = c.num_key_value_heads, hd = c.head_dim(), rep = nh / nkv;
+    const int64_t T0 = m.host_ctx_len, Tt = T0 + S;
+    T* scores = (T*)m.scores.raw();
+    cgk::View4 bt;
+    std::memset(&bt, 0, sizeof(bt));
+    bt.rank = 3;
+    bt.shape[0] = B; bt.shape[1] = nkv; bt.shape[2] = rep;
+    bt.total = B * nh;
+    bt.sa[0] = S * qs; bt.sa[1] = rep * hd; bt.sa[2] = hd;            // Q[b, s, h, :] with h = kvh*rep + r
+    bt.sb[0] = nkv * m.P * hd; bt.sb[1] = m.P * hd; bt.sb[2] = 0;     // K[b, kvh, t, :]
+    // scores: A = Q rows (pitch qs, K-contiguous), B = K^T: k-stride 1, n-stride hd
+    cgk::launch_matmul((int)m.dt, bt, B * nh, q, kcl, scores, S, Tt, hd, qs, 1, 1, hd, sm, st);
+    launched("scores");
+    const float scale = cgk_host_round((float)std::sqrt((float)hd));
+    if ((size_t)Tt * 4 > 48 * 1024)
+      cudaFuncSetAttribute(cgk::softmax_mask_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(Tt * 4));
+    cgk::softmax_mask_kernel<T><<<(unsigned)(B * nh * S), 256, (size_t)Tt * 4, st>>>(scores, (int)S, (int)Tt, (int)T0, scale);
+    launched("softmax_mask");
+    // out[b,h,s,:] = P[b,h,s,:] x V[b,kvh]  (V: k-stride hd, n-stride 1)
+    cgk::View4 bp;
+    std::memset(&bp, 0, sizeof(bp));
+    bp.rank = 3;
+    bp.shape[0] = B; bp.shape[1] = nkv; bp.shape[2] = rep;
+    bp.total = B * nh;
+    bp.sa[0] = nh * S * Tt; bp.sa[1] = rep * S * Tt; bp.sa[2] = S * Tt;
+    bp.sb[0] = nkv * m.P * hd; bp.sb[1] = m.P * hd; bp.sb[2] = 0;
+    T* obhsd = (T*)m.attn_bhsd.raw();
+    cgk::launch_matmul((int)m.dt, bp, B * nh, scores, vcl, obhsd, S, hd, Tt, Tt, 1, hd, 1, sm, st);
+    launched("pv");
+    cgk::bhsd_to_bshd_kernel<T><<<grid_for(B * nh * S * (hd / (16 / sizeof(T)))), 256, 0, st>>>(obhsd, attn_out, (int)B,
+                                                                                              (int)nh, (int)S, (int)hd);
+    launched("bhsd_to_bshd");
+  }
+};
+
+const Tensor& find_param(const cg_params* p, const std::string& key, Dtype dt, const Shape& shape) {
+  auto it = p->p.find(key);
+  CG_CHECK(it != p->p.end(), ERR_INTERP, "Load: no parameter named " + key);
+  const Tensor& t = it->second;
+  CG_CHECK(t.dt == dt, ERR_DTYPE_MISMATCH, "parameter " + key + " has dtype " + dtype_name(t.dt));
+  CG_CHECK(t.shape == shape, ERR_SHAPE_MISMATCH, "parameter " + key + " has shape " + shape_str(t.shape) + ", expected " + shape_str(shape));
+  CG_CHECK(t.is_contiguous() && ((uintptr_t)t.raw() % 16 == 0), ERR_INVALID_ARG, "parameter " + key + " must be contiguous and 16-byte aligned");
+  return t;
+}
+
+void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
+  const LlamaConfig& c = m.cfg;
+  int64_t M = B * S;
+  int64_t H = c.hidden_size, F = c.intermediate_size, nh = c.num_attention_heads, hd = c.head_dim(),
+          NQKV = (c.num_attention_heads + 2 * c.num_key_value_heads) * hd;
+  if (M > m.cap_tokens) {
+    if (m.graph) {
+      cudaGraphExecDestroy(m.graph);
+      m.graph = nullptr;
+      m.graph_batch = -1;
+    }
+    m.be->synchronize();
+    m.x = m.be->empty({M, H}, m.dt);
+    m.xn = m.be->empty({M, H}, m.dt);
+    m.qkv = m.be->empty({M, NQKV}, m.dt);
+    m.attn = m.be->empty({M, nh * hd}, m.dt);
+    m.h = m.be->empty({M, F}, m.dt);
+    m.tmp = m.be->empty({M, H}, m.dt);
+    if (M > 16 || (size_t)16 * H * m.es > 160 * 1024) {  // gate/up buffers of the GEMM path
+      m.g = m.be->empty({M, F}, m.dt);
+      m.u = m.be->empty({M, F}, m.dt);
+    }
+    m.ids_in = m.be->empty({M}, Dtype::U32);
+    m.cap_tokens = M;
+  }
+  if (S > 1) {
+    int64_t Tt = m.host_ctx_len + S;
+    int64_t need = B * nh * S * Tt;
+    if (!m.scores.defined() || m.scores.size() < need) m.scores = m.be->empty({need}, m.dt);
+    int64_t need2 = B * nh * S * hd;
+    if (!m.attn_bhsd.defined() || m.attn_bhsd.size() < need2) m.attn_bhsd = m.be->empty({need2}, m.dt);
+  }
+}
+
+void run_step(cg_llama& m, const unsigned* ids, int64_t B, int64_t S) {
+  if (m.dt == Dtype::BF16) Plan<__nv_bfloat16>(m).step(ids, B, S);
+  else Plan<float>(m).step(ids, B, S);
+  m.host_ctx_len += S;
+}
+
+cg_llama* L(cg_llama* m) {
+  CG_CHECK(m != nullptr, ERR_BAD_HANDLE, "null runner");
+  return m;
+}
+}  // namespace
+
+extern "C" {
+
+typedef struct {
+  uint64_t hidden_size, intermediate_size, num_hidden_layers, num_attention_heads, num_key_value_heads, vocab_size;
+  float rope_theta, rms_norm_eps;
+  int tie_word_embeddings;
+} api_llama_config;
+
+int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const cg_params* params, uint64_t max_batch,
+                    uint64_t max_positions, cg_llama** out) {
+  CG_API_BEGIN
+  CG_CHECK(ctx && ctx->be && cfg && params && out, ERR_BAD_HANDLE, "null argument");
+  CG_CHECK(dtype == (int)Dtype::F32 || dtype == (int)Dtype::BF16, ERR_UNSUPPORTED_DTYPE,
+           "the fused runner supports f32 and bf16");
+  CG_CHECK(max_batch >= 1 && max_positions >= 1, ERR_INVALID_ARG, "max_batch and max_positions must be positive");
+  std::unique_ptr<cg_llama> m(new cg_llama());
+  m->ctx = ctx;
+  m->be = static_cast<CudaBackend*>(ctx->be.get());
+  m->be->guard();
+  LlamaConfig& c = m->cfg;
+  c.hidden_size = (int64_t)cfg->hidden_size;
+  c.intermediate_size = (int64_t)cfg->intermediate_size;
+  c.num_hidden_layers = (int64_t)cfg->num_hidden_layers;
+  c.num_attention_heads = (int64_t)cfg->num_attention_heads;
+  c.num_key_value_heads = (int64_t)cfg->num_key_value_heads;
+  c.vocab_size = (int64_t)cfg->vocab_size;
+  c.rope_theta = cfg->rope_theta;
+  c.rms_norm_eps = cfg->rms_norm_eps;
+  c.tie_word_embeddings = cfg->tie_word_embeddings;
+  CG_CHECK(c.num_attention_heads > 0 && c.num_key_value_heads > 0 && c.hidden_size % c.num_attention_heads == 0 &&
+               c.num_attention_heads % c.num_key_value_heads == 0 && c.num_hidden_layers > 0,
+           ERR_INVALID_ARG, "inconsistent Llama config");
+  const int64_t hd = c.head_dim();
+  CG_CHECK(hd == 64 || hd == 128, ERR_INVALID_ARG, "the fused runner supports head_dim 64 and 128");
+  m->dt = (Dtype)dtype;
+  m->es = dtype_size(m->dt);
+  const int64_t vec = 16 / (int64_t)m->es;
+  CG_CHECK(c.hidden_size % vec == 0 && c.intermediate_size % vec == 0, ERR_INVALID_ARG,
+           "hidden and intermediate sizes must be multiples of 16 bytes");
+  CG_CHECK(max_positions * 4 + 32 * 128 * 4 <= 200 * 1024, ERR_INVALID_ARG, "max_positions above 47000 is not supported");
+  m->max_batch = (int64_t)max_batch;
+  m->P = (int64_t)max_positions;
+
+  const int64_t H = c.hidden_size, F = c.intermediate_size, NKV = c.num_key_value_heads * hd, V = c.vocab_size;
+  auto get = [&](const std::string& key, const Shape& shape) {
+    const Tensor& t = find_param(params, key, m->dt, shape);
+    m->keep.push_back(t);
+    return (const void*)t.raw();
+  };
+  m->embed = get("model.embed_tokens.weight", {V, H});
+  for (int64_t l = 0; l < c.num_hidden_layers; ++l) {
+    std::string p = "model.layers." + std::to_string(l) + ".";
+    LayerW w;
+    w.in_norm = get(p + "input_layernorm.weight", {H});
+    w.q = get(p + "self_attn.q_proj.weight", {H, H});
+    w.k = get(p + "self_attn.k_proj.weight", {NKV, H});
+    w.v = get(p + "self_attn.v_proj.weight", {NKV, H});
+    w.o = get(p + "self_attn.o_proj.weight", {H, H});
+    w.post_norm = get(p + "post_attention_layernorm.weight", {H});
+    w.gate = get(p + "mlp.gate_proj.weight", {F, H});
+    w.up = get(p + "mlp.up_proj.weight", {F, H});
+    w.down = get(p + "mlp.down_proj.weight", {H, F});
+    m->layers.push_back(w);
+  }
+  m->final_norm = get("model.norm.weight", {H});
+  m->head = c.tie_word_embeddings ? m->embed : get("lm_head.weight", {V, H});
+
+  CudaBackend& be = *m->be;
+  m->kc = be.zeros({c.num_hidden_layers, m->max_batch, c.num_key_value_heads, m->P, hd}, m->dt);
+  m->vc = be.zeros({c.num_hidden_layers, m->max_batch, c.num_key_value_heads, m->P, hd}, m->dt);
+  m->cos_t = be.empty({m->P, hd / 2}, Dtype::F32);
+  m->sin_t = be.empty({m->P, hd / 2}, Dtype::F32);
+  cgk::rope_table_kernel<<<std::max<int>(1, (int)std::min<int64_t>((m->P * (hd / 2) + 255) / 256, 1024)), 256, 0,
+                           be.stream()>>>((float*)m->cos_t.raw(), (float*)m->sin_t.raw(), (int)m->P, (int)(hd / 2),
+                                          c.rope_theta, 2.0f / (float)hd);
+  be.check_launch("rope_table");
+  m->words = be.zeros({16}, Dtype::U32);
+  m->ids_cur = be.zeros({m->max_batch}, Dtype::U32);
+  m->ids_new = be.zeros({m->max_batch}, Dtype::U32);
+  m->logits = be.zeros({m->max_batch, V}, m->dt);
+  m->out_cap_steps = 0;
+  *out = m.release();
+  CG_API_END(ctx)
+}
+
+void cg_llama_free(cg_llama* m) {
+  if (!m) return;
+  if (m->be) {
+    m->be->guard();
+    cudaStreamSynchronize(m->be->stream());
+  }
+  delete m;
+}
+
+int cg_llama_reset(cg_llama* mm, uint64_t batch) {
+  cg_ctx* ctx = mm ? mm->ctx : nullptr;
+  CG_API_BEGIN
+  cg_llama& m = *L(mm);
+  CG_CHECK(batch >= 1 && (int64_t)batch <= m.max_batch, ERR_INVALID_ARG, "batch exceeds max_batch");
+  m.be->guard();
+  CG_CUDA(cudaMemsetAsync(m.words.raw(), 0, 64, m.be->stream()));
+  m.batch = (int64_t)batch;
+  m.host_ctx_len = 0;
+  CG_API_END(ctx)
+}
+
+int cg_llama_forward(cg_llama* mm, const uint32_t* ids, uint64_t batch, uint64_t seq, uint32_t* out_ids) {
+  cg_ctx* ctx = mm ? mm->ctx : nullptr;
+  CG_API_BEGIN
+  cg_llama& m = *L(mm);
+  CG_CHECK(ids != nullptr, ERR_INVALID_ARG, "ids is null");
+  CG_CHECK((int64_t)batch == m.batch, ERR_INVALID_ARG, "batch differs from the one given to cg_llama_reset");
+  CG_CHECK(seq >= 1 && m.host_ctx_len + (int64_t)seq <= m.P, ERR_INVALID_ARG, "sequence exceeds max_positions");
+  m.be->guard();
+  ensure_capacity(m, (int64_t)batch, (int64_t)seq);
+  if (m.out_cap_steps < 1) {
+    m.ids_out = m.be->zeros({m.max_batch}, Dtype::U32);
+    m.out_cap_steps = 1;
+  }
+  cudaStream_t st = m.be->stream();
+  CG_CUDA(cudaMemcpyAsync(m.ids_in.raw(), ids, batch * seq * 4, cudaMemcpyHostToDevice, st));
+  CG_CUDA(cudaMemsetAsync((int*)m.words.raw() + 1, 0, 4, st));  // step_no = 0
+  run_step(m, (const unsigned*)m.ids_in.raw(), (int64_t)batch, (int64_t)seq);
+  if (out_ids) {
+    CG_CUDA(cudaMemcpyAsync(out_ids, m.ids_cur.raw(), batch * 4, cudaMemcpyDeviceToHost, st));
+    CG_CUDA(cudaStreamSynchronize(st));
+    m.be->check_device_errors();
+  }
+  CG_API_END(ctx)
+}
+
+int cg_llama_decode(cg_llama* mm, uint64_t steps, uint32_t* out_ids) {
+  cg_ctx* ctx = mm ? mm->ctx : nullptr;
+  CG_API_BEGIN
+  cg_llama& m = *L(mm);
+  CG_CHECK(m.batch >= 1 && m.host_ctx_len >= 1, ERR_INVALID_ARG, "decode needs a prefilled context");
+  CG_CHECK(m.host_ctx_len + (int64_t)steps <= m.P, ERR_INVALID_ARG, "decode would exceed max_positions");
+  if (steps == 0) return 0;
+  m.be->guard();
+  const int64_t B = m.batch;
+  ensure_capacity(m, B, 1);
+  cudaStream_t st = m.be->stream();
+  if (m.out_cap_steps < (int64_t)steps) {
+    if (m.graph) {
+      cudaGraphExecDestroy(m.graph);
+      m.graph = nullptr;
+      m.graph_batch = -1;
+    }
+    m.be->synchronize();
+    m.ids_out = m.be->zeros({(int64_t)steps * m.max_batch}, Dtype::U32);
+    m.out_cap_steps = (int64_t)steps;
+  }
+  CG_CUDA(cudaMemsetAsync((int*)m.words.raw() + 1, 0, 4, st));  // step_no = 0
+  const bool use_graph = std::getenv("CATGRAD_B200_NO_GRAPH") == nullptr;
+  uint64_t first = 0;
+  if (use_graph && (m.graph == nullptr || m.graph_batch != B)) {
+    // The first step of a new shape runs eagerly (it also loads the kernels and sets their attributes,
+    // neither of which belongs inside a capture); the capture below records the same launches.
+    run_step(m, (const unsigned*)m.ids_cur.raw(), B, 1);
+    first = 1;
+    if (m.graph) {
+      cudaGraphExecDestroy(m.graph);
+      m.graph = nullptr;
+    }
+    // One decode step captured once: the context length and step number are device scalars.
+    uint64_t before = m.launches;
+    int64_t ctx_before = m.host_ctx_len;
+    cudaGraph_t g = nullptr;
+    CG_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    try {
+      run_step(m, (const unsigned*)m.ids_cur.raw(), B, 1);
+    } catch (...) {
+      cudaStreamEndCapture(st, &g);
+      if (g) cudaGraphDestroy(g);
+      m.host_ctx_len = ctx_before;
+      throw;
+    }
+    CG_CUDA(cudaStreamEndCapture(st, &g));
+    m.host_ctx_len = ctx_before;  // capture only recorded the step
+    m.graph_nodes = m.launches - before;
+    m.launches = before;
+    cudaError_t e = cudaGraphInstantiate(&m.graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) throw Error(ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+    m.graph_batch = B;
+  }
+  for (uint64_t i = first; i < steps; ++i) {
+    if (use_graph) {
+      CG_CUDA(cudaGraphLaunch(m.graph, st));
+      m.launches += m.graph_nodes;
+      m.host_ctx_len += 1;
+    } else {
+      run_step(m, (const unsigned*)m.ids_cur.raw(), B, 1);
+    }
+  }
+  if (out_ids) {
+    std::vector<uint32_t> stage((size_t)steps * B);
+    CG_CUDA(cudaMemcpyAsync(stage.data(), m.ids_out.raw(), stage.size() * 4, cudaMemcpyDeviceToHost, st));
+    CG_CUDA(cudaStreamSynchronize(st));
+    m.be->check_device_errors();
+    for (uint64_t s = 0; s < steps; ++s)
+      for (int64_t b = 0; b < B; ++b) out_ids[(size_t)b * steps + s] = stage[(size_t)s * B + b];
+  }
+  CG_API_END(ctx)
+}
+
+int cg_llama_last_logits(cg_llama* mm, float* dst, uint64_t cap_elems) {
+  cg_ctx* ctx = mm ? mm->ctx : nullptr;
+  CG_API_BEGIN
+  cg_llama& m = *L(mm);
+  int64_t n = m.batch * m.cfg.vocab_size;
+  CG_CHECK((int64_t)cap_elems >= n, ERR_INVALID_ARG, "destination too small");
+  m.be->guard();
+  Tensor view = m.logits;
+  view.shape = {m.batch, m.cfg.vocab_size};
+  view.strides = contiguous_strides(view.shape);
+  Tensor f = m.be->cast(view, Dtype::F32);
+  m.be->to_vec(f, dst, (size_t)n * 4);
+  CG_API_END(ctx)
+}
+
+uint64_t cg_llama_context_len(const cg_llama* m) { return m ? (uint64_t)m->host_ctx_len : 0; }
+uint64_t cg_llama_launch_count(const cg_llama* m) { return m ? m->launches : 0; }
+
+// ---- timing and allocator introspection --------------------------------------------------------
+int cg_event_record(cg_ctx* ctx, int slot) {
+  CG_API_BEGIN
+  CG_CHECK(ctx && ctx->be, ERR_BAD_HANDLE, "null context");
+  CudaBackend* be = static_cast<CudaBackend*>(ctx->be.get());
+  be->guard();
+  CG_CUDA(cudaEventRecord(be->event(slot), be->stream()));
+  CG_API_END(ctx)
+}
+int cg_event_elapsed_ms(cg_ctx* ctx, int a, int b, float* out_ms) {
+  CG_API_BEGIN
+  CG_CHECK(ctx && ctx->be && out_ms, ERR_BAD_HANDLE, "null argument");
+  CudaBackend* be = static_cast<CudaBackend*>(ctx->be.get());
+  be->guard();
+  CG_CUDA(cudaEventSynchronize(be->event(b)));
+  CG_CUDA(cudaEventElapsedTime(out_ms, be->event(a), be->event(b)));
+  CG_API_END(ctx)
+}
+int cg_ctx_stats(cg_ctx* ctx, uint64_t stats[4]) {
+  CG_API_BEGIN
+  CG_CHECK(ctx && ctx->be, ERR_BAD_HANDLE, "null context");
+  CudaBackend* be = static_cast<CudaBackend*>(ctx->be.get());
+  stats[0] = be->allocator().live_bytes();
+  stats[1] = be->allocator().cached_bytes();
+  stats[2] = be->allocator().cuda_mallocs();
+  stats[3] = be->launches;
+  CG_API_END(ctx)
+}
+namespace {
+__global__ void flush_kernel(uint4* p, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    p[i] = make_uint4((unsigned)i, 0, 0, 0);
+}
+}  // namespace
+int cg_flush_l2(cg_ctx* ctx, uint64_t bytes) {
+  CG_API_BEGIN
+  CG_CHECK(ctx && ctx->be, ERR_BAD_HANDLE, "null context");
+  CudaBackend* be = static_cast<CudaBackend*>(ctx->be.get());
+  Tensor t = be->empty({(int64_t)(bytes / 4)}, Dtype::U32);
+  flush_kernel<<<be->sm_count() * 8, 256, 0, be->stream()>>>((uint4*)t.raw(), (long long)(bytes / 16));
+  be->check_launch("flush_l2");
+  CG_API_END(ctx)
+}
+
+}  // extern "C"

@@ -1,0 +1,467 @@
+// Fused kernels of the Llama plan.  Each kernel covers a sub-graph of the Llama term
+// (catgrad-llm-models/src/models/llama.rs:144-385 and the helpers it expands) and keeps the term's rounding
+// points: values the graph types as bf16 are rounded to bf16 exactly where an op of the graph would produce
+// them; the f32 islands (rmsnorm, softmax, silu, rope: stdlib/nn/mod.rs:117-179, helpers/tensors.rs:82-111,
+// helpers/rope.rs:430-451) run in f32.  Compiled with -fmad=false: products and sums that are separate ops in
+// the graph stay separate roundings; dot products use explicit fmaf (accumulation order is free there).
+//
+// All of them are HBM- or latency-bound; the weight-streaming GEMV dominates a decode step.
+#pragma once
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace cgk {
+
+template <class T, int N> struct alignas(sizeof(T) * N) VecT { T v[N]; };
+
+template <class T> __device__ __forceinline__ float rt(float v) { return Elem<T>::load(Elem<T>::store(v)); }  // round trip through T
+
+// Deterministic block-wide reductions for 256-thread CTAs (fixed tree).
+__device__ __forceinline__ float block_sum_256(float v, float* scratch /* >= 8 floats */) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) r += scratch[w];
+  return r;
+}
+__device__ __forceinline__ float block_max_256(float v, float* scratch) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = -FLT_MAX;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) r = fmaxf(r, scratch[w]);
+  return r;
+}
+
+// ---- embedding gather (helpers/tensors.rs:255-272) ------------------------------------------------
+// x[m, :] = table[ids[m], :].  16-byte copies; an id >= vocab records DEV_ERR_INDEX_OOB and writes zeros.
+template <class T>
+__global__ void __launch_bounds__(256) embed_kernel(const unsigned* __restrict__ ids, const T* __restrict__ table,
+                                                    T* __restrict__ x, int M, int H, int vocab, unsigned* err) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int per_row = H / VEC;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < (long long)M * per_row;
+       t += (long long)gridDim.x * blockDim.x) {
+    int m = (int)(t / per_row), c = (int)(t - (long long)m * per_row);
+    unsigned id = ids[m];
+    VecT<T, VEC> v;
+    if (id >= (unsigned)vocab) {
+      if (c == 0) atomicOr(err, DEV_ERR_INDEX_OOB);
+      memset(&v, 0, sizeof(v));
+    } else {
+      v = *reinterpret_cast<const VecT<T, VEC>*>(table + (long long)id * H + c * VEC);
+    }
+    *reinterpret_cast<VecT<T, VEC>*>(x + (long long)m * H + c * VEC) = v;
+  }
+}
+
+// ---- RMSNorm (helpers/tensors.rs:82-111) ------------------------------------------------------------
+// y = T( T(x / sqrt(mean(x^2) + eps)) * g ); the reference writes sqrt as pow(.,0.5) (nn/mod.rs:117-122);
+// sqrtf is used here, within the logits tolerance.  One CTA per row; source row = in + (m*row_mul+row_off)*H.
+template <class T>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ in, const T* __restrict__ gain,
+                                                      T* __restrict__ out, int H, float eps, long long row_mul,
+                                                      long long row_off) {
+  __shared__ float scratch[8];
+  const T* x = in + ((long long)blockIdx.x * row_mul + row_off) * H;
+  T* y = out + (long long)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    float v = Elem<T>::load(x[i]);
+    ss += v * v;
+  }
+  ss = block_sum_256(ss, scratch);
+  float rms = sqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += 256) {
+    float n = rt<T>(Elem<T>::load(x[i]) / rms);
+    y[i] = Elem<T>::store(n * Elem<T>::load(gain[i]));
+  }
+}
+
+// ---- weight-streaming GEMV with fused prologue/epilogue --------------------------------------------
+// out[m, n] = epilogue( sum_k xin[m, k] * W[n, k] ),  m < M <= MT, W rows K-contiguous (the [out,in] layout of
+// every linear layer, nn/mod.rs:182-204: x @ transpose(W) without ever forming the transpose or its broadcast).
+enum { PRO_NONE = 0, PRO_NORM = 1 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2 };
+
+struct GemvArgs {
+  const void* w[3];   // up to three weight matrices stacked along N (q,k,v) or paired (gate, up)
+  int n_end[3];       // exclusive end row of each segment in the stacked N space
+  const void* x;      // [M, K] rows at x + m * x_row_stride
+  long long x_row_stride;
+  const void* gain;   // PRO_NORM: RMSNorm gain [K]
+  float eps;
+  void* out;          // [M, N]
+  const void* res;    // EPI_RESIDUAL: [M, N], may alias out
+  int M, N, K;
+};
+
+template <class T>
+__device__ __forceinline__ const T* gemv_row(const GemvArgs& a, int n) {
+  int seg = n < a.n_end[0] ? 0 : (n < a.n_end[1] ? 1 : 2);
+  int base = seg == 0 ? 0 : a.n_end[seg - 1];
+  return (const T*)a.w[seg] + (long long)(n - base) * a.K;
+}
+
+// 256 threads; each warp owns a PAIR of weight rows per iteration (two columns, or gate[n]/up[n] for
+// EPI_SILU_MUL) and streams them with 16-byte loads; the M input rows sit in shared memory as T.
+template <class T, int MT, int PRO, int EPI>
+__global__ void __launch_bounds__(256) gemv_fused_kernel(GemvArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* xs = reinterpret_cast<T*>(smem_raw);  // [MT][K]
+  __shared__ float scratch[8];
+  constexpr int VEC = 16 / sizeof(T);
+  const int K = a.K;
+  const T* xin = (const T*)a.x;
+
+  if (PRO == PRO_NORM) {
+    const T* g = (const T*)a.gain;
+    for (int m = 0; m < MT; ++m) {
+      if (m < a.M) {
+        const T* x = xin + m * a.x_row_stride;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < K; i += 256) {
+          float v = Elem<T>::load(x[i]);
+          ss += v * v;
+        }
+        ss = block_sum_256(ss, scratch);
+        float rms = sqrtf(ss / (float)K + a.eps);
+        for (int i = threadIdx.x; i < K; i += 256) {
+          float n = rt<T>(Elem<T>::load(x[i]) / rms);
+          xs[m * K + i] = Elem<T>::store(n * Elem<T>::load(g[i]));
+        }
+      } else {
+        for (int i = threadIdx.x; i < K; i += 256) xs[m * K + i] = Elem<T>::store(0.f);
+      }
+    }
+  } else {
+    for (int e = threadIdx.x; e < MT * (K / VEC); e += 256) {
+      int m = e / (K / VEC), c = e - m * (K / VEC);
+      VecT<T, VEC> v;
+      if (m < a.M) v = *reinterpret_cast<const VecT<T, VEC>*>(xin + m * a.x_row_stride + c * VEC);
+      else memset(&v, 0, sizeof(v));
+      *reinterpret_cast<VecT<T, VEC>*>(xs + m * K + c * VEC) = v;
+    }
+  }
+  __syncthreads();
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_pairs = EPI == EPI_SILU_MUL ? a.N : (a.N + 1) / 2;
+  const int nvec = K / VEC;
+  for (int p = blockIdx.x * 8 + warp; p < n_pairs; p += gridDim.x * 8) {
+    int n0, n1;
+    const T *w0, *w1;
+    if (EPI == EPI_SILU_MUL) {
+      n0 = n1 = p;
+      w0 = (const T*)a.w[0] + (long long)p * K;
+      w1 = (const T*)a.w[1] + (long long)p * K;
+    } else {
+      n0 = 2 * p;
+      n1 = 2 * p + 1 < a.N ? 2 * p + 1 : n0;
+      w0 = gemv_row<T>(a, n0);
+      w1 = gemv_row<T>(a, n1);
+    }
+    float acc0[MT], acc1[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
+#pragma unroll 4
+    for (int v = lane; v < nvec; v += 32) {
+      VecT<T, VEC> a0 = *reinterpret_cast<const VecT<T, VEC>*>(w0 + v * VEC);
+      VecT<T, VEC> a1 = *reinterpret_cast<const VecT<T, VEC>*>(w1 + v * VEC);
+      float f0[VEC], f1[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        f0[i] = Elem<T>::load(a0.v[i]);
+        f1[i] = Elem<T>::load(a1.v[i]);
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        VecT<T, VEC> xv = *reinterpret_cast<const VecT<T, VEC>*>(xs + m * K + v * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          float xf = Elem<T>::load(xv.v[i]);
+          acc0[m] = fmaf(xf, f0[i], acc0[m]);
+          acc1[m] = fmaf(xf, f1[i], acc1[m]);
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      float s0 = warp_sum(acc0[m]);
+      float s1 = warp_sum(acc1[m]);
+      if (lane == 0 && m < a.M) {
+        T* o = (T*)a.out + (long long)m * a.N;
+        if (EPI == EPI_STORE) {
+          o[n0] = Elem<T>::store(s0);
+          if (n1 != n0) o[n1] = Elem<T>::store(s1);
+        } else if (EPI == EPI_RESIDUAL) {
+          // x = res + linear(.)  (llama.rs:375,384): the linear output is a T tensor, then one add in T
+          const T* r = (const T*)a.res + (long long)m * a.N;
+          o[n0] = Elem<T>::store(Elem<T>::load(r[n0]) + rt<T>(s0));
+          if (n1 != n0) o[n1] = Elem<T>::store(Elem<T>::load(r[n1]) + rt<T>(s1));
+        } else {
+          // silu(gate) * up  (llama.rs:245; nn/mod.rs:124-148): gate, up are T tensors; silu runs in f32 as
+          // x * (1 / (1 + exp(-x))) and is cast back to T before the multiply in T.
+          float g = rt<T>(s0), u = rt<T>(s1);
+          float sg = 1.f / (1.f + expf(-g));
+          float si = rt<T>(g * sg);
+          o[n0] = Elem<T>::store(si * u);
+        }
+      }
+    }
+  }
+}
+
+// ---- RoPE + KV append (helpers/rope.rs:423-451; helpers/cache.rs:30-39) ----------------------------
+// One CTA per token m = (b, s).  q is rotated in place; rotated k and plain v go to the cache row `pos`.
+// cos/sin tables are [P, HD/2] f32 (the reference concatenates each with itself, rope.rs:100-101).
+struct RopeArgs {
+  void* q; long long q_row_stride;        // [M, nh*HD]
+  const void* k; long long k_row_stride;  // [M, nkv*HD]
+  const void* v; long long v_row_stride;
+  void* kc; void* vc;                     // this layer's cache slices [B, nkv, P, HD]
+  const float* cos_t; const float* sin_t;
+  const int* ctx_len;                     // device scalar: positions already in the cache
+  int B, S, nh, nkv, HD, P;
+};
+template <class T>
+__global__ void __launch_bounds__(256) rope_append_kernel(RopeArgs a, unsigned* err) {
+  const int m = blockIdx.x, b = m / a.S, s = m - b * a.S;
+  const int pos = *a.ctx_len + s;
+  if (pos >= a.P) {
+    if (threadIdx.x == 0) atomicOr(err, DEV_ERR_INDEX_OOB);
+    return;
+  }
+  const int half = a.HD / 2;
+  T* q = (T*)a.q + (long long)m * a.q_row_stride;
+  const T* k = (const T*)a.k + (long long)m * a.k_row_stride;
+  const T* v = (const T*)a.v + (long long)m * a.v_row_stride;
+  const float* ct = a.cos_t + (long long)pos * half;
+  const float* st = a.sin_t + (long long)pos * half;
+  const int q_pairs = a.nh * half, k_pairs = a.nkv * half;
+  for (int e = threadIdx.x; e < q_pairs + k_pairs; e += 256) {
+    bool is_q = e < q_pairs;
+    int ee = is_q ? e : e - q_pairs;
+    int h = ee / half, i = ee - h * half;
+    const T* src = is_q ? q + h * a.HD : k + h * a.HD;
+    float x1 = Elem<T>::load(src[i]), x2 = Elem<T>::load(src[i + half]);
+    float c = ct[i], sn = st[i];
+    // cos*x + sin*rotate_half(x), rotate_half = cat(-x2, x1): two products and one sum, each rounded
+    float o1 = c * x1 + sn * (-x2);
+    float o2 = c * x2 + sn * x1;
+    T* dst = is_q ? q + h * a.HD : (T*)a.kc + (((long long)b * a.nkv + h) * a.P + pos) * a.HD;
+    dst[i] = Elem<T>::store(o1);
+    dst[i + half] = Elem<T>::store(o2);
+  }
+  for (int e = threadIdx.x; e < a.nkv * a.HD; e += 256) {
+    int h = e / a.HD, i = e - h * a.HD;
+    ((T*)a.vc)[(((long long)b * a.nkv + h) * a.P + pos) * a.HD + i] = v[e];
+  }
+}
+
+// ---- decode attention, S = 1 (llama.rs:322-345) ------------------------------------------------------
+// One CTA per (query head, sequence).  scores = T(q.k), T(scores / T(sqrt(HD))), softmax in f32 -> T,
+// out = T(P.v).  The causal-mask row of a single new token is all -0.0 and adding it changes nothing
+// (helpers/tensors.rs:207-224), so it is skipped.  GQA: head h reads kv head h / rep (repeat_kv,
+// tensors.rs:128-151, never materialised).
+struct AttnArgs {
+  const void* q; long long q_row_stride;  // [B, nh*HD] (rotated)
+  const void* kc; const void* vc;         // [B, nkv, P, HD]
+  void* out; long long out_row_stride;    // [B, nh*HD]
+  const int* ctx_len;                     // positions in the cache BEFORE this step; this step appended one
+  int nh, nkv, P;
+  float scale;                            // T(sqrt(HD)) widened
+};
+template <class T, int HD>
+__global__ void __launch_bounds__(256) attn_decode_kernel(AttnArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* sc = reinterpret_cast<float*>(smem_raw);  // [P] scores / probabilities
+  __shared__ float scratch[8];
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int LPK = HD / VEC;        // lanes per key
+  constexpr int KPW = 32 / LPK;        // keys per warp per iteration
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int kvh = h / (a.nh / a.nkv);
+  const int total = *a.ctx_len + 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % LPK, kslot = lane / LPK;
+  const T* q = (const T*)a.q + (long long)b * a.q_row_stride + h * HD;
+  const T* kc = (const T*)a.kc + ((long long)b * a.nkv + kvh) * a.P * HD;
+  const T* vc = (const T*)a.vc + ((long long)b * a.nkv + kvh) * a.P * HD;
+
+  float qf[VEC];
+  {
+    VecT<T, VEC> qv = *reinterpret_cast<const VecT<T, VEC>*>(q + sub * VEC);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) qf[i] = Elem<T>::load(qv.v[i]);
+  }
+  for (int t0 = warp * KPW; t0 < total; t0 += 8 * KPW) {
+    int t = t0 + kslot;
+    float d = 0.f;
+    if (t < total) {
+      VecT<T, VEC> kv = *reinterpret_cast<const VecT<T, VEC>*>(kc + (long long)t * HD + sub * VEC);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) d = fmaf(qf[i], Elem<T>::load(kv.v[i]), d);
+    }
+#pragma unroll
+    for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    if (sub == 0 && t < total) sc[t] = rt<T>(rt<T>(d) / a.scale);
+  }
+  __syncthreads();
+  float mx = -FLT_MAX;  // `max` folds from f32::MIN (ndarray.rs:656-661)
+  for (int t = threadIdx.x; t < total; t += 256) mx = fmaxf(mx, sc[t]);
+  mx = block_max_256(mx, scratch);
+  float sum = 0.f;
+  for (int t = threadIdx.x; t < total; t += 256) {
+    float e = expf(sc[t] - mx);
+    sc[t] = e;
+    sum += e;
+  }
+  sum = block_sum_256(sum, scratch);
+  for (int t = threadIdx.x; t < total; t += 256) sc[t] = rt<T>(sc[t] / sum);
+  __syncthreads();
+
+  // P.v: thread = (16-byte chunk of the head dim, key group); partial sums over its keys, then a fixed-order
+  // reduction over the key groups through shared memory.
+  constexpr int NCH = HD / VEC, TG = 256 / NCH;
+  float* part = sc + a.P;  // [TG][HD]
+  const int ch = threadIdx.x % NCH, tg = threadIdx.x / NCH;
+  float acc[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+  for (int t = tg; t < total; t += TG) {
+    float p = sc[t];
+    VecT<T, VEC> vv = *reinterpret_cast<const VecT<T, VEC>*>(vc + (long long)t * HD + ch * VEC);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(p, Elem<T>::load(vv.v[i]), acc[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) part[tg * HD + ch * VEC + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < HD) {
+    float s = 0.f;
+    for (int g = 0; g < TG; ++g) s += part[g * HD + threadIdx.x];
+    ((T*)a.out)[(long long)b * a.out_row_stride + h * HD + threadIdx.x] = Elem<T>::store(s);
+  }
+}
+
+// ---- prefill: scale + causal mask + softmax over score rows (llama.rs:330-339) ------------------------
+// Row r = ((b*nh + h)*S + s) of scores [.., S, Tt] (T, in place): x = T(x / scale); x = T(x + mask) where the
+// mask is T(f32::MIN) for keys after position T0+s (in bf16 that is -inf) and -0.0 otherwise; softmax in f32.
+template <class T>
+__global__ void __launch_bounds__(256) softmax_mask_kernel(T* __restrict__ scores, int S, int Tt, int T0, float scale) {
+  __shared__ float scratch[8];
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* row = reinterpret_cast<float*>(smem_raw);  // [Tt]
+  T* x = scores + (long long)blockIdx.x * Tt;
+  const int s = blockIdx.x % S;
+  const float masked = rt<T>(-FLT_MAX);
+  float mx = -FLT_MAX;
+  for (int t = threadIdx.x; t < Tt; t += 256) {
+    float v = rt<T>(Elem<T>::load(x[t]) / scale);
+    v = rt<T>(v + (t > T0 + s ? masked : -0.0f));
+    row[t] = v;
+    mx = fmaxf(mx, v);
+  }
+  mx = block_max_256(mx, scratch);
+  float sum = 0.f;
+  for (int t = threadIdx.x; t < Tt; t += 256) {
+    float e = expf(row[t] - mx);
+    row[t] = e;
+    sum += e;
+  }
+  sum = block_sum_256(sum, scratch);
+  for (int t = threadIdx.x; t < Tt; t += 256) x[t] = Elem<T>::store(row[t] / sum);
+}
+
+// out[b, s, h, :] = in[b, h, s, :]  (the transpose(1,2) + reshape after attention, llama.rs:342-344)
+template <class T>
+__global__ void __launch_bounds__(256) bhsd_to_bshd_kernel(const T* __restrict__ in, T* __restrict__ out, int B, int nh,
+                                                           int S, int HD) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int per = HD / VEC;
+  const long long total = (long long)B * nh * S * per;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int c = (int)(t % per);
+    long long r = t / per;
+    int s = (int)(r % S);
+    r /= S;
+    int h = (int)(r % nh);
+    int b = (int)(r / nh);
+    VecT<T, VEC> v = *reinterpret_cast<const VecT<T, VEC>*>(in + t * VEC);
+    *reinterpret_cast<VecT<T, VEC>*>(out + (((long long)b * S + s) * nh + h) * HD + c * VEC) = v;
+  }
+}
+
+// h = T( T(silu(gate)) * up )  for the GEMM path (same rounding points as EPI_SILU_MUL)
+template <class T>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up,
+                                                       T* __restrict__ out, long long n) {
+  constexpr int VEC = 16 / sizeof(T);
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n / VEC; t += (long long)gridDim.x * blockDim.x) {
+    VecT<T, VEC> g = *reinterpret_cast<const VecT<T, VEC>*>(gate + t * VEC);
+    VecT<T, VEC> u = *reinterpret_cast<const VecT<T, VEC>*>(up + t * VEC);
+    VecT<T, VEC> o;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      float gf = Elem<T>::load(g.v[i]);
+      float sg = 1.f / (1.f + expf(-gf));
+      float si = rt<T>(gf * sg);
+      o.v[i] = Elem<T>::store(si * Elem<T>::load(u.v[i]));
+    }
+    *reinterpret_cast<VecT<T, VEC>*>(out + t * VEC) = o;
+  }
+}
+
+// x = T(x + y)  (residual add for the GEMM path)
+template <class T>
+__global__ void __launch_bounds__(256) add_inplace_kernel(T* __restrict__ x, const T* __restrict__ y, long long n) {
+  constexpr int VEC = 16 / sizeof(T);
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n / VEC; t += (long long)gridDim.x * blockDim.x) {
+    VecT<T, VEC> a = *reinterpret_cast<const VecT<T, VEC>*>(x + t * VEC);
+    VecT<T, VEC> b = *reinterpret_cast<const VecT<T, VEC>*>(y + t * VEC);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) a.v[i] = Elem<T>::store(Elem<T>::load(a.v[i]) + Elem<T>::load(b.v[i]));
+    *reinterpret_cast<VecT<T, VEC>*>(x + t * VEC) = a;
+  }
+}
+
+// RoPE tables, the f32 op sequence of rope_tables_default (helpers/rope.rs:65-104):
+// f = i * (2/HD); freq = pow(theta, f); inv = 1/freq; inv = inv / 1.0; ang = pos * inv; cos, sin.
+__global__ void rope_table_kernel(float* cos_t, float* sin_t, int P, int half, float theta, float two_over_d) {
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < P * half; e += gridDim.x * blockDim.x) {
+    int pos = e / half, i = e - pos * half;
+    float f = (float)i * two_over_d;
+    float inv = 1.0f / powf(theta, f);
+    inv = inv / 1.0f;
+    float ang = (float)pos * inv;
+    cos_t[e] = cosf(ang);
+    sin_t[e] = sinf(ang);
+  }
+}
+
+// End of a step: the greedy ids of this step become the next step's input, are recorded for the host, and
+// the context length advances.
+__global__ void advance_kernel(const unsigned* __restrict__ new_ids, unsigned* __restrict__ cur_ids,
+                               unsigned* __restrict__ out_ids, int* ctx_len, int* step_no, int B, int S,
+                               int out_cap_steps) {
+  int step = *step_no;
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    unsigned id = new_ids[b];
+    cur_ids[b] = id;
+    if (step < out_cap_steps) out_ids[(long long)step * B + b] = id;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *ctx_len += S;
+    *step_no = step + 1;
+  }
+}
+
+}  // namespace cgk

@@ -1,0 +1,165 @@
+"""Llama through the C ABI on the GPU against the CPU oracle (BASELINE config 1 and reduced bf16 shapes).
+
+Bars: greedy ids exact and f32 logits within rel 1e-4 on the tiny model; bf16 logits within 2e-2 max-abs of the
+f32 oracle run on the same (bf16-rounded) weights."""
+import numpy as np
+import pytest
+
+import catgrad_b200 as cb
+from catgrad_b200 import Dtype
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+REL_F32 = 1e-4
+ABS_BF16 = 2e-2
+
+
+def tiny_inputs():
+    cfg = cb.TINY
+    w = cb.random_weights(cfg, seed=0)
+    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(1, 64), dtype=np.uint32)
+    return cfg, w, ids
+
+
+@pytest.fixture(scope="module")
+def oracle_tiny(oracle):
+    cfg, w, ids = tiny_inputs()
+    term = cb.llama_term(oracle, cfg, tap_logits=True)
+    params = cb.upload_weights(oracle, w, Dtype.F32)
+    out, logits = cb.generate_with_interpreter(oracle, term, params, cfg, ids, 33, Dtype.F32, 97, tap=True)
+    return out, logits
+
+
+def test_config1_interpreter_path(gpu, oracle_tiny):
+    """64-token prompt + 32 greedy steps through the op-by-op interpreter: ids exact, logits rel <= 1e-4."""
+    cfg, w, ids = tiny_inputs()
+    ref_ids, ref_logits = oracle_tiny
+    term = cb.llama_term(gpu, cfg, tap_logits=True)
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    out, logits = cb.generate_with_interpreter(gpu, term, params, cfg, ids, 33, Dtype.F32, 97, tap=True)
+    np.testing.assert_array_equal(out, ref_ids)
+    for a, b in zip(logits, ref_logits):
+        assert helpers.rel_err(a, b) <= REL_F32
+
+
+def test_config1_fused_runner(gpu, oracle_tiny):
+    cfg, w, ids = tiny_inputs()
+    ref_ids, ref_logits = oracle_tiny
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    runner = cb.LlamaRunner(gpu, cfg, params, Dtype.F32, max_batch=1, max_positions=97)
+    out = runner.generate(ids, 33)
+    np.testing.assert_array_equal(out, ref_ids)
+    # logits after the prefill and after every decode step, stepping by hand
+    runner.reset(1)
+    first = runner.forward(ids)
+    assert helpers.rel_err(runner.last_logits()[0], ref_logits[0][0, -1]) <= REL_F32
+    tok = first
+    for i in range(1, 6):
+        tok = runner.forward(tok.reshape(1, 1))
+        assert helpers.rel_err(runner.last_logits()[0], ref_logits[i][0, -1]) <= REL_F32
+        assert tok[0] == ref_ids[0, i]
+    assert runner.context_len == 64 + 5
+    assert runner.launch_count > 0
+
+
+def test_fused_runner_batch_and_graph_replay_match_stepwise(gpu):
+    """Batch of 3 sequences: decode through the captured graph equals stepping one call at a time, and every
+    sequence equals running it alone (batch independence, which batch-sharding across GPUs relies on)."""
+    cfg, w, _ = tiny_inputs()
+    ids = np.random.default_rng(11).integers(0, cfg.vocab_size, size=(3, 16), dtype=np.uint32)
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    runner = cb.LlamaRunner(gpu, cfg, params, Dtype.F32, max_batch=3, max_positions=64)
+    out = runner.generate(ids, 12)
+    runner.reset(3)
+    tok = runner.forward(ids)
+    cols = [tok]
+    for _ in range(11):
+        tok = runner.forward(tok.reshape(3, 1))
+        cols.append(tok)
+    np.testing.assert_array_equal(out, np.stack(cols, 1))
+    solo = cb.LlamaRunner(gpu, cfg, params, Dtype.F32, max_batch=1, max_positions=64)
+    for b in range(3):
+        np.testing.assert_array_equal(solo.generate(ids[b:b + 1], 12)[0], out[b])
+
+
+def small_bf16_model():
+    # Llama-3.2-1B proportions (GQA 4:1, head_dim 64, tied head, theta 5e5) at 2 layers / hidden 512
+    cfg = cb.LlamaConfig(512, 1536, 2, 8, 2, 4096, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=True)
+    w = cb.random_weights(cfg, seed=0)
+    wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(2, 40), dtype=np.uint32)
+    return cfg, wb, ids
+
+
+def test_bf16_logits_against_f32_oracle(oracle, gpu):
+    cfg, wb, ids = small_bf16_model()
+    term_o = cb.llama_term(oracle, cfg, tap_logits=True)
+    po = cb.upload_weights(oracle, wb, Dtype.F32)
+    ref_ids, ref_logits = cb.generate_with_interpreter(oracle, term_o, po, cfg, ids, 4, Dtype.F32, 64, tap=True)
+
+    # op-by-op interpreter on the GPU in bf16
+    term_g = cb.llama_term(gpu, cfg, tap_logits=True)
+    pg = cb.upload_weights(gpu, wb, Dtype.BF16)
+    out_i, logits_i = cb.generate_with_interpreter(gpu, term_g, pg, cfg, ids, 4, Dtype.BF16, 64, tap=True)
+    for a, b in zip(logits_i, ref_logits):
+        assert np.abs(a[:, -1] - b[:, -1]).max() <= ABS_BF16
+
+    # fused runner in bf16: same bar against the oracle, and near-identical to the unfused GPU path
+    runner = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=2, max_positions=64)
+    runner.reset(2)
+    tok = runner.forward(ids)
+    lg = runner.last_logits()
+    assert np.abs(lg - ref_logits[0][:, -1]).max() <= ABS_BF16
+    assert np.abs(lg - logits_i[0][:, -1]).max() <= ABS_BF16
+    for i in range(1, 4):
+        tok = runner.forward(ref_ids[:, i - 1].reshape(2, 1))   # teacher-forced with the oracle's ids
+        lg = runner.last_logits()
+        assert np.abs(lg - ref_logits[i][:, -1]).max() <= ABS_BF16
+
+
+def test_oracle_bf16_interpreter_matches_gpu_bf16_interpreter(oracle, gpu):
+    """Same bf16 op stream on both sides (the oracle rounds at every op output like the GPU kernels): logits agree
+    to bf16 resolution."""
+    cfg, wb, ids = small_bf16_model()
+    res = []
+    for be in (oracle, gpu):
+        term = cb.llama_term(be, cfg, tap_logits=True)
+        p = cb.upload_weights(be, wb, Dtype.BF16)
+        _, logits = cb.generate_with_interpreter(be, term, p, cfg, ids[:, :12], 1, Dtype.BF16, 32, tap=True)
+        res.append(logits[0])
+    assert np.abs(res[0] - res[1]).max() <= ABS_BF16
+
+
+def test_kv_cache_roundtrip_property(gpu):
+    """Prefill(prompt) then one decode step equals prefill(prompt + token): the appended cache row and the
+    single-row attention path reproduce what the full causal pass computes."""
+    cfg, w, _ = tiny_inputs()
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    ids = np.random.default_rng(5).integers(0, cfg.vocab_size, size=(2, 24), dtype=np.uint32)
+    r = cb.LlamaRunner(gpu, cfg, params, Dtype.F32, max_batch=2, max_positions=64)
+    r.reset(2)
+    r.forward(ids[:, :23])
+    r.forward(ids[:, 23:24])
+    a = r.last_logits()
+    r.reset(2)
+    r.forward(ids)
+    b = r.last_logits()
+    assert helpers.rel_err(a, b) <= REL_F32
+
+
+def test_runner_refuses_bad_use(gpu):
+    cfg, w, ids = tiny_inputs()
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    r = cb.LlamaRunner(gpu, cfg, params, Dtype.F32, max_batch=1, max_positions=32)
+    r.reset(1)
+    with pytest.raises(cb.BackendError):
+        r.forward(ids)                       # 64 tokens > max_positions
+    with pytest.raises(cb.BackendError):
+        cb.LlamaRunner(gpu, cfg, cb.Parameters(gpu), Dtype.F32, 1, 32)   # missing parameters
+    bad = np.full((1, 4), cfg.vocab_size + 5, np.uint32)
+    r.reset(1)
+    with pytest.raises(cb.BackendError):
+        r.forward(bad)                       # token id outside the vocabulary: reported, not trapped
+    r.reset(1)
+    assert r.forward(ids[:, :8]).shape == (1,)

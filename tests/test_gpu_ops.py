@@ -1,0 +1,305 @@
+"""Parity of the CUDA backend with the CPU oracle, op by op, through the C ABI.
+
+Bit-exact for integer/index/shape ops and for the correctly-rounded float ops (add/sub/mul/div/neg/floor/round/
+compare/where/cast/max); libm-vs-CUDA ulp tolerance for exp/log/sin/cos/pow; accumulation-order tolerance for
+sum/matmul (tolerances stated per test)."""
+import numpy as np
+import pytest
+
+import catgrad_b200 as cb
+from catgrad_b200 import Dtype
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+FLOAT_DTYPES = [Dtype.F32, Dtype.BF16, Dtype.F16]
+
+
+def both(oracle, gpu, arr, dtype=None):
+    return oracle.from_numpy(arr, dtype), gpu.from_numpy(arr, dtype)
+
+
+def same_bits(oracle, gpu, ro, rg):
+    assert ro.dtype == rg.dtype and ro.shape == rg.shape
+    a, b = oracle.to_numpy(ro), gpu.to_numpy(rg)
+    if a.dtype == np.float32:
+        a, b = a.view(np.uint32), b.view(np.uint32)
+    if a.dtype == np.float16:
+        a, b = a.view(np.uint16), b.view(np.uint16)
+    np.testing.assert_array_equal(a, b)
+
+
+@pytest.mark.parametrize("case", helpers.golden_cases("op"), ids=lambda c: c["name"])
+def test_reference_vectors(gpu, case):
+    run = helpers.call_op_via_interpreter if case.get("via_interpreter") else helpers.call_op
+    helpers.check_expect(gpu, run(gpu, case), case)
+
+
+@pytest.mark.parametrize("case", helpers.golden_cases("error"), ids=lambda c: c["name"])
+def test_shape_mismatch_is_refused(gpu, case):
+    with pytest.raises(cb.BackendError) as e:
+        helpers.call_op(gpu, case)
+    assert e.value.status.name == case["error"]
+    assert "Shape mismatch in operation" in str(e.value)
+
+
+@pytest.mark.parametrize("case", helpers.golden_cases("graph"), ids=lambda c: c["name"])
+def test_helper_graphs(gpu, case):
+    helpers.check_expect(gpu, helpers.run_graph_case(gpu, case), case)
+
+
+@pytest.mark.parametrize("dtype", FLOAT_DTYPES, ids=lambda d: d.name)
+@pytest.mark.parametrize("shape", [(4096, 1024), (37, 129), (1,), (3, 5, 7, 2), (0, 4)], ids=str)
+def test_exact_float_binary_ops(oracle, gpu, dtype, shape):
+    rng = np.random.default_rng(2)
+    a = rng.uniform(-4, 4, shape).astype(np.float32)
+    b = rng.uniform(-4, 4, shape).astype(np.float32)
+    if a.size > 4:
+        b.reshape(-1)[:3] = [0.0, -0.0, np.inf]
+        a.reshape(-1)[:3] = [1.0, -1.0, np.nan]
+    ao, ag = both(oracle, gpu, a, dtype)
+    bo, bg = both(oracle, gpu, b, dtype)
+    for op in ("add", "sub", "mul", "div", "lt", "gt", "gte", "lte", "eq"):
+        same_bits(oracle, gpu, getattr(oracle, op)(ao, bo), getattr(gpu, op)(ag, bg))
+    same_bits(oracle, gpu, oracle.where_cond(ao, ao, bo), gpu.where_cond(ag, ag, bg))
+    for op in ("neg", "floor", "round"):
+        same_bits(oracle, gpu, getattr(oracle, op)(ao), getattr(gpu, op)(ag))
+
+
+def test_broadcast_row_vector_sweep_shape(oracle, gpu):
+    """The op-sweep layout: [4096, 8192] against an explicitly broadcast [8192] row vector (scaled down in rows
+    so the CPU oracle finishes in seconds; the row length is the full 8192)."""
+    rng = np.random.default_rng(2)
+    x = rng.uniform(-4, 4, (256, 8192)).astype(np.float32)
+    v = rng.uniform(-4, 4, (8192,)).astype(np.float32)
+    for dtype in (Dtype.F32, Dtype.BF16):
+        xo, xg = both(oracle, gpu, x, dtype)
+        vo, vg = both(oracle, gpu, v, dtype)
+        bo, bg = oracle.broadcast(vo, x.shape), gpu.broadcast(vg, x.shape)
+        assert bg.strides == (0, 1)          # a view, not a copy
+        for op in ("add", "mul", "div"):
+            same_bits(oracle, gpu, getattr(oracle, op)(xo, bo), getattr(gpu, op)(xg, bg))
+        eo, eg = oracle.exp(xo), gpu.exp(xg)
+        tol = 2e-6 if dtype == Dtype.F32 else 1e-2
+        np.testing.assert_allclose(gpu.to_f32(eg), oracle.to_f32(eo), rtol=tol)
+
+
+def test_strided_and_column_broadcast_operands(oracle, gpu):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((6, 10, 12)).astype(np.float32)
+    y = rng.standard_normal((6, 12, 10)).astype(np.float32)
+    c = rng.standard_normal((6, 10, 1)).astype(np.float32)
+    for dtype in (Dtype.F32, Dtype.BF16):
+        xo, xg = both(oracle, gpu, x, dtype)
+        yo, yg = both(oracle, gpu, y, dtype)
+        co, cg = both(oracle, gpu, c, dtype)
+        same_bits(oracle, gpu, oracle.add(xo, oracle.transpose(yo, 1, 2)), gpu.add(xg, gpu.transpose(yg, 1, 2)))
+        same_bits(oracle, gpu, oracle.sub(xo, oracle.broadcast(co, x.shape)), gpu.sub(xg, gpu.broadcast(cg, x.shape)))
+        so, sg = oracle.slice(xo, 2, 3, 5), gpu.slice(xg, 2, 3, 5)
+        same_bits(oracle, gpu, oracle.mul(so, so), gpu.mul(sg, sg))
+        same_bits(oracle, gpu, oracle.reshape(oracle.transpose(xo, 0, 2), (12, 60)), gpu.reshape(gpu.transpose(xg, 0, 2), (12, 60)))
+
+
+def test_u32_ops(oracle, gpu):
+    rng = np.random.default_rng(4)
+    a = rng.integers(0, 2**32, (33, 17), dtype=np.uint32)
+    b = rng.integers(1, 2**32, (33, 17), dtype=np.uint32)
+    ao, ag = both(oracle, gpu, a)
+    bo, bg = both(oracle, gpu, b)
+    for op in ("add", "sub", "mul", "div", "lt", "gt", "gte", "lte", "eq"):
+        same_bits(oracle, gpu, getattr(oracle, op)(ao, bo), getattr(gpu, op)(ag, bg))
+    e = rng.integers(0, 6, (33, 17), dtype=np.uint32)
+    eo, eg = both(oracle, gpu, e)
+    same_bits(oracle, gpu, oracle.pow(ao, eo), gpu.pow(ag, eg))
+    same_bits(oracle, gpu, oracle.neg(ao), gpu.neg(ag))
+    same_bits(oracle, gpu, oracle.where_cond(eo, ao, bo), gpu.where_cond(eg, ag, bg))
+    same_bits(oracle, gpu, oracle.sum(ao), gpu.sum(ag))
+    same_bits(oracle, gpu, oracle.max(ao), gpu.max(ag))
+    same_bits(oracle, gpu, oracle.argmax(ao), gpu.argmax(ag))
+    small = rng.integers(0, 50, (4, 6, 5), dtype=np.uint32)
+    so, sg = both(oracle, gpu, small)
+    same_bits(oracle, gpu, oracle.matmul(so, oracle.transpose(so, 1, 2)), gpu.matmul(sg, gpu.transpose(sg, 1, 2)))
+    with pytest.raises(cb.BackendError):
+        gpu.sin(ag)
+
+
+@pytest.mark.parametrize("dtype", FLOAT_DTYPES, ids=lambda d: d.name)
+def test_transcendentals(oracle, gpu, dtype):
+    """libm (the reference's f32::exp etc.) vs CUDA's full-precision functions: a few ulp in f32."""
+    rng = np.random.default_rng(5)
+    x = rng.uniform(-4, 4, (513, 77)).astype(np.float32)
+    xo, xg = both(oracle, gpu, x, dtype)
+    rtol, atol = (4e-6, 1e-6) if dtype == Dtype.F32 else (1e-2, 1e-2)
+    for op in ("exp", "sin", "cos"):
+        np.testing.assert_allclose(gpu.to_f32(getattr(gpu, op)(xg)), oracle.to_f32(getattr(oracle, op)(xo)), rtol=rtol, atol=atol)
+    p = np.abs(x) + 0.5
+    po, pg = both(oracle, gpu, p, dtype)
+    np.testing.assert_allclose(gpu.to_f32(gpu.log(pg)), oracle.to_f32(oracle.log(po)), rtol=rtol, atol=atol)
+    np.testing.assert_allclose(gpu.to_f32(gpu.pow(pg, xg)), oracle.to_f32(oracle.pow(po, xo)), rtol=2e-5 if dtype == Dtype.F32 else 2e-2)
+
+
+def test_casts(oracle, gpu):
+    rng = np.random.default_rng(6)
+    x = np.concatenate([rng.uniform(-10, 300, 1000), [np.nan, np.inf, -np.inf, 5e9, -0.0, 0.49999997, 2.5, 16777217.0]]).astype(np.float32)
+    xo, xg = both(oracle, gpu, x)
+    for target in (Dtype.U32, Dtype.BF16, Dtype.F16, Dtype.F32):
+        same_bits(oracle, gpu, oracle.cast(xo, target), gpu.cast(xg, target))
+    u = rng.integers(0, 2**32, 1000, dtype=np.uint32)
+    uo, ug = both(oracle, gpu, u)
+    for target in (Dtype.F32, Dtype.BF16, Dtype.F16):
+        same_bits(oracle, gpu, oracle.cast(uo, target), gpu.cast(ug, target))
+    bo, bg = both(oracle, gpu, x, Dtype.BF16)
+    for target in (Dtype.F32, Dtype.U32, Dtype.F16):
+        same_bits(oracle, gpu, oracle.cast(bo, target), gpu.cast(bg, target))
+    # strided source
+    m = rng.standard_normal((9, 16)).astype(np.float32)
+    mo, mg = both(oracle, gpu, m)
+    same_bits(oracle, gpu, oracle.cast(oracle.transpose(mo, 0, 1), Dtype.BF16), gpu.cast(gpu.transpose(mg, 0, 1), Dtype.BF16))
+
+
+@pytest.mark.parametrize("shape", [(512, 4096), (7, 3, 1000), (5, 1), (3, 33)], ids=str)
+def test_reductions(oracle, gpu, shape):
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal(shape).astype(np.float32)
+    for dtype in (Dtype.F32, Dtype.BF16):
+        xo, xg = both(oracle, gpu, x, dtype)
+        same_bits(oracle, gpu, oracle.max(xo), gpu.max(xg))
+        same_bits(oracle, gpu, oracle.argmax(xo), gpu.argmax(xg))
+        tol = 1e-5 if dtype == Dtype.F32 else 1e-2
+        np.testing.assert_allclose(gpu.to_f32(gpu.sum(xg)), oracle.to_f32(oracle.sum(xo)), rtol=tol, atol=tol * shape[-1] ** 0.5)
+        # strided rows (reduce over a transposed view)
+        if len(shape) == 2:
+            to, tg = oracle.transpose(xo, 0, 1), gpu.transpose(xg, 0, 1)
+            same_bits(oracle, gpu, oracle.max(to), gpu.max(tg))
+            same_bits(oracle, gpu, oracle.argmax(to), gpu.argmax(tg))
+
+
+def test_softmax_graph_sweep_shape(oracle, gpu):
+    """nn::softmax (stdlib/nn/mod.rs:168-179) as the 9-op graph, rows of 4096 (fewer rows than the sweep's 8192)."""
+    rng = np.random.default_rng(2)
+    x = rng.uniform(-4, 4, (128, 4096)).astype(np.float32)
+    outs = []
+    for be in (oracle, gpu):
+        tb = cb.TermBuilder(be)
+        s = tb.source()
+        xf = tb.cast(s, Dtype.F32)
+        sh = tb.shape(xf)
+        e = tb.exp(xf - tb.broadcast(sh, tb.max(xf)))
+        y = tb.cast(e / tb.broadcast(sh, tb.sum(e)), tb.dtype(s))
+        term = tb.finish([y])
+        outs.append(be.to_f32(cb.Interpreter(be).run(term, [be.from_numpy(x)])[0]))
+    np.testing.assert_allclose(outs[1], outs[0], rtol=1e-5, atol=1e-9)
+    np.testing.assert_allclose(outs[1].sum(-1), 1.0, rtol=1e-5)
+
+
+def test_argmax_ties_nan_and_signed_zero(oracle, gpu):
+    rows = np.array([[1, 7, 7, 2, 7, 0], [-0.0, 0.0, -0.0, 0.0, -0.0, -0.0], [np.nan, 1, 2, 3, 4, 5],
+                     [-np.inf] * 6, [3, 3, 3, 3, 3, 3]], np.float32)
+    for dtype in (Dtype.F32, Dtype.BF16):
+        xo, xg = both(oracle, gpu, rows, dtype)
+        same_bits(oracle, gpu, oracle.argmax(xo), gpu.argmax(xg))
+        same_bits(oracle, gpu, oracle.max(xo), gpu.max(xg))
+    assert gpu.to_numpy(gpu.argmax(gpu.from_numpy(rows))).reshape(-1).tolist() == [4, 3, 0, 5, 5]
+    # wide vocabulary row with many ties, as bf16 logits have
+    rng = np.random.default_rng(8)
+    wide = np.round(rng.standard_normal((64, 32000)) * 4) / 4
+    xo, xg = both(oracle, gpu, wide.astype(np.float32), Dtype.BF16)
+    same_bits(oracle, gpu, oracle.argmax(xo), gpu.argmax(xg))
+
+
+def test_topk_tie_order(oracle, gpu):
+    rng = np.random.default_rng(9)
+    x = np.round(rng.standard_normal((5, 300)) * 3).astype(np.float32)
+    xo, xg = both(oracle, gpu, x)
+    for k in (1, 4, 17):
+        vo, io = oracle.topk(xo, k)
+        vg, ig = gpu.topk(xg, k)
+        same_bits(oracle, gpu, vo, vg)
+        same_bits(oracle, gpu, io, ig)
+
+
+def test_gather_concat_slice_arange(oracle, gpu):
+    rng = np.random.default_rng(2)
+    table = rng.standard_normal((32000, 256)).astype(np.float32)
+    idx = rng.integers(0, 32000, 4096, dtype=np.uint32)
+    for dtype in (Dtype.F32, Dtype.BF16):
+        to, tg = both(oracle, gpu, table, dtype)
+        io, ig = both(oracle, gpu, idx)
+        same_bits(oracle, gpu, oracle.index(to, 0, io), gpu.index(tg, 0, ig))
+    small = rng.standard_normal((3, 7, 5)).astype(np.float32)
+    so, sg = both(oracle, gpu, small)
+    j = np.array([6, 0, 0, 3], np.uint32)
+    jo, jg = both(oracle, gpu, j)
+    same_bits(oracle, gpu, oracle.index(so, 1, jo), gpu.index(sg, 1, jg))
+    same_bits(oracle, gpu, oracle.index(so, 2, oracle.slice(jo, 0, 1, 3)), gpu.index(sg, 2, gpu.slice(jg, 0, 1, 3)))
+    for dim in (0, 1, 2):
+        same_bits(oracle, gpu, oracle.concat(so, so, dim), gpu.concat(sg, sg, dim))
+    same_bits(oracle, gpu, oracle.concat(oracle.transpose(so, 0, 2), oracle.transpose(so, 0, 2), 1),
+              gpu.concat(gpu.transpose(sg, 0, 2), gpu.transpose(sg, 0, 2), 1))
+    eo, eg = oracle.zeros((3, 0, 5), Dtype.F32), gpu.zeros((3, 0, 5), Dtype.F32)
+    same_bits(oracle, gpu, oracle.concat(eo, so, 1), gpu.concat(eg, sg, 1))
+    same_bits(oracle, gpu, oracle.arange(1000), gpu.arange(1000))
+    assert gpu.arange(0).shape == (0,)
+    assert gpu.compare(sg, sg) and not gpu.compare(sg, gpu.neg(sg))
+    assert gpu.to_bool(gpu.from_numpy(np.array([0.0, -1.0, 2.0], np.float32)))
+    assert not gpu.to_bool(gpu.from_numpy(np.array([0.0, -1.0, np.nan], np.float32)))
+    assert not gpu.compare(gpu.from_numpy(np.array([np.nan], np.float32)), gpu.from_numpy(np.array([np.nan], np.float32)))
+
+
+@pytest.mark.parametrize("dtype", [Dtype.F32, Dtype.BF16], ids=lambda d: d.name)
+def test_matmul(oracle, gpu, dtype):
+    rng = np.random.default_rng(2)
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == Dtype.F32 else dict(rtol=2e-2, atol=2e-2)
+    cases = [((4, 96, 80), (4, 80, 72)), ((2, 3, 5, 7), (2, 3, 7, 1)), ((33, 65), (65, 17)), ((1, 1, 256), (1, 256, 384)),
+             ((2, 130, 64), (2, 64, 130))]
+    for sa, sb in cases:
+        a = rng.standard_normal(sa).astype(np.float32)
+        b = rng.standard_normal(sb).astype(np.float32)
+        ao, ag = both(oracle, gpu, a, dtype)
+        bo, bg = both(oracle, gpu, b, dtype)
+        np.testing.assert_allclose(gpu.to_f32(gpu.matmul(ag, bg)), oracle.to_f32(oracle.matmul(ao, bo)), **tol)
+    # the `linear` pattern: x @ broadcast(transpose(W)) with W [out, in]; nothing is copied on the GPU
+    x = rng.standard_normal((2, 5, 256)).astype(np.float32)
+    w = (rng.standard_normal((384, 256)) * 0.05).astype(np.float32)
+    res = []
+    for be in (oracle, gpu):
+        xt, wt = be.from_numpy(x, dtype), be.from_numpy(w, dtype)
+        wv = be.broadcast(be.transpose(wt, 0, 1), (2, 256, 384))
+        res.append(be.to_f32(be.matmul(xt, wv)))
+    np.testing.assert_allclose(res[1], res[0], **tol)
+    # single-row products take the weight-streaming kernel
+    x1 = rng.standard_normal((1, 1, 256)).astype(np.float32)
+    res = []
+    for be in (oracle, gpu):
+        xt, wt = be.from_numpy(x1, dtype), be.from_numpy(w, dtype)
+        res.append(be.to_f32(be.matmul(xt, be.broadcast(be.transpose(wt, 0, 1), (1, 256, 384)))))
+    np.testing.assert_allclose(res[1], res[0], **tol)
+    with pytest.raises(cb.BackendError):
+        gpu.matmul(gpu.from_numpy(x), gpu.from_numpy(w))
+
+
+def test_matmul_sweep_shape_linearity(gpu):
+    """Full op-sweep size [16,1024,1024]^2 (too slow for the scalar oracle): checked through linearity,
+    (A1+A2) B = A1 B + A2 B, and against a float64 numpy product on a sampled block."""
+    rng = np.random.default_rng(2)
+    a1 = rng.standard_normal((16, 1024, 1024)).astype(np.float32)
+    a2 = rng.standard_normal((16, 1024, 1024)).astype(np.float32)
+    b = rng.standard_normal((16, 1024, 1024)).astype(np.float32)
+    A1, A2, B = gpu.from_numpy(a1), gpu.from_numpy(a2), gpu.from_numpy(b)
+    lhs = gpu.to_numpy(gpu.matmul(gpu.add(A1, A2), B))
+    rhs = gpu.to_numpy(gpu.add(gpu.matmul(A1, B), gpu.matmul(A2, B)))
+    assert helpers.rel_err(lhs, rhs) < 1e-5
+    ref = (a1[3, :64].astype(np.float64) + a2[3, :64]) @ b[3].astype(np.float64)
+    assert helpers.rel_err(lhs[3, :64], ref) < 1e-5
+
+
+def test_fp8_moves_and_casts(oracle, gpu):
+    bits = np.arange(256, dtype=np.uint8)
+    fo, fg = oracle.ndarray_from_vec_fp8(bits, (256,)), gpu.ndarray_from_vec_fp8(bits, (256,))
+    a, b = oracle.to_f32(oracle.cast(fo, Dtype.F32)), gpu.to_f32(gpu.cast(fg, Dtype.F32))
+    np.testing.assert_array_equal(np.nan_to_num(a, nan=12345.0), np.nan_to_num(b, nan=12345.0))
+    x = np.linspace(-500, 500, 4001).astype(np.float32)
+    np.testing.assert_array_equal(oracle.to_numpy(oracle.cast(oracle.from_numpy(x), Dtype.F8)),
+                                  gpu.to_numpy(gpu.cast(gpu.from_numpy(x), Dtype.F8)))
+    with pytest.raises(cb.BackendError):
+        gpu.add(fg, fg)

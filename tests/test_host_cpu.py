@@ -1,0 +1,162 @@
+"""Host-side checks that need no GPU: the C-ABI library loads and exports what include/*.h declares, the term
+builder/evaluator behave like the reference's, and the Llama term is a Llama."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+import catgrad_b200 as cb
+from catgrad_b200 import Dtype, NodeType, OpKind
+from catgrad_b200 import _ffi
+import helpers
+import llama_numpy
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    hdr = open(os.path.join(ROOT, "include", "catgrad_b200.h")).read()
+    names = sorted(set(re.findall(r"\b(cg_[a-z0-9_]+)\s*\(", hdr)))
+    assert len(names) > 70
+    path = _ffi.library_path()
+    assert os.path.exists(path), "build the library first: python -m catgrad_b200._build"
+    lib = ctypes.CDLL(path)
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+    _ffi.bind(lib, "cg_")          # every symbol the host wrapper binds exists too
+
+
+def test_no_cpu_fallback():
+    """Without a GPU the product refuses to start; nothing silently computes on the host."""
+    try:
+        import torch
+        has_gpu = torch.cuda.is_available()
+    except Exception:
+        has_gpu = False
+    if has_gpu:
+        pytest.skip("a GPU is present")
+    with pytest.raises(cb.BackendError) as e:
+        cb.Backend(0)
+    assert e.value.status == cb.Status.CUDA
+
+
+def test_product_sources_do_not_reach_into_the_oracle():
+    for base in ("catgrad_b200", "include"):
+        for root, _, files in os.walk(os.path.join(ROOT, base)):
+            for f in files:
+                if f.endswith((".py", ".cc", ".cu", ".cuh", ".h")):
+                    text = open(os.path.join(root, f)).read()
+                    assert "oracle/" not in text and "ndarray_ref" not in text, os.path.join(root, f)
+
+
+def test_builder_inserts_copies_and_evaluator_consumes_once(oracle):
+    tb = cb.TermBuilder(oracle)
+    x = tb.source()
+    y = x * x + x                       # x used three times -> one Copy edge with three outputs
+    term = tb.finish([y, x])            # and once more as an output
+    st = term.stats()
+    assert st["tensor_ops"] == 2 and st["edges"] == 3
+    a = oracle.from_numpy(np.array([1.0, 2.0, 3.0], np.float32))
+    r = cb.Interpreter(oracle).run(term, [a])
+    assert oracle.to_numpy(r[0]).tolist() == [2.0, 6.0, 12.0]
+    assert oracle.to_numpy(r[1]).tolist() == [1.0, 2.0, 3.0]
+
+
+def test_interpreter_errors(oracle):
+    tb = cb.TermBuilder(oracle)
+    x, y = tb.source(), tb.source()
+    term = tb.finish([x + y])
+    interp = cb.Interpreter(oracle)
+    f = oracle.from_numpy(np.zeros(3, np.float32))
+    u = oracle.from_numpy(np.zeros(3, np.uint32))
+    with pytest.raises(cb.BackendError) as e:
+        interp.run(term, [f, u])                       # TypeError: dtypes of one op differ
+    assert e.value.status == cb.Status.DTYPE_MISMATCH
+    with pytest.raises(cb.BackendError) as e:
+        interp.run(term, [f])                          # wrong number of inputs
+    assert e.value.status == cb.Status.INTERP
+    tb = cb.TermBuilder(oracle)
+    term = tb.finish([tb.param("no.such.weight")])
+    with pytest.raises(cb.BackendError) as e:
+        cb.Interpreter(oracle, cb.Parameters(oracle)).run(term, [])
+    assert "no.such.weight" in str(e.value)
+
+
+def test_nat_shape_and_dtype_values(oracle):
+    tb = cb.TermBuilder(oracle)
+    x = tb.source()
+    d = tb.unpack(tb.shape(x), 3)
+    n = tb.nat_add(tb.nat_mul(d[0], d[1]), d[2])
+    term = tb.finish([n, tb.shape(x), tb.dtype(x), tb.nat_to_u32(d[2])])
+    r = cb.Interpreter(oracle).run(term, [oracle.zeros((2, 3, 5), Dtype.U32)])
+    assert r[0] == 11 and r[1] == (2, 3, 5) and r[2] == Dtype.U32
+    assert oracle.to_numpy(r[3]).tolist() == 5
+
+
+def test_llama_term_shape(oracle):
+    """~137 tensor ops per layer plus prologue/epilogue; prefill and decode run the same term."""
+    t2 = cb.llama_term(oracle, cb.TINY).stats()
+    cfg4 = cb.LlamaConfig(256, 688, 4, 4, 4, 1024)
+    t4 = cb.llama_term(oracle, cfg4).stats()
+    per_layer = (t4["tensor_ops"] - t2["tensor_ops"]) / 2
+    assert 120 <= per_layer <= 150
+    assert t2["layers"] < t2["edges"]
+
+
+def test_tiny_llama_oracle_equals_textbook_llama(oracle):
+    cfg = cb.TINY
+    w = cb.random_weights(cfg, 0)
+    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(1, 64), dtype=np.uint32)
+    term = cb.llama_term(oracle, cfg, tap_logits=True)
+    params = cb.upload_weights(oracle, w, Dtype.F32)
+    out, logits = cb.generate_with_interpreter(oracle, term, params, cfg, ids, 3, Dtype.F32, 96, tap=True)
+    lg, cache = llama_numpy.forward(cfg, w, ids.astype(np.int64))
+    assert helpers.rel_err(logits[0], lg) < 1e-5
+    assert int(lg[0, -1].argmax()) == int(out[0, 0])
+    lg2, cache = llama_numpy.forward(cfg, w, out[:, :1].astype(np.int64), cache)
+    assert helpers.rel_err(logits[1], lg2) < 1e-5
+    # GQA + tied head + batch 2 take the other branches of the term
+    cfg2 = cb.LlamaConfig(128, 256, 2, 8, 2, 512, rope_theta=500000.0, tie_word_embeddings=True)
+    w2 = cb.random_weights(cfg2, 3)
+    ids2 = np.random.default_rng(4).integers(0, 512, size=(2, 9), dtype=np.uint32)
+    term2 = cb.llama_term(oracle, cfg2, tap_logits=True)
+    out2, logits2 = cb.generate_with_interpreter(oracle, term2, cb.upload_weights(oracle, w2, Dtype.F32), cfg2, ids2, 1,
+                                                 Dtype.F32, 16, tap=True)
+    lgb, _ = llama_numpy.forward(cfg2, w2, ids2.astype(np.int64))
+    assert helpers.rel_err(logits2[0], lgb) < 1e-5
+
+
+def test_config1_golden_ids(oracle):
+    """Config 1 of the baseline (tiny f32 model, seed-0 weights, seed-1 prompt, 32 greedy steps after the prefill
+    token) against the committed fixture written by tests/golden/make_tiny_llama_fixture.py."""
+    import json
+    fx = json.load(open(os.path.join(helpers.GOLDEN, "tiny_llama_c1.json")))
+    cfg = cb.TINY
+    w = cb.random_weights(cfg, fx["weight_seed"])
+    ids = np.random.default_rng(fx["prompt_seed"]).integers(0, cfg.vocab_size, size=(1, 64), dtype=np.uint32)
+    assert ids[0, :8].tolist() == fx["prompt_head"]
+    term = cb.llama_term(oracle, cfg, tap_logits=True)
+    params = cb.upload_weights(oracle, w, Dtype.F32)
+    out, logits = cb.generate_with_interpreter(oracle, term, params, cfg, ids, 33, Dtype.F32, 97, tap=True)
+    assert out[0].tolist() == fx["ids"]
+    np.testing.assert_allclose(logits[0][0, -1, :16], np.array(fx["prefill_logits_head"], np.float32), rtol=1e-5, atol=1e-6)
+
+
+def test_reduced_precision_conversions(oracle):
+    """The oracle's bf16/f16 rounding against numpy's (f16) and the bit formula (bf16), incl. ties, subnormals, NaN."""
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(5000) * 10.0 ** rng.integers(-8, 6, 5000),
+                        [0.0, -0.0, np.inf, -np.inf, np.nan, 65504.0, 65519.9, 65520.0, 6e-8, 2.98e-8, 2.99e-8, 1.00390625]]).astype(np.float32)
+    t = oracle.from_numpy(x)
+    h = oracle.to_numpy(oracle.cast(t, Dtype.F16))
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16)
+    np.testing.assert_array_equal(h.view(np.uint16)[~np.isnan(x)], want.view(np.uint16)[~np.isnan(x)])
+    assert np.isnan(h[np.isnan(x)]).all()
+    b = oracle.to_numpy(oracle.cast(t, Dtype.BF16))
+    wantb = cb.f32_to_bf16_bits(x)
+    np.testing.assert_array_equal(b[~np.isnan(x)], wantb[~np.isnan(x)])
+    back = oracle.to_numpy(oracle.cast(oracle.cast(t, Dtype.F16), Dtype.F32))
+    np.testing.assert_array_equal(back[~np.isnan(x)], want.astype(np.float32)[~np.isnan(x)])
