@@ -52,6 +52,9 @@ struct cg_llama {
   Tensor words;               // int32: [0] ctx_len, [1] step_no
   Tensor ids_in, ids_cur, ids_new, ids_out;  // u32: prompt ids [M], current [B], argmax result [B], record [steps*B]
   Tensor logits;              // [Bmax, V]
+  Tensor partials;            // u64 [Bmax, ceil(V/4096)]: stage-1 keys of the greedy pick (scratch)
+  int argmax_chunks = 0;
+  bool use_pdl = false;       // programmatic dependent launch between the kernels of a step (opt-in)
   int64_t out_cap_steps = 0;
   // activation buffers sized for `cap_tokens` tokens
   int64_t cap_tokens = 0;
@@ -89,8 +92,35 @@ struct Plan {
     return M <= 16 && (size_t)mt_for(M) * K * sizeof(T) <= 160 * 1024 && K % (16 / sizeof(T)) == 0;
   }
 
+  // Launch with the programmatic-stream-serialization attribute: the kernel may be scheduled while its
+  // predecessor drains and blocks in griddepcontrol.wait until that one has completed.
+  template <class... KArgs, class... Args>
+  void launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = m.use_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+    if (e != cudaSuccess) throw Error(ERR_CUDA, std::string("cudaLaunchKernelEx: ") + cudaGetErrorString(e));
+  }
+
+  // K split so that even the smallest projection puts >= 16 warps on every SM
+  int ks_for(int n_pairs, int K) const {
+    int nvec = K / (int)(16 / sizeof(T));
+    int ks = 1;
+    while (ks < 8 && (long long)n_pairs * ks < (long long)sm * 16 && nvec / (ks * 2) >= 64) ks *= 2;
+    return ks;
+  }
+
   template <int MT, int PRO, int EPI>
-  void gemv_launch(const cgk::GemvArgs& a) {
+  void gemv_launch(cgk::GemvArgs a) {
     size_t smem = (size_t)MT * a.K * sizeof(T);
     auto kern = cgk::gemv_fused_kernel<T, MT, PRO, EPI>;
     static size_t smem_set = 0;  // per instantiation: raise the dynamic shared-memory limit once per size class
@@ -99,9 +129,11 @@ struct Plan {
       smem_set = smem;
     }
     int pairs = EPI == cgk::EPI_SILU_MUL ? a.N : (a.N + 1) / 2;
+    a.ks = ks_for(pairs, a.K);
+    int ppc = 8 / a.ks;
     int ctas_per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
-    int grid = std::min((pairs + 7) / 8, sm * ctas_per_sm);
-    kern<<<grid, 256, smem, st>>>(a);
+    int grid = std::min((pairs + ppc - 1) / ppc, sm * ctas_per_sm);
+    launch(kern, dim3(grid), dim3(256), smem, a);
     launched("gemv");
   }
   template <int PRO, int EPI>
@@ -167,8 +199,8 @@ struct Plan {
     unsigned* err = m.be->dev_err();
     T* x = (T*)m.x.raw();
 
-    cgk::embed_kernel<T><<<grid_for(M * (H / (16 / sizeof(T)))), 256, 0, st>>>(ids, (const T*)m.embed, x, (int)M, (int)H,
-                                                                             (int)V, err);
+    launch(cgk::embed_kernel<T>, dim3(grid_for(M * (H / (16 / sizeof(T))))), dim3(256), 0, ids, (const T*)m.embed, x,
+           (int)M, (int)H, (int)V, err);
     launched("embed");
 
     const float scale = cgk_host_round((float)std::sqrt((float)hd));
@@ -197,21 +229,15 @@ struct Plan {
       const int64_t qs = packed_rows ? NQKV : NQ, ks = packed_rows ? NQKV : NKV;
       T* kcl = (T*)m.kc.raw() + l * m.max_batch * nkv * m.P * hd;
       T* vcl = (T*)m.vc.raw() + l * m.max_batch * nkv * m.P * hd;
-      {
-        cgk::RopeArgs r{};
-        r.q = q; r.q_row_stride = qs; r.k = k; r.k_row_stride = ks; r.v = v; r.v_row_stride = ks;
-        r.kc = kcl; r.vc = vcl; r.cos_t = (const float*)m.cos_t.raw(); r.sin_t = (const float*)m.sin_t.raw();
-        r.ctx_len = ctx_len; r.B = (int)B; r.S = (int)S; r.nh = (int)nh; r.nkv = (int)nkv; r.HD = (int)hd; r.P = (int)m.P;
-        cgk::rope_append_kernel<T><<<(int)M, 256, 0, st>>>(r, err);
-        launched("rope_append");
-      }
       T* attn = (T*)m.attn.raw();
       if (S == 1) {
         cgk::AttnArgs a{};
-        a.q = q; a.q_row_stride = qs; a.kc = kcl; a.vc = vcl; a.out = attn; a.out_row_stride = NQ;
+        a.q = q; a.q_row_stride = qs; a.k = k; a.k_row_stride = ks; a.v = v; a.v_row_stride = ks;
+        a.kc = kcl; a.vc = vcl; a.out = attn; a.out_row_stride = NQ;
+        a.cos_t = (const float*)m.cos_t.raw(); a.sin_t = (const float*)m.sin_t.raw();
         a.ctx_len = ctx_len; a.nh = (int)nh; a.nkv = (int)nkv; a.P = (int)m.P; a.scale = scale;
         constexpr int VEC = 16 / sizeof(T);
-        size_t smem = (size_t)m.P * 4 + (size_t)(256 / (hd / VEC)) * hd * 4;
+        size_t smem = (size_t)(m.P + 1) * 4 + (size_t)(256 / (hd / VEC)) * hd * 4;
         dim3 grid((unsigned)nh, (unsigned)B);
         if (hd == 64) {
           auto kern = cgk::attn_decode_kernel<T, 64>;
@@ -220,7 +246,7 @@ struct Plan {
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             smem_set = smem;
           }
-          kern<<<grid, 256, smem, st>>>(a);
+          launch(kern, grid, dim3(256), smem, a, err);
         } else {
           auto kern = cgk::attn_decode_kernel<T, 128>;
           static size_t smem_set = 0;
@@ -228,10 +254,16 @@ struct Plan {
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             smem_set = smem;
           }
-          kern<<<grid, 256, smem, st>>>(a);
+          launch(kern, grid, dim3(256), smem, a, err);
         }
         launched("attn_decode");
       } else {
+        cgk::RopeArgs r{};
+        r.q = q; r.q_row_stride = qs; r.k = k; r.k_row_stride = ks; r.v = v; r.v_row_stride = ks;
+        r.kc = kcl; r.vc = vcl; r.cos_t = (const float*)m.cos_t.raw(); r.sin_t = (const float*)m.sin_t.raw();
+        r.ctx_len = ctx_len; r.B = (int)B; r.S = (int)S; r.nh = (int)nh; r.nkv = (int)nkv; r.HD = (int)hd; r.P = (int)m.P;
+        cgk::rope_append_kernel<T><<<(int)M, 256, 0, st>>>(r, err);
+        launched("rope_append");
         prefill_attention(q, qs, kcl, vcl, attn, B, S);
       }
       // ---- o_proj + residual ----
@@ -282,19 +314,12 @@ struct Plan {
       rmsnorm(x, m.final_norm, m.xn.raw(), B, H, S, S - 1);
       gemm(m.xn.raw(), H, m.head, logits, B, V, H);
     }
-    {
-      cgk::View4 outer;
-      std::memset(&outer, 0, sizeof(outer));
-      outer.rank = 1;
-      outer.total = B;
-      outer.shape[0] = B;
-      outer.sa[0] = V;
-      cgk::launch_reduce(cgk::R_ARGMAX, (int)m.dt, outer, B, V, 1, logits, m.ids_new.raw(), sm, st);
-      launched("argmax");
-    }
-    cgk::advance_kernel<<<1, 256, 0, st>>>((const unsigned*)m.ids_new.raw(), (unsigned*)m.ids_cur.raw(),
-                                           (unsigned*)m.ids_out.raw(), ctx_len, ctx_len + 1, (int)B, (int)S,
-                                           (int)m.out_cap_steps);
+    launch(cgk::argmax_partial_kernel<T>, dim3((unsigned)m.argmax_chunks, (unsigned)B), dim3(256), 0, (const T*)logits,
+           (long long)V, (int)V, (unsigned long long*)m.partials.raw());
+    launched("argmax_partial");
+    launch(cgk::advance_kernel, dim3(1), dim3(256), 0, (const unsigned long long*)m.partials.raw(), m.argmax_chunks,
+           (unsigned*)m.ids_cur.raw(), (unsigned*)m.ids_out.raw(), ctx_len, ctx_len + 1, (int)B, (int)S,
+           (int)m.out_cap_steps);
     launched("advance");
   }
 
@@ -444,7 +469,7 @@ int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const c
   const int64_t vec = 16 / (int64_t)m->es;
   CG_CHECK(c.hidden_size % vec == 0 && c.intermediate_size % vec == 0, ERR_INVALID_ARG,
            "hidden and intermediate sizes must be multiples of 16 bytes");
-  CG_CHECK(max_positions * 4 + 32 * 128 * 4 <= 200 * 1024, ERR_INVALID_ARG, "max_positions above 47000 is not supported");
+  CG_CHECK((max_positions + 1) * 4 + 32 * 128 * 4 <= 200 * 1024, ERR_INVALID_ARG, "max_positions above 47000 is not supported");
   m->max_batch = (int64_t)max_batch;
   m->P = (int64_t)max_positions;
 
@@ -485,6 +510,10 @@ int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const c
   m->ids_cur = be.zeros({m->max_batch}, Dtype::U32);
   m->ids_new = be.zeros({m->max_batch}, Dtype::U32);
   m->logits = be.zeros({m->max_batch, V}, m->dt);
+  m->argmax_chunks = (int)((V + cgk::ARGMAX_CHUNK - 1) / cgk::ARGMAX_CHUNK);
+  m->partials = be.zeros({m->max_batch * m->argmax_chunks * 2}, Dtype::U32);
+  // measured slower than plain graph edges on B200 for this chain (waiting CTAs hold SM resources): opt-in
+  m->use_pdl = std::getenv("CATGRAD_B200_PDL") != nullptr;
   m->out_cap_steps = 0;
   *out = m.release();
   CG_API_END(ctx)

@@ -25,7 +25,10 @@ template <> struct Elem<float> {
   static __device__ __forceinline__ float store(float v) { return v; }
 };
 template <> struct Elem<__nv_bfloat16> {
-  static __device__ __forceinline__ float load(__nv_bfloat16 v) { return __bfloat162float(v); }
+  // bf16 -> f32 is a 16-bit shift: exact, and NaN payloads/signs pass through unchanged
+  static __device__ __forceinline__ float load(__nv_bfloat16 v) {
+    return __uint_as_float(((unsigned)__bfloat16_as_ushort(v)) << 16);
+  }
   static __device__ __forceinline__ __nv_bfloat16 store(float v) { return __float2bfloat16_rn(v); }
 };
 template <> struct Elem<__half> {

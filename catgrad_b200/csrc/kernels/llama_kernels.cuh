@@ -39,6 +39,12 @@ __device__ __forceinline__ float block_max_256(float v, float* scratch) {
   return r;
 }
 
+// Programmatic dependent launch: a kernel may be scheduled while its predecessor drains; everything that reads
+// the predecessor's results or writes global memory comes after pdl_wait().  Both are no-ops for a kernel
+// launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- embedding gather (helpers/tensors.rs:255-272) ------------------------------------------------
 // x[m, :] = table[ids[m], :].  16-byte copies; an id >= vocab records DEV_ERR_INDEX_OOB and writes zeros.
 template <class T>
@@ -46,6 +52,8 @@ __global__ void __launch_bounds__(256) embed_kernel(const unsigned* __restrict__
                                                     T* __restrict__ x, int M, int H, int vocab, unsigned* err) {
   constexpr int VEC = 16 / sizeof(T);
   const int per_row = H / VEC;
+  pdl_launch_dependents();
+  pdl_wait();
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < (long long)M * per_row;
        t += (long long)gridDim.x * blockDim.x) {
     int m = (int)(t / per_row), c = (int)(t - (long long)m * per_row);
@@ -100,6 +108,7 @@ struct GemvArgs {
   void* out;          // [M, N]
   const void* res;    // EPI_RESIDUAL: [M, N], may alias out
   int M, N, K;
+  int ks;             // K is split over `ks` warps of a CTA (1, 2, 4 or 8) so that small N still fills the GPU
 };
 
 template <class T>
@@ -109,16 +118,20 @@ __device__ __forceinline__ const T* gemv_row(const GemvArgs& a, int n) {
   return (const T*)a.w[seg] + (long long)(n - base) * a.K;
 }
 
-// 256 threads; each warp owns a PAIR of weight rows per iteration (two columns, or gate[n]/up[n] for
-// EPI_SILU_MUL) and streams them with 16-byte loads; the M input rows sit in shared memory as T.
+// 256 threads = 8 warps.  A work item is a PAIR of weight rows (two output columns, or gate[n]/up[n] for
+// EPI_SILU_MUL); `ks` consecutive warps share one pair, each streaming a 1/ks slice of K with 16-byte loads;
+// partial sums meet in shared memory in a fixed order.  The M input rows sit in shared memory as T.
 template <class T, int MT, int PRO, int EPI>
 __global__ void __launch_bounds__(256) gemv_fused_kernel(GemvArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* xs = reinterpret_cast<T*>(smem_raw);  // [MT][K]
   __shared__ float scratch[8];
+  __shared__ float part[8][2 * MT];
   constexpr int VEC = 16 / sizeof(T);
   const int K = a.K;
   const T* xin = (const T*)a.x;
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (PRO == PRO_NORM) {
     const T* g = (const T*)a.gain;
@@ -152,50 +165,85 @@ __global__ void __launch_bounds__(256) gemv_fused_kernel(GemvArgs a) {
   __syncthreads();
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ks = a.ks, ppc = 8 / ks;            // pairs per CTA per iteration
+  const int split = warp % ks, slot = warp / ks;
   const int n_pairs = EPI == EPI_SILU_MUL ? a.N : (a.N + 1) / 2;
   const int nvec = K / VEC;
-  for (int p = blockIdx.x * 8 + warp; p < n_pairs; p += gridDim.x * 8) {
-    int n0, n1;
-    const T *w0, *w1;
-    if (EPI == EPI_SILU_MUL) {
-      n0 = n1 = p;
-      w0 = (const T*)a.w[0] + (long long)p * K;
-      w1 = (const T*)a.w[1] + (long long)p * K;
-    } else {
-      n0 = 2 * p;
-      n1 = 2 * p + 1 < a.N ? 2 * p + 1 : n0;
-      w0 = gemv_row<T>(a, n0);
-      w1 = gemv_row<T>(a, n1);
-    }
+  const int v_lo = (int)((long long)nvec * split / ks), v_hi = (int)((long long)nvec * (split + 1) / ks);
+  const int iters = (n_pairs + gridDim.x * ppc - 1) / (gridDim.x * ppc);
+  for (int it = 0; it < iters; ++it) {
+    const int p = (it * gridDim.x + blockIdx.x) * ppc + slot;
+    const bool valid = p < n_pairs;
+    int n0 = 0, n1 = 0;
     float acc0[MT], acc1[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
-#pragma unroll 4
-    for (int v = lane; v < nvec; v += 32) {
-      VecT<T, VEC> a0 = *reinterpret_cast<const VecT<T, VEC>*>(w0 + v * VEC);
-      VecT<T, VEC> a1 = *reinterpret_cast<const VecT<T, VEC>*>(w1 + v * VEC);
-      float f0[VEC], f1[VEC];
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        f0[i] = Elem<T>::load(a0.v[i]);
-        f1[i] = Elem<T>::load(a1.v[i]);
+    if (valid) {
+      const T *w0, *w1;
+      if (EPI == EPI_SILU_MUL) {
+        n0 = n1 = p;
+        w0 = (const T*)a.w[0] + (long long)p * K;
+        w1 = (const T*)a.w[1] + (long long)p * K;
+      } else {
+        n0 = 2 * p;
+        n1 = 2 * p + 1 < a.N ? 2 * p + 1 : n0;
+        w0 = gemv_row<T>(a, n0);
+        w1 = gemv_row<T>(a, n1);
       }
-#pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        VecT<T, VEC> xv = *reinterpret_cast<const VecT<T, VEC>*>(xs + m * K + v * VEC);
+#pragma unroll 4
+      for (int v = v_lo + lane; v < v_hi; v += 32) {
+        VecT<T, VEC> a0 = *reinterpret_cast<const VecT<T, VEC>*>(w0 + v * VEC);
+        VecT<T, VEC> a1 = *reinterpret_cast<const VecT<T, VEC>*>(w1 + v * VEC);
+        float f0[VEC], f1[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
-          float xf = Elem<T>::load(xv.v[i]);
-          acc0[m] = fmaf(xf, f0[i], acc0[m]);
-          acc1[m] = fmaf(xf, f1[i], acc1[m]);
+          f0[i] = Elem<T>::load(a0.v[i]);
+          f1[i] = Elem<T>::load(a1.v[i]);
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          VecT<T, VEC> xv = *reinterpret_cast<const VecT<T, VEC>*>(xs + m * K + v * VEC);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            float xf = Elem<T>::load(xv.v[i]);
+            acc0[m] = fmaf(xf, f0[i], acc0[m]);
+            acc1[m] = fmaf(xf, f1[i], acc1[m]);
+          }
         }
       }
     }
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
-      float s0 = warp_sum(acc0[m]);
-      float s1 = warp_sum(acc1[m]);
-      if (lane == 0 && m < a.M) {
+      acc0[m] = warp_sum(acc0[m]);
+      acc1[m] = warp_sum(acc1[m]);
+    }
+    if (ks > 1) {
+      if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          part[warp][2 * m] = acc0[m];
+          part[warp][2 * m + 1] = acc1[m];
+        }
+      }
+      __syncthreads();
+      if (split == 0 && lane == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          float s0 = 0.f, s1 = 0.f;
+          for (int q = 0; q < ks; ++q) {
+            s0 += part[warp + q][2 * m];
+            s1 += part[warp + q][2 * m + 1];
+          }
+          acc0[m] = s0;
+          acc1[m] = s1;
+        }
+      }
+    }
+    if (valid && split == 0 && lane == 0) {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m >= a.M) continue;
+        const float s0 = acc0[m], s1 = acc1[m];
         T* o = (T*)a.out + (long long)m * a.N;
         if (EPI == EPI_STORE) {
           o[n0] = Elem<T>::store(s0);
@@ -215,10 +263,11 @@ __global__ void __launch_bounds__(256) gemv_fused_kernel(GemvArgs a) {
         }
       }
     }
+    if (ks > 1) __syncthreads();
   }
 }
 
-// ---- RoPE + KV append (helpers/rope.rs:423-451; helpers/cache.rs:30-39) ----------------------------
+// ---- RoPE + KV append for prefill (helpers/rope.rs:423-451; helpers/cache.rs:30-39) -----------------
 // One CTA per token m = (b, s).  q is rotated in place; rotated k and plain v go to the cache row `pos`.
 // cos/sin tables are [P, HD/2] f32 (the reference concatenates each with itself, rope.rs:100-101).
 struct RopeArgs {
@@ -265,53 +314,107 @@ __global__ void __launch_bounds__(256) rope_append_kernel(RopeArgs a, unsigned* 
   }
 }
 
-// ---- decode attention, S = 1 (llama.rs:322-345) ------------------------------------------------------
-// One CTA per (query head, sequence).  scores = T(q.k), T(scores / T(sqrt(HD))), softmax in f32 -> T,
-// out = T(P.v).  The causal-mask row of a single new token is all -0.0 and adding it changes nothing
-// (helpers/tensors.rs:207-224), so it is skipped.  GQA: head h reads kv head h / rep (repeat_kv,
-// tensors.rs:128-151, never materialised).
+// ---- decode attention, S = 1, with RoPE and the KV append fused (llama.rs:296-345) -------------------
+// One CTA per (query head, sequence).  It rotates its q and the new k row (rope.rs:430-451), the first head of
+// each GQA group stores the rotated k and the v row into the cache (cache.rs:30-39); every head of the group
+// uses its own copy of the new row, so no CTA waits for another.  Then scores = T(q.k), T(scores / T(sqrt(HD))),
+// softmax in f32 -> T, out = T(P.v).  The causal-mask row of a single new token is all -0.0 and adding it
+// changes nothing (helpers/tensors.rs:207-224), so it is skipped.  GQA: head h reads kv head h / rep
+// (repeat_kv, tensors.rs:128-151, never materialised).
 struct AttnArgs {
-  const void* q; long long q_row_stride;  // [B, nh*HD] (rotated)
-  const void* kc; const void* vc;         // [B, nkv, P, HD]
+  const void* q; long long q_row_stride;  // raw projections [B, ...]: q at [b*stride + h*HD]
+  const void* k; long long k_row_stride;  // new k row [b*stride + kvh*HD] (not rotated)
+  const void* v; long long v_row_stride;
+  void* kc; void* vc;                     // [B, nkv, P, HD]
   void* out; long long out_row_stride;    // [B, nh*HD]
-  const int* ctx_len;                     // positions in the cache BEFORE this step; this step appended one
+  const float* cos_t; const float* sin_t; // [P, HD/2]
+  const int* ctx_len;                     // positions in the cache before this step
   int nh, nkv, P;
   float scale;                            // T(sqrt(HD)) widened
 };
 template <class T, int HD>
-__global__ void __launch_bounds__(256) attn_decode_kernel(AttnArgs a) {
+__global__ void __launch_bounds__(256) attn_decode_kernel(AttnArgs a, unsigned* err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* sc = reinterpret_cast<float*>(smem_raw);  // [P] scores / probabilities
+  float* sc = reinterpret_cast<float*>(smem_raw);  // [P + 1] scores / probabilities
   __shared__ float scratch[8];
+  __shared__ __align__(16) float q_s[HD];
+  __shared__ __align__(16) T k_new[HD];
+  __shared__ __align__(16) T v_new[HD];
   constexpr int VEC = 16 / sizeof(T);
   constexpr int LPK = HD / VEC;        // lanes per key
-  constexpr int KPW = 32 / LPK;        // keys per warp per iteration
+  constexpr int KPW = 32 / LPK;        // keys per warp per load round
+  constexpr int half = HD / 2;
   const int h = blockIdx.x, b = blockIdx.y;
-  const int kvh = h / (a.nh / a.nkv);
-  const int total = *a.ctx_len + 1;
+  const int rep = a.nh / a.nkv, kvh = h / rep;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pos = *a.ctx_len;          // the new token's position
+  if (pos >= a.P) {
+    if (threadIdx.x == 0) atomicOr(err, DEV_ERR_INDEX_OOB);
+    return;
+  }
+  const int total = pos + 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane % LPK, kslot = lane / LPK;
-  const T* q = (const T*)a.q + (long long)b * a.q_row_stride + h * HD;
-  const T* kc = (const T*)a.kc + ((long long)b * a.nkv + kvh) * a.P * HD;
-  const T* vc = (const T*)a.vc + ((long long)b * a.nkv + kvh) * a.P * HD;
+  T* kc = (T*)a.kc + ((long long)b * a.nkv + kvh) * a.P * HD;
+  T* vc = (T*)a.vc + ((long long)b * a.nkv + kvh) * a.P * HD;
+
+  // RoPE of q and of the new k row; v row copied
+  if (threadIdx.x < HD) {  // threads [0, half): q pair; [half, HD): k pair
+    const bool is_q = threadIdx.x < half;
+    const int i = is_q ? threadIdx.x : threadIdx.x - half;
+    const T* src = is_q ? (const T*)a.q + (long long)b * a.q_row_stride + h * HD
+                        : (const T*)a.k + (long long)b * a.k_row_stride + kvh * HD;
+    float x1 = Elem<T>::load(src[i]), x2 = Elem<T>::load(src[i + half]);
+    float c = a.cos_t[(long long)pos * half + i], sn = a.sin_t[(long long)pos * half + i];
+    float o1 = c * x1 + sn * (-x2);
+    float o2 = c * x2 + sn * x1;
+    if (is_q) {
+      q_s[i] = rt<T>(o1);
+      q_s[i + half] = rt<T>(o2);
+    } else {
+      k_new[i] = Elem<T>::store(o1);
+      k_new[i + half] = Elem<T>::store(o2);
+    }
+  } else if (threadIdx.x < 2 * HD) {
+    const int i = threadIdx.x - HD;
+    v_new[i] = ((const T*)a.v)[(long long)b * a.v_row_stride + kvh * HD + i];
+  }
+  __syncthreads();
+  if (h % rep == 0 && threadIdx.x < HD) {
+    kc[(long long)pos * HD + threadIdx.x] = k_new[threadIdx.x];
+    vc[(long long)pos * HD + threadIdx.x] = v_new[threadIdx.x];
+  }
 
   float qf[VEC];
-  {
-    VecT<T, VEC> qv = *reinterpret_cast<const VecT<T, VEC>*>(q + sub * VEC);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) qf[i] = Elem<T>::load(qv.v[i]);
-  }
-  for (int t0 = warp * KPW; t0 < total; t0 += 8 * KPW) {
-    int t = t0 + kslot;
-    float d = 0.f;
-    if (t < total) {
-      VecT<T, VEC> kv = *reinterpret_cast<const VecT<T, VEC>*>(kc + (long long)t * HD + sub * VEC);
+  for (int i = 0; i < VEC; ++i) qf[i] = q_s[sub * VEC + i];
+  // scores over the cached keys: 4 independent 16-byte loads in flight per lane
+  constexpr int UN = 4;
+  for (int t0 = warp * KPW * UN; t0 < pos; t0 += 8 * KPW * UN) {
+    VecT<T, VEC> kv[UN];
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) d = fmaf(qf[i], Elem<T>::load(kv.v[i]), d);
+    for (int u = 0; u < UN; ++u) {
+      int t = t0 + u * KPW + kslot;
+      if (t < pos) kv[u] = *reinterpret_cast<const VecT<T, VEC>*>(kc + (long long)t * HD + sub * VEC);
+      else memset(&kv[u], 0, sizeof(kv[u]));
     }
 #pragma unroll
-    for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-    if (sub == 0 && t < total) sc[t] = rt<T>(rt<T>(d) / a.scale);
+    for (int u = 0; u < UN; ++u) {
+      int t = t0 + u * KPW + kslot;
+      float d = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) d = fmaf(qf[i], Elem<T>::load(kv[u].v[i]), d);
+#pragma unroll
+      for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      if (sub == 0 && t < pos) sc[t] = rt<T>(rt<T>(d) / a.scale);
+    }
+  }
+  if (warp == 0) {  // the new key, from shared memory
+    float d = 0.f;
+    for (int i = lane; i < HD; i += 32) d = fmaf(q_s[i], Elem<T>::load(k_new[i]), d);
+    d = warp_sum(d);
+    if (lane == 0) sc[pos] = rt<T>(rt<T>(d) / a.scale);
   }
   __syncthreads();
   float mx = -FLT_MAX;  // `max` folds from f32::MIN (ndarray.rs:656-661)
@@ -330,16 +433,31 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnArgs a) {
   // P.v: thread = (16-byte chunk of the head dim, key group); partial sums over its keys, then a fixed-order
   // reduction over the key groups through shared memory.
   constexpr int NCH = HD / VEC, TG = 256 / NCH;
-  float* part = sc + a.P;  // [TG][HD]
+  float* part = sc + a.P + 1;  // [TG][HD]
   const int ch = threadIdx.x % NCH, tg = threadIdx.x / NCH;
   float acc[VEC];
 #pragma unroll
   for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-  for (int t = tg; t < total; t += TG) {
-    float p = sc[t];
-    VecT<T, VEC> vv = *reinterpret_cast<const VecT<T, VEC>*>(vc + (long long)t * HD + ch * VEC);
+  for (int t0 = tg; t0 < pos; t0 += TG * UN) {
+    VecT<T, VEC> vv[UN];
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(p, Elem<T>::load(vv.v[i]), acc[i]);
+    for (int u = 0; u < UN; ++u) {
+      int t = t0 + u * TG;
+      if (t < pos) vv[u] = *reinterpret_cast<const VecT<T, VEC>*>(vc + (long long)t * HD + ch * VEC);
+      else memset(&vv[u], 0, sizeof(vv[u]));
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      int t = t0 + u * TG;
+      float p = t < pos ? sc[t] : 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = fmaf(p, Elem<T>::load(vv[u].v[i]), acc[i]);
+    }
+  }
+  if (tg == (pos % TG)) {  // the new value row joins the group that would have owned key `pos`
+    float p = sc[pos];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(p, Elem<T>::load(v_new[ch * VEC + i]), acc[i]);
   }
 #pragma unroll
   for (int i = 0; i < VEC; ++i) part[tg * HD + ch * VEC + i] = acc[i];
@@ -446,16 +564,64 @@ __global__ void rope_table_kernel(float* cos_t, float* sin_t, int P, int half, f
   }
 }
 
-// End of a step: the greedy ids of this step become the next step's input, are recorded for the host, and
-// the context length advances.
-__global__ void advance_kernel(const unsigned* __restrict__ new_ids, unsigned* __restrict__ cur_ids,
-                               unsigned* __restrict__ out_ids, int* ctx_len, int* step_no, int B, int S,
-                               int out_cap_steps) {
-  int step = *step_no;
-  for (int b = threadIdx.x; b < B; b += blockDim.x) {
-    unsigned id = new_ids[b];
-    cur_ids[b] = id;
-    if (step < out_cap_steps) out_ids[(long long)step * B + b] = id;
+// ---- greedy pick over the logits (llama.rs:225; ndarray.rs:670-694), two stages ----------------------
+// Stage 1: every CTA reduces one 4096-wide chunk of one row to a 64-bit key (value image under total_cmp in the
+// high word, index in the low word: the maximum key is the LAST index among the greatest values) and writes it
+// to the scratch array partials[row * chunks + chunk].  Stage 2 (advance_kernel) reduces the partial keys.
+constexpr int ARGMAX_CHUNK = 4096;
+template <class T>
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const T* __restrict__ logits, long long row_stride, int n,
+                                                             unsigned long long* __restrict__ partials) {
+  __shared__ unsigned long long wbest[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int chunk = blockIdx.x, row = blockIdx.y, chunks = gridDim.x;
+  const T* x = logits + (long long)row * row_stride;
+  const int lo = chunk * ARGMAX_CHUNK, hi = min(n, lo + ARGMAX_CHUNK);
+  unsigned long long best = 0ull;
+  for (int i = lo + threadIdx.x; i < hi; i += 256) {
+    unsigned hiw = (unsigned)total_key(Elem<T>::load(x[i])) ^ 0x80000000u;
+    unsigned long long key = ((unsigned long long)hiw << 32) | (unsigned)i;
+    best = key > best ? key : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((threadIdx.x & 31) == 0) wbest[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) best = wbest[w] > best ? wbest[w] : best;
+    partials[(long long)row * chunks + chunk] = best;
+  }
+}
+
+// End of a step: stage 2 of the greedy pick, then the new ids become the next step's input, are recorded for
+// the host, and the context length advances.  One CTA; warp w handles rows w, w+8, ...
+__global__ void __launch_bounds__(256) advance_kernel(const unsigned long long* __restrict__ partials, int chunks,
+                                                      unsigned* __restrict__ cur_ids, unsigned* __restrict__ out_ids,
+                                                      int* ctx_len, int* step_no, int B, int S, int out_cap_steps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int step = *step_no;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int b = warp; b < B; b += 8) {
+    unsigned long long best = 0ull;
+    for (int c = lane; c < chunks; c += 32) {
+      unsigned long long k = partials[(long long)b * chunks + c];
+      best = k > best ? k : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+    if (lane == 0) {
+      unsigned id = (unsigned)(best & 0xffffffffull);
+      cur_ids[b] = id;
+      if (step < out_cap_steps) out_ids[(long long)step * B + b] = id;
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
