@@ -119,6 +119,7 @@ CUDA_ONLY = {
     "event_elapsed_ms": (C.c_int, [_CTX, C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "ctx_stats": (C.c_int, [_CTX, u64p]),
     "flush_l2": (C.c_int, [_CTX, C.c_uint64]),
+    "argmax_rows_noalloc": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p]),
 }
 
 

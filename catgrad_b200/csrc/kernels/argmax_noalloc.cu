@@ -1,0 +1,144 @@
+// cg_argmax_rows_noalloc: the two-stage greedy pick (last-axis argmax) for callers that must not allocate.
+//
+// Who needs it: code that runs where device allocation is off the table.  Examples are a serving loop whose
+// memory was carved up front and is owned by another allocator (any cudaMalloc would fragment or fail it), a
+// host callback or latency-critical section where cudaMalloc's implicit device synchronisation is unacceptable,
+// and plug-ins that are handed raw device pointers and a stream but no allocator to ask.  The regular entry
+// point cg_argmax returns a NEW tensor from the context's caching allocator, so it may call cudaMalloc.
+//
+// This variant takes caller-owned input and output buffers and keeps its only scratch (the stage-1 partial
+// keys) in a fixed array that is part of the library image: every GPU that loads the library holds
+// CG_NOALLOC_MAX_PARTIALS * 8 bytes (128 KiB) of it until the process exits.  It calls no cudaMalloc, cudaFree
+// or any allocating routine.
+//
+// Sharing rules that follow from the fixed array:
+//  * all calls on one GPU use the same scratch; two calls whose kernels overlap on the GPU (different streams,
+//    different threads) race on it.  Serialise them.
+//  * the array keeps whatever the last call left.  Nothing has to start at zero here: stage 1 writes every
+//    entry [0, rows * chunks) that stage 2 of the same call reads.
+//  * the first call on each device looks the array's device address up (cudaGetSymbolAddress).  Make that first
+//    call outside any stream capture.
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <string>
+
+#include "../host/c_api_internal.h"
+#include "elementwise.h"
+
+#define CG_NOALLOC_MAX_PARTIALS 16384
+
+namespace {
+
+// Host code may only use this name to ask the runtime for its device address; kernels get the address as an
+// ordinary pointer argument.
+static __device__ __align__(256) unsigned long long g_noalloc_partials[CG_NOALLOC_MAX_PARTIALS];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_setup_mu;
+unsigned long long* g_scratch_ptr[kMaxDevices] = {nullptr};
+
+constexpr int kChunk = 4096;  // elements of one row reduced by one CTA in stage 1
+
+// Stage 1: CTA (chunk, row) reduces 4096 elements of one row to a 64-bit key: the value's image under
+// f32::total_cmp in the high word, the index in the low word, so the greatest key is the LAST index among the
+// greatest values (the rule of the reference's argmax, ndarray.rs:670-694).  Writes scratch[row * chunks + chunk].
+template <class T>
+__global__ void __launch_bounds__(256) argmax_stage1_kernel(const T* __restrict__ x, long long row_stride, int n,
+                                                            unsigned long long* __restrict__ scratch) {
+  __shared__ unsigned long long wbest[8];
+  const int chunk = blockIdx.x, row = blockIdx.y, chunks = gridDim.x;
+  const T* r = x + (long long)row * row_stride;
+  const int lo = chunk * kChunk, hi = min(n, lo + kChunk);
+  unsigned long long best = 0ull;
+  for (int i = lo + threadIdx.x; i < hi; i += 256) {
+    unsigned hiw = (unsigned)cgk::total_key(cgk::Elem<T>::load(r[i])) ^ 0x80000000u;
+    unsigned long long key = ((unsigned long long)hiw << 32) | (unsigned)i;
+    best = key > best ? key : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((threadIdx.x & 31) == 0) wbest[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) best = wbest[w] > best ? wbest[w] : best;
+    scratch[(long long)row * chunks + chunk] = best;
+  }
+}
+
+// Stage 2: one warp per row reduces that row's partial keys; the low word of the greatest key is the index.
+__global__ void __launch_bounds__(256) argmax_finish_kernel(const unsigned long long* __restrict__ partials, int chunks,
+                                                            int rows, unsigned* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  unsigned long long best = 0ull;
+  for (int c = lane; c < chunks; c += 32) {
+    unsigned long long k = partials[(long long)row * chunks + c];
+    best = k > best ? k : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if (lane == 0) out[row] = (unsigned)(best & 0xffffffffull);
+}
+
+// Device address of the scratch array on the current device, looked up once per device.
+unsigned long long* scratch_for_current_device() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) throw cg::Error(cg::ERR_CUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) throw cg::Error(cg::ERR_INVALID_ARG, "device index above 63");
+  std::lock_guard<std::mutex> lk(g_setup_mu);
+  if (!g_scratch_ptr[dev]) {
+    unsigned long long* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_partials);
+    if (e != cudaSuccess || p == nullptr)
+      throw cg::Error(cg::ERR_CUDA, std::string("cudaGetSymbolAddress(scratch): ") + cudaGetErrorString(e));
+    g_scratch_ptr[dev] = p;
+  }
+  return g_scratch_ptr[dev];
+}
+
+}  // namespace
+
+extern "C" int cg_argmax_rows_noalloc(const void* x, int dtype, uint64_t rows, uint64_t n, uint64_t row_stride,
+                                      uint32_t* out, void* stream) {
+  CG_API_BEGIN
+  CG_CHECK(x != nullptr && out != nullptr, cg::ERR_INVALID_ARG, "cg_argmax_rows_noalloc: null buffer");
+  CG_CHECK(dtype == cgk::DT_F32 || dtype == cgk::DT_BF16 || dtype == cgk::DT_F16, cg::ERR_UNSUPPORTED_DTYPE,
+           "cg_argmax_rows_noalloc: dtype must be f32, bf16 or f16");
+  CG_CHECK(rows >= 1 && n >= 1 && n <= 0x7fffffffull && row_stride >= n, cg::ERR_INVALID_ARG,
+           "cg_argmax_rows_noalloc: need rows >= 1, 1 <= n < 2^31, row_stride >= n");
+  const uint64_t chunks = (n + kChunk - 1) / kChunk;
+  CG_CHECK(rows <= 65535 && rows * chunks <= CG_NOALLOC_MAX_PARTIALS, cg::ERR_INVALID_ARG,
+           "cg_argmax_rows_noalloc: rows * ceil(n / 4096) = " + std::to_string(rows * chunks) +
+               " exceeds the fixed scratch of " + std::to_string(CG_NOALLOC_MAX_PARTIALS) +
+               " entries; use cg_argmax or split the rows");
+  unsigned long long* scratch = scratch_for_current_device();
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid((unsigned)chunks, (unsigned)rows);
+  switch (dtype) {
+    case cgk::DT_F32:
+      argmax_stage1_kernel<float><<<grid, 256, 0, st>>>((const float*)x, (long long)row_stride, (int)n, scratch);
+      break;
+    case cgk::DT_BF16:
+      argmax_stage1_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (long long)row_stride,
+                                                                     (int)n, scratch);
+      break;
+    default:
+      argmax_stage1_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, (long long)row_stride, (int)n, scratch);
+      break;
+  }
+  argmax_finish_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(scratch, (int)chunks, (int)rows, out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw cg::Error(cg::ERR_CUDA, std::string("cg_argmax_rows_noalloc launch: ") + cudaGetErrorString(e));
+  e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) throw cg::Error(cg::ERR_CUDA, std::string("cg_argmax_rows_noalloc: ") + cudaGetErrorString(e));
+  CG_API_END(nullptr)
+}

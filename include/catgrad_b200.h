@@ -210,6 +210,19 @@ cg_status cg_ctx_stats(cg_ctx*, uint64_t stats[4] /* live bytes, cached bytes, c
 /* Writes `bytes` of device memory on the context's stream (used by benchmarks to evict L2). */
 cg_status cg_flush_l2(cg_ctx*, uint64_t bytes);
 
+/* ---- allocation-free entry point ------------------------------------------------------------
+ * No counterpart in the reference (its backends allocate freely; argmax there is mod.rs:85).
+ * Last-axis argmax of `rows` rows of `n` elements (row r starts at x + r * row_stride elements; dtype CG_F32,
+ * CG_BF16 or CG_F16), same result as cg_argmax: the u32 index of the LAST maximum under f32::total_cmp.
+ * For callers that cannot allocate device memory: x and out ([rows] u32) are caller-owned device buffers on the
+ * CURRENT device, `stream` is a cudaStream_t (NULL = default stream), and the only scratch is a fixed 128 KiB
+ * array inside the library.  Limits: rows <= 65535 and rows * ceil(n / 4096) <= 16384, otherwise
+ * CG_ERR_INVALID_ARG.  The call returns after the kernels have finished (it synchronises `stream`) and calls no
+ * cudaMalloc/cudaFree.  All calls on one GPU share the scratch: do not let two of them overlap on the device.
+ * The first call on each device looks up the scratch address; make it outside any stream capture. */
+cg_status cg_argmax_rows_noalloc(const void* x, cg_dtype dtype, uint64_t rows, uint64_t n, uint64_t row_stride,
+                                 uint32_t* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
