@@ -164,9 +164,8 @@ struct Plan {
     std::memset(&bt, 0, sizeof(bt));
     bt.rank = 0;
     bt.total = 1;
-    if (std::is_same<T, __nv_bfloat16>::value &&
-        cgk::tcgen05_gemm_applicable(bt, 1, xin, W, M, N, K, ldx, 1, 1, K)) {
-      cgk::launch_tcgen05_gemm(bt, 1, xin, W, out, M, N, K, ldx, K, m.be->dev_err(), sm, st);
+    if (std::is_same<T, __nv_bfloat16>::value && cgk::tcgen05_gemm_applicable(bt, 1, xin, W, M, N, K, ldx, 1, 1, K) &&
+        cgk::launch_tcgen05_gemm(bt, 1, xin, W, out, M, N, K, ldx, K, m.be->dev_err(), sm, st)) {
       launched("gemm(tcgen05)");
       return;
     }

@@ -1,8 +1,385 @@
-// placeholder while the tensor-core kernel is being written
+// bf16 GEMM on Blackwell tensor cores: C[M,N] = A[M,K] x B[N,K]^T, f32 accumulation in tensor memory.
+//
+// This is the tensor-core path of `matmul` (catgrad/src/interpreter/backend/mod.rs:61; ndarray.rs:732-816;
+// bf16 semantics = candle.rs:601-610: bf16 operands, wide accumulate, bf16 result) for the layout every
+// `linear` produces: activations [M,K] row-major times a weight kept as W[N,K] row-major
+// (stdlib/nn/mod.rs:182-204: x @ broadcast(transpose(W)); both operands are K-contiguous, nothing is copied).
+//
+// Structure of one CTA (192 threads), one 128 x BN output tile:
+//   warp 0, one lane : TMA producer.  cp.async.bulk.tensor loads 128x64 (A) and BNx64 (B) bf16 boxes with the
+//                      128-byte swizzle into a ring of shared-memory stages; completion lands on an mbarrier.
+//   warp 1, one lane : issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) from shared-memory descriptors into a
+//                      TMEM accumulator; tcgen05.commit releases each stage and finally signals the epilogue.
+//                      Warp 1 also allocates/frees the TMEM columns.
+//   warps 2..5       : epilogue.  tcgen05.ld pulls the f32 accumulator (each warp its 32 TMEM lanes = 32 rows),
+//                      rounds once to bf16 and stores 64-byte row segments.
+// Rows/columns beyond M, N, K are zero-filled by TMA on the way in and masked on the way out, so any M, N and any
+// K that keeps rows 16-byte aligned work.  No multicast, no clusters: the kernel may run in multi-GPU jobs.
+//
+// Every wait on an mbarrier is bounded: after ~1 s a role records DEV_ERR_WAIT_TIMEOUT, raises a CTA-wide abort
+// flag, all roles fall through, TMEM is freed and the kernel returns.
+//
+// Bound: bf16 tensor pipe for large M; for M <= 128 (decode of a batch) it streams W once and is HBM-bound.
+// Algorithmic work: 2*M*N*K flop, (M*K + N*K + M*N) * 2 bytes.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <mutex>
+
 #include "gemm_tcgen05.h"
+
 namespace cgk {
-bool tcgen05_gemm_applicable(const View4&, long long, const void*, const void*, long long, long long, long long,
-                             long long, long long, long long, long long) { return false; }
-void launch_tcgen05_gemm(const View4&, long long, const void*, const void*, void*, long long, long long, long long,
-                         long long, long long, unsigned*, int, cudaStream_t) {}
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr long long WAIT_CYCLES = 2000000000ll;  // ~1 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred P1;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, P1;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if the barrier did not flip in time or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > WAIT_CYCLES) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major operand tile written by TMA with the 128-byte swizzle:
+// rows are 128 bytes, groups of 8 rows are 1024 bytes apart (stride byte offset), descriptor version 1,
+// layout type 2 (SWIZZLE_128B).  The tile base is 1024-byte aligned.
+__device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+  d |= (uint64_t)1 << 46;                            // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::f16: D = f32, A = B = bf16, both K-major, shape M x N.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+};
+
+// grid: (ceil(N/BN), ceil(M/BM), batch).  BATCHED selects 3-D tensor maps {K, rows, batch}.
+template <int BN, int STAGES, bool BATCHED>
+__global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                           const __grid_constant__ CUtensorMap tmB,
+                                                           __nv_bfloat16* __restrict__ C, int M, int N, int K,
+                                                           long long c_batch_stride, unsigned* err) {
+  using L = SmemLayout<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(tmem_full + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, bz = blockIdx.z;
+  const int num_k = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer ----
+    int issued = 0;
+    for (int k = 0; k < num_k; ++k) {
+      const int s = k % STAGES;
+      const uint32_t par = ((k / STAGES) & 1) ^ 1;
+      if (!mbar_wait(&empty[s], par, abort_flag)) break;
+      unsigned char* a_dst = smem + s * L::STAGE_BYTES;
+      unsigned char* b_dst = a_dst + L::A_BYTES;
+      mbar_expect_tx(&full[s], L::STAGE_BYTES);
+      if (BATCHED) {
+        tma_load_3d(a_dst, &tmA, &full[s], k * BK, m0, bz);
+        tma_load_3d(b_dst, &tmB, &full[s], k * BK, n0, bz);
+      } else {
+        tma_load_2d(a_dst, &tmA, &full[s], k * BK, m0);
+        tma_load_2d(b_dst, &tmB, &full[s], k * BK, n0);
+      }
+      issued = k + 1;
+    }
+    if (*abort_flag) {
+      // give copies already in flight a bounded time to land before the CTA's shared memory goes away
+      for (int k = (issued > STAGES ? issued - STAGES : 0); k < issued; ++k) {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&full[k % STAGES], (k / STAGES) & 1) && clock64() - t0 < WAIT_CYCLES) {
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ----
+    constexpr uint32_t idesc = make_idesc(BM, BN);
+    bool ok = true;
+    for (int k = 0; k < num_k && ok; ++k) {
+      const int s = k % STAGES;
+      ok = mbar_wait(&full[s], (k / STAGES) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const unsigned char* a_tile = smem + s * L::STAGE_BYTES;
+      const uint64_t adesc = make_smem_desc(a_tile);
+      const uint64_t bdesc = make_smem_desc(a_tile + L::A_BYTES);
+#pragma unroll
+      for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+        // advancing 16 bf16 = 32 bytes along K inside the swizzle row: +2 in the 16-byte address field
+        umma_bf16(tmem_base, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (k | kk) != 0 ? 1u : 0u);
+      }
+      umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+    }
+    if (ok) umma_commit(tmem_full);  // accumulator complete
+  } else if (warp >= 2) {
+    // ---- epilogue: warp w owns TMEM lanes 32*(w%4) .. +31 = rows m0 + 32*(w%4) + lane ----
+    bool ok = mbar_wait(tmem_full, 0, abort_flag);
+    // all lanes of the warp must agree before the warp-collective tcgen05.ld
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const int row = m0 + q * 32 + lane;
+      __nv_bfloat16* crow = C + (long long)bz * c_batch_stride + (long long)row * N;
+      const bool vec_ok = (N % 8 == 0) && (((uintptr_t)C & 15) == 0) && ((c_batch_stride % 8) == 0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (row < M) {
+          const int col = n0 + c0;
+          if (vec_ok && col + 32 <= N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+                w[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(crow + col + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col + j < N) crow[col + j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+          }
+        }
+      }
+    }
+  }
+  if (*abort_flag && threadIdx.x == 0) atomicOr(err, DEV_ERR_WAIT_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN));
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is resolved through the runtime, so the library has no link-time dependency on libcuda.
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// rows x K bf16 matrix with K contiguous and a row pitch of ld elements; optional batch axis.
+bool make_map(CUtensorMap* map, const void* base, long long K, long long rows, long long ld, long long batch,
+              long long batch_stride, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)batch_stride * 2};
+  cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  int rank = batch > 1 ? 3 : 2;
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct Problem {
+  bool ok = false;
+  long long M, batch, a_bs, b_bs;  // after folding a shared-B batch into M
+};
+
+Problem analyse(const View4& bt, long long batch, const void* A, const void* B, long long M, long long N, long long K,
+                long long sam, long long sak, long long sbk, long long sbn) {
+  Problem p;
+  if (sak != 1 || sbk != 1) return p;
+  if (K < 16 || K % 8 != 0 || sam % 8 != 0 || sbn % 8 != 0) return p;
+  if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return p;
+  if (sam < K || sbn < K) return p;
+  if (N < 16) return p;
+  p.M = M;
+  p.batch = 1;
+  p.a_bs = p.b_bs = 0;
+  if (batch > 1) {
+    if (bt.rank != 1) return p;
+    long long as = bt.sa[0], bs = bt.sb[0];
+    if (bs == 0 && as == M * sam) {
+      p.M = M * batch;  // one weight shared by the whole batch: the batch is just more rows
+    } else {
+      if (as % 8 != 0 || bs % 8 != 0 || as <= 0 || bs <= 0 || batch > 65535) return p;
+      p.batch = batch;
+      p.a_bs = as;
+      p.b_bs = bs;
+    }
+  }
+  if (p.M * p.batch < 17) return p;  // tiny products stay on the streaming GEMV
+  if (p.M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll) return p;
+  p.ok = encode_fn() != nullptr;
+  return p;
+}
+
+template <int BN, int STAGES, bool BATCHED>
+void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K,
+              long long batch, unsigned* err, cudaStream_t st) {
+  using L = SmemLayout<BN>;
+  size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 /* alignment slack */ + (2 * STAGES + 1) * 8 + 16;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, BATCHED>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)batch);
+  kern<<<grid, 192, smem, st>>>(ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, M * N, err);
+}
+}  // namespace
+
+bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, const void* B, long long M, long long N,
+                             long long K, long long sam, long long sak, long long sbk, long long sbn) {
+  static const bool disabled = std::getenv("CATGRAD_B200_NO_TCGEN05") != nullptr;
+  if (disabled) return false;
+  return analyse(bt, batch, A, B, M, N, K, sam, sak, sbk, sbn).ok;
+}
+
+bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
+                         long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
+                         cudaStream_t st) {
+  Problem p = analyse(bt, batch, A, B, M, N, K, lda, 1, 1, ldb);
+  if (!p.ok) return false;
+  CUtensorMap ta, tb;
+  // 128x256 tiles only when 128x128 tiles would already give every SM two CTAs
+  const long long tiles128 = ((p.M + BM - 1) / BM) * ((N + 127) / 128) * p.batch;
+  const bool wide = N >= 256 && tiles128 >= 2ll * sm_count;
+  const int bn = wide ? 256 : 128;
+  if (!make_map(&ta, A, K, p.M, lda, p.batch, p.a_bs, BM) || !make_map(&tb, B, K, N, ldb, p.batch, p.b_bs, bn)) return false;
+  if (p.batch > 1) {
+    if (wide) launch_t<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, st);
+    else launch_t<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, st);
+  } else {
+    if (wide) launch_t<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, st);
+    else launch_t<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, st);
+  }
+  return true;
+}
+
+}  // namespace cgk

@@ -9,7 +9,8 @@ bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, co
                              long long K, long long sam, long long sak, long long sbk, long long sbn);
 // C[batch, M, N] (contiguous bf16) = A x B^T-layout; f32 accumulation in TMEM, one rounding to bf16.
 // Device-side waits are bounded; a timeout sets DEV_ERR_WAIT_TIMEOUT in *err and the kernel returns.
-void launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
+// Returns false (nothing launched) if the tensor maps cannot be made; the caller then uses the SIMT kernel.
+bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
                          long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
                          cudaStream_t st);
 }  // namespace cgk

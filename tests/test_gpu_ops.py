@@ -311,3 +311,47 @@ def test_fp8_moves_and_casts(oracle, gpu):
                                   gpu.to_numpy(gpu.cast(gpu.from_numpy(x), Dtype.F8)))
     with pytest.raises(cb.BackendError):
         gpu.add(fg, fg)
+
+
+def _bf16_round(a):
+    return cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(a)).reshape(a.shape)
+
+
+@pytest.mark.parametrize("mnk", [(128, 128, 64), (300, 200, 264), (17, 2048, 512), (512, 384, 2048), (1000, 136, 72),
+                                 (129, 257, 1032), (64, 16, 16)], ids=str)
+def test_tensor_core_gemm_against_f32_path(gpu, mnk):
+    """bf16 `x @ W^T` products (both operands K-contiguous) run on the tcgen05 kernel; the same bf16-rounded
+    operands multiplied by the exact-f32 SIMT kernel give the reference.  Only the accumulation order differs, so
+    after one rounding to bf16 the results agree to 1 bf16 ulp of the row scale."""
+    m, n, k = mnk
+    rng = np.random.default_rng(m * 7 + n * 3 + k)
+    x = _bf16_round(rng.standard_normal((m, k)).astype(np.float32))
+    w = _bf16_round((rng.standard_normal((n, k)) / np.sqrt(k)).astype(np.float32))
+    got = gpu.to_f32(gpu.matmul(gpu.from_numpy(x, Dtype.BF16), gpu.transpose(gpu.from_numpy(w, Dtype.BF16), 0, 1)))
+    ref = gpu.to_numpy(gpu.matmul(gpu.from_numpy(x), gpu.transpose(gpu.from_numpy(w), 0, 1)))
+    np.testing.assert_allclose(got, ref, rtol=1e-2, atol=1e-2)
+    assert helpers.rel_err(got, ref) < 6e-3
+    # float64 check of a corner block, independent of any GPU kernel
+    ref64 = x[:8].astype(np.float64) @ w[-8:].astype(np.float64).T
+    np.testing.assert_allclose(got[:8, -8:], ref64, rtol=1e-2, atol=1e-2)
+
+
+def test_tensor_core_gemm_batched_and_shared_weight(oracle, gpu):
+    rng = np.random.default_rng(12)
+    # a weight shared by the batch (the `linear` pattern): the batch folds into rows
+    x = _bf16_round(rng.standard_normal((4, 40, 256)).astype(np.float32))
+    w = _bf16_round((rng.standard_normal((192, 256)) / 16).astype(np.float32))
+    res = []
+    for be in (oracle, gpu):
+        xt, wt = be.from_numpy(x, Dtype.BF16), be.from_numpy(w, Dtype.BF16)
+        res.append(be.to_f32(be.matmul(xt, be.broadcast(be.transpose(wt, 0, 1), (4, 256, 192)))))
+    np.testing.assert_allclose(res[1], res[0], rtol=2e-2, atol=2e-2)
+    # a true batch: q @ k^T per head, k stored [heads, T, D]
+    q = _bf16_round(rng.standard_normal((3, 150, 64)).astype(np.float32))
+    kk = _bf16_round(rng.standard_normal((3, 96, 64)).astype(np.float32))
+    res = []
+    for be in (oracle, gpu):
+        res.append(be.to_f32(be.matmul(be.from_numpy(q, Dtype.BF16), be.transpose(be.from_numpy(kk, Dtype.BF16), 1, 2))))
+    np.testing.assert_allclose(res[1], res[0], rtol=2e-2, atol=6e-2)
+    ref64 = np.einsum("bmk,bnk->bmn", q.astype(np.float64), kk.astype(np.float64))
+    np.testing.assert_allclose(res[1], ref64, rtol=2e-2, atol=8e-2)
