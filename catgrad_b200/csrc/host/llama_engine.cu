@@ -14,11 +14,13 @@
 // llama_kernels.cuh).  The lm_head runs on the last position of each sequence only: the reference computes it
 // for all S positions (llama.rs:217-225) and its runner reads only the last element.
 #include <cmath>
+#include <cstdio>
 #include <cstring>
 
 #include "../kernels/elementwise.h"
 #include "../kernels/gemm_tcgen05.h"
 #include "../kernels/llama_kernels.cuh"
+#include "../kernels/llama_mega.cuh"
 #include "../kernels/matmul.h"
 #include "c_api_internal.h"
 #include "cuda_backend.h"
@@ -54,7 +56,13 @@ struct cg_llama {
   Tensor logits;              // [Bmax, V]
   Tensor partials;            // u64 [Bmax, ceil(V/4096)]: stage-1 keys of the greedy pick (scratch)
   int argmax_chunks = 0;
+  // persistent one-kernel decode step (batch <= 4)
+  Tensor mega_layers, mega_partials, mega_prof;
+  bool mega_enabled = false;
+  unsigned long long bar_base = 0;
+  int mega_grid = 0;
   bool use_pdl = false;       // programmatic dependent launch between the kernels of a step (opt-in)
+  bool l2_prefetch = false;   // decode kernels pull the weights of later launches into L2 (opt-in)
   int64_t out_cap_steps = 0;
   // activation buffers sized for `cap_tokens` tokens
   int64_t cap_tokens = 0;
@@ -188,6 +196,106 @@ struct Plan {
     launched("add");
   }
 
+  // ---- the one-kernel decode step (llama_mega.cuh) ----
+  static int mega_mt(int64_t B) { return B <= 1 ? 1 : (B <= 2 ? 2 : 4); }
+  struct MegaGeom { bool ok = false; int nslots = 0; int xs_bytes = 0; size_t smem = 0; };
+  MegaGeom mega_geom(int64_t B) const {
+    MegaGeom g;
+    const LlamaConfig& c = m.cfg;
+    if (!m.mega_enabled || B > 4) return g;
+    const int mt = mega_mt(B);
+    const int64_t kmax = std::max<int64_t>(std::max<int64_t>(c.hidden_size, c.intermediate_size), c.num_attention_heads * c.head_dim());
+    constexpr int VEC = 16 / sizeof(T);
+    const int64_t hd = c.head_dim();
+    int64_t attn_bytes = (m.P + 1 + (256 / (hd / VEC)) * hd) * 4;
+    int64_t xs = std::max<int64_t>(mt * kmax * (int64_t)sizeof(T), attn_bytes);
+    xs = (xs + 127) / 128 * 128;
+    const int64_t tail = 8192;
+    const int64_t budget = 227 * 1024;
+    int64_t nslots = (budget - xs - tail) / cgk::MEGA_SLOT_BYTES;
+    if (nslots > 8) nslots = 8;
+    if (nslots < 2) return g;
+    // every row of every matrix must fit one slot; the input loader holds at most 4 x 256 16-byte groups;
+    // the row split uses 32-bit arithmetic
+    if (kmax * (int64_t)sizeof(T) > cgk::MEGA_SLOT_BYTES) return g;
+    if (kmax / VEC > 1024) return g;
+    if (std::max<int64_t>(c.vocab_size, c.intermediate_size) * (m.mega_grid + 1) >= (1ll << 31)) return g;
+    g.ok = true;
+    g.nslots = (int)nslots;
+    g.xs_bytes = (int)xs;
+    g.smem = (size_t)(nslots * cgk::MEGA_SLOT_BYTES + xs + tail);
+    return g;
+  }
+  template <int MT, int HD>
+  bool mega_launch_t(const cgk::MegaArgs& a, const MegaGeom& g) {
+    auto kern = m.mega_prof.defined() ? cgk::llama_decode_mega_kernel<T, MT, HD, true> : cgk::llama_decode_mega_kernel<T, MT, HD, false>;
+    static size_t smem_set[2] = {0, 0};
+    size_t& smem_set_ref = smem_set[m.mega_prof.defined() ? 1 : 0];
+    if (g.smem > smem_set_ref) {
+      cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+      if (e0 != cudaSuccess) {
+        cudaGetLastError();
+        std::fprintf(stderr, "[catgrad_b200] persistent decode kernel unavailable (shared memory %zu: %s); using the multi-kernel plan\n",
+                     g.smem, cudaGetErrorString(e0));
+        m.mega_enabled = false;
+        return false;
+      }
+      smem_set_ref = g.smem;
+    }
+    int per_sm = 0;
+    cudaError_t e1 = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, cgk::MEGA_THREADS, g.smem);
+    if (e1 != cudaSuccess || per_sm < 1) {
+      cudaGetLastError();
+      cudaFuncAttributes fa;
+      cudaFuncGetAttributes(&fa, kern);
+      std::fprintf(stderr, "[catgrad_b200] persistent decode kernel unavailable (occupancy %d, %s, regs %d, smem %zu); using the multi-kernel plan\n",
+                   per_sm, cudaGetErrorString(e1), fa.numRegs, g.smem);
+      m.mega_enabled = false;
+      return false;
+    }
+    cgk::MegaArgs args = a;
+    int xs_bytes = g.xs_bytes;
+    void* params[] = {(void*)&args, (void*)&xs_bytes};
+    cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(a.G), dim3(cgk::MEGA_THREADS), params, g.smem, st);
+    if (e != cudaSuccess) throw Error(ERR_CUDA, std::string("cooperative launch of the decode kernel: ") + cudaGetErrorString(e));
+    return true;
+  }
+  // Runs one decode step (S = 1) as one persistent kernel.  Returns false if this shape cannot use it.
+  bool mega_step(int64_t B) {
+    MegaGeom g = mega_geom(B);
+    if (!g.ok) return false;
+    const LlamaConfig& c = m.cfg;
+    cgk::MegaArgs a{};
+    a.L = (int)c.num_hidden_layers; a.H = (int)c.hidden_size; a.F = (int)c.intermediate_size;
+    a.NQ = (int)(c.num_attention_heads * c.head_dim()); a.NKV = (int)(c.num_key_value_heads * c.head_dim());
+    a.V = (int)c.vocab_size; a.nh = (int)c.num_attention_heads; a.nkv = (int)c.num_key_value_heads;
+    a.P = (int)m.P; a.B = (int)B; a.G = m.mega_grid; a.nslots = g.nslots;
+    a.eps = c.rms_norm_eps; a.scale = cgk_host_round((float)std::sqrt((float)c.head_dim()));
+    a.embed = m.embed; a.final_norm = m.final_norm; a.head = m.head;
+    a.layers = (const cgk::MegaLayer*)m.mega_layers.raw();
+    a.x = m.x.raw(); a.qkv = m.qkv.raw(); a.attn = m.attn.raw(); a.h = m.h.raw(); a.logits = m.logits.raw();
+    a.kc = m.kc.raw(); a.vc = m.vc.raw();
+    a.kv_layer_stride = m.max_batch * c.num_key_value_heads * m.P * c.head_dim();
+    a.cos_t = (const float*)m.cos_t.raw(); a.sin_t = (const float*)m.sin_t.raw();
+    a.ids_cur = (unsigned*)m.ids_cur.raw(); a.out_ids = (unsigned*)m.ids_out.raw();
+    a.ctx_len = (int*)m.words.raw(); a.step_no = (int*)m.words.raw() + 1; a.out_cap_steps = (int)m.out_cap_steps;
+    a.partials = (unsigned long long*)m.mega_partials.raw();
+    a.bar_counter = (unsigned long long*)((unsigned*)m.words.raw() + 4);
+    a.bar_base = m.bar_base;
+    a.err = m.be->dev_err(); a.abort_word = (unsigned*)m.words.raw() + 2;
+    a.prof = m.mega_prof.defined() ? (unsigned long long*)m.mega_prof.raw() : nullptr;
+    const int mt = mega_mt(B);
+    const bool hd64 = c.head_dim() == 64;
+    bool ok;
+    if (mt == 1) ok = hd64 ? mega_launch_t<1, 64>(a, g) : mega_launch_t<1, 128>(a, g);
+    else if (mt == 2) ok = hd64 ? mega_launch_t<2, 64>(a, g) : mega_launch_t<2, 128>(a, g);
+    else ok = hd64 ? mega_launch_t<4, 64>(a, g) : mega_launch_t<4, 128>(a, g);
+    if (!ok) return false;
+    m.bar_base += (unsigned long long)(5 * c.num_hidden_layers + 1) * (unsigned long long)a.G;
+    ++m.launches;
+    return true;
+  }
+
   // One evaluation of the term on M = B*S tokens whose ids are in `ids` (device).
   void step(const unsigned* ids, int64_t B, int64_t S) {
     const LlamaConfig& c = m.cfg;
@@ -203,6 +311,11 @@ struct Plan {
     launched("embed");
 
     const float scale = cgk_host_round((float)std::sqrt((float)hd));
+    const bool pf_on = m.l2_prefetch && S == 1 && gemv_ok(M, H);
+    const long long es = (long long)sizeof(T);
+    auto region = [&](cgk::PrefetchArgs& pf, int i, const void* p, long long elems) {
+      if (pf_on && p) { pf.ptr[i] = p; pf.bytes[i] = elems * es; }
+    };
     for (int64_t l = 0; l < L; ++l) {
       const LayerW& w = m.layers[l];
       // ---- attention block ----
@@ -213,6 +326,7 @@ struct Plan {
         a.n_end[0] = (int)NQ; a.n_end[1] = (int)(NQ + NKV); a.n_end[2] = (int)NQKV;
         a.x = x; a.x_row_stride = H; a.gain = w.in_norm; a.eps = c.rms_norm_eps;
         a.out = qkv; a.M = (int)M; a.N = (int)NQKV; a.K = (int)H;
+        region(a.pf, 0, w.o, H * NQ); region(a.pf, 1, w.gate, F * H); region(a.pf, 2, w.up, F * H);
         gemv(cgk::PRO_NORM, cgk::EPI_STORE, a);
       } else {
         rmsnorm(x, w.in_norm, m.xn.raw(), M, H, 1, 0);
@@ -270,6 +384,7 @@ struct Plan {
         cgk::GemvArgs a{};
         a.w[0] = w.o; a.n_end[0] = a.n_end[1] = a.n_end[2] = (int)H;
         a.x = attn; a.x_row_stride = NQ; a.out = x; a.res = x; a.M = (int)M; a.N = (int)H; a.K = (int)NQ;
+        region(a.pf, 0, w.down, H * F);
         gemv(cgk::PRO_NONE, cgk::EPI_RESIDUAL, a);
       } else {
         gemm(attn, NQ, w.o, m.tmp.raw(), M, H, NQ);
@@ -282,6 +397,12 @@ struct Plan {
         a.w[0] = w.gate; a.w[1] = w.up; a.n_end[0] = a.n_end[1] = a.n_end[2] = (int)F;
         a.x = x; a.x_row_stride = H; a.gain = w.post_norm; a.eps = c.rms_norm_eps;
         a.out = hbuf; a.M = (int)M; a.N = (int)F; a.K = (int)H;
+        if (l + 1 < L) {
+          const LayerW& nx = m.layers[l + 1];
+          region(a.pf, 0, nx.q, NQ * H); region(a.pf, 1, nx.k, NKV * H); region(a.pf, 2, nx.v, NKV * H);
+        } else {
+          region(a.pf, 0, m.head, std::min<long long>(V * H, 48ll << 20));  // the start of the lm_head
+        }
         gemv(cgk::PRO_NORM, cgk::EPI_SILU_MUL, a);
       } else {
         rmsnorm(x, w.post_norm, m.xn.raw(), M, H, 1, 0);
@@ -417,7 +538,20 @@ void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
   }
 }
 
-void run_step(cg_llama& m, const unsigned* ids, int64_t B, int64_t S) {
+bool mega_available(cg_llama& m, int64_t B) {
+  return m.dt == Dtype::BF16 ? Plan<__nv_bfloat16>(m).mega_geom(B).ok : Plan<float>(m).mega_geom(B).ok;
+}
+
+// allow_mega: decode steps that take their ids from the device id buffer may run as the single persistent
+// kernel; a step being captured into a CUDA graph may not (cooperative launch, per-launch barrier base).
+void run_step(cg_llama& m, const unsigned* ids, int64_t B, int64_t S, bool allow_mega = false) {
+  if (allow_mega && S == 1 && ids == (const unsigned*)m.ids_cur.raw()) {
+    bool done = m.dt == Dtype::BF16 ? Plan<__nv_bfloat16>(m).mega_step(B) : Plan<float>(m).mega_step(B);
+    if (done) {
+      m.host_ctx_len += 1;
+      return;
+    }
+  }
   if (m.dt == Dtype::BF16) Plan<__nv_bfloat16>(m).step(ids, B, S);
   else Plan<float>(m).step(ids, B, S);
   m.host_ctx_len += S;
@@ -513,7 +647,26 @@ int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const c
   m->partials = be.zeros({m->max_batch * m->argmax_chunks * 2}, Dtype::U32);
   // measured slower than plain graph edges on B200 for this chain (waiting CTAs hold SM resources): opt-in
   m->use_pdl = std::getenv("CATGRAD_B200_PDL") != nullptr;
+  // measured neutral-to-slower on B200 for this chain (the launches are latency-bound, not HBM-bound): opt-in
+  m->l2_prefetch = std::getenv("CATGRAD_B200_L2_PREFETCH") != nullptr;
   m->out_cap_steps = 0;
+  {
+    // table of per-layer weight pointers for the persistent decode kernel
+    std::vector<cgk::MegaLayer> tab;
+    for (auto& w : m->layers) tab.push_back(cgk::MegaLayer{w.in_norm, w.q, w.k, w.v, w.o, w.post_norm, w.gate, w.up, w.down});
+    m->mega_layers = be.empty({(int64_t)(tab.size() * sizeof(cgk::MegaLayer) / 4)}, Dtype::U32);
+    CG_CUDA(cudaMemcpyAsync(m->mega_layers.raw(), tab.data(), tab.size() * sizeof(cgk::MegaLayer), cudaMemcpyHostToDevice,
+                            be.stream()));
+    CG_CUDA(cudaStreamSynchronize(be.stream()));
+    m->mega_grid = be.sm_count();
+    m->mega_partials = be.zeros({(int64_t)m->mega_grid * 4 * 2}, Dtype::U32);
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, be.device());
+    // opt-in: at the current tuning the graph of per-sub-graph kernels is faster
+    m->mega_enabled = coop != 0 && std::getenv("CATGRAD_B200_MEGA") != nullptr;
+    // CATGRAD_B200_MEGA_PROF: per-CTA cycle counters of the persistent kernel, printed by cg_llama_free
+    if (std::getenv("CATGRAD_B200_MEGA_PROF")) m->mega_prof = be.zeros({(int64_t)m->mega_grid * 8 * 2}, Dtype::U32);
+  }
   *out = m.release();
   CG_API_END(ctx)
 }
@@ -523,6 +676,19 @@ void cg_llama_free(cg_llama* m) {
   if (m->be) {
     m->be->guard();
     cudaStreamSynchronize(m->be->stream());
+    if (m->mega_prof.defined()) {
+      std::vector<unsigned long long> h((size_t)m->mega_grid * 8);
+      if (cudaMemcpy(h.data(), m->mega_prof.raw(), h.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
+        static const char* names[] = {"barrier", "prologue", "wait_data", "multiply", "epilogue", "attention", "total"};
+        for (int c : {0, 1, 31, 32, 100, m->mega_grid - 1}) {
+          if (c < 0 || c >= m->mega_grid || h[(size_t)c * 8 + 7] == 0) continue;
+          double steps = (double)h[(size_t)c * 8 + 7];
+          std::fprintf(stderr, "[mega prof] cta %3d steps %.0f cycles/step:", c, steps);
+          for (int i = 0; i < 7; ++i) std::fprintf(stderr, " %s=%.0f", names[i], (double)h[(size_t)c * 8 + i] / steps);
+          std::fprintf(stderr, "\n");
+        }
+      }
+    }
   }
   delete m;
 }
@@ -536,6 +702,7 @@ int cg_llama_reset(cg_llama* mm, uint64_t batch) {
   CG_CUDA(cudaMemsetAsync(m.words.raw(), 0, 64, m.be->stream()));
   m.batch = (int64_t)batch;
   m.host_ctx_len = 0;
+  m.bar_base = 0;  // the barrier counter lives in `words` and was just cleared
   CG_API_END(ctx)
 }
 
@@ -553,9 +720,11 @@ int cg_llama_forward(cg_llama* mm, const uint32_t* ids, uint64_t batch, uint64_t
     m.out_cap_steps = 1;
   }
   cudaStream_t st = m.be->stream();
-  CG_CUDA(cudaMemcpyAsync(m.ids_in.raw(), ids, batch * seq * 4, cudaMemcpyHostToDevice, st));
+  // a single new token per sequence is a decode step: its ids go where the on-device loop keeps them
+  void* ids_dst = seq == 1 ? m.ids_cur.raw() : m.ids_in.raw();
+  CG_CUDA(cudaMemcpyAsync(ids_dst, ids, batch * seq * 4, cudaMemcpyHostToDevice, st));
   CG_CUDA(cudaMemsetAsync((int*)m.words.raw() + 1, 0, 4, st));  // step_no = 0
-  run_step(m, (const unsigned*)m.ids_in.raw(), (int64_t)batch, (int64_t)seq);
+  run_step(m, (const unsigned*)ids_dst, (int64_t)batch, (int64_t)seq, /*allow_mega=*/true);
   if (out_ids) {
     CG_CUDA(cudaMemcpyAsync(out_ids, m.ids_cur.raw(), batch * 4, cudaMemcpyDeviceToHost, st));
     CG_CUDA(cudaStreamSynchronize(st));
@@ -586,7 +755,8 @@ int cg_llama_decode(cg_llama* mm, uint64_t steps, uint32_t* out_ids) {
     m.out_cap_steps = (int64_t)steps;
   }
   CG_CUDA(cudaMemsetAsync((int*)m.words.raw() + 1, 0, 4, st));  // step_no = 0
-  const bool use_graph = std::getenv("CATGRAD_B200_NO_GRAPH") == nullptr;
+  const bool mega = mega_available(m, B);
+  const bool use_graph = !mega && std::getenv("CATGRAD_B200_NO_GRAPH") == nullptr;
   uint64_t first = 0;
   if (use_graph && (m.graph == nullptr || m.graph_batch != B)) {
     // The first step of a new shape runs eagerly (it also loads the kernels and sets their attributes,
@@ -625,7 +795,7 @@ int cg_llama_decode(cg_llama* mm, uint64_t steps, uint32_t* out_ids) {
       m.launches += m.graph_nodes;
       m.host_ctx_len += 1;
     } else {
-      run_step(m, (const unsigned*)m.ids_cur.raw(), B, 1);
+      run_step(m, (const unsigned*)m.ids_cur.raw(), B, 1, /*allow_mega=*/true);
     }
   }
   if (out_ids) {

@@ -45,6 +45,29 @@ __device__ __forceinline__ float block_max_256(float v, float* scratch) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Software pipelining across kernel launches: a kernel asks the L2 to fetch the weights of the launches that follow
+// it (fire-and-forget bulk prefetch), so HBM keeps streaming while this kernel works on data that an earlier
+// launch prefetched, and across the launch gap.  Each CTA requests its 1/gridDim slice of each region.
+struct PrefetchArgs {
+  const void* ptr[3];
+  long long bytes[3];
+};
+__device__ __forceinline__ void l2_prefetch_slices(const PrefetchArgs& pf) {
+  if (threadIdx.x != 0) return;
+  const long long nb = (long long)gridDim.x * gridDim.y, b = (long long)blockIdx.y * gridDim.x + blockIdx.x;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    if (pf.ptr[i] == nullptr || pf.bytes[i] <= 0) continue;
+    long long per = ((pf.bytes[i] + nb - 1) / nb + 15) & ~15ll;
+    long long lo = b * per, hi = lo + per < pf.bytes[i] ? lo + per : pf.bytes[i];
+    const char* base = (const char*)pf.ptr[i];
+    for (long long o = lo; o < hi; o += 65536) {
+      unsigned sz = (unsigned)((hi - o < 65536 ? hi - o : 65536) & ~15ll);
+      if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + o), "r"(sz) : "memory");
+    }
+  }
+}
+
 // ---- embedding gather (helpers/tensors.rs:255-272) ------------------------------------------------
 // x[m, :] = table[ids[m], :].  16-byte copies; an id >= vocab records DEV_ERR_INDEX_OOB and writes zeros.
 template <class T>
@@ -109,6 +132,7 @@ struct GemvArgs {
   const void* res;    // EPI_RESIDUAL: [M, N], may alias out
   int M, N, K;
   int ks;             // K is split over `ks` warps of a CTA (1, 2, 4 or 8) so that small N still fills the GPU
+  PrefetchArgs pf;    // weights of later launches to pull into L2
 };
 
 template <class T>
@@ -130,6 +154,7 @@ __global__ void __launch_bounds__(256) gemv_fused_kernel(GemvArgs a) {
   constexpr int VEC = 16 / sizeof(T);
   const int K = a.K;
   const T* xin = (const T*)a.x;
+  l2_prefetch_slices(a.pf);
   pdl_launch_dependents();
   pdl_wait();
 
@@ -331,6 +356,7 @@ struct AttnArgs {
   const int* ctx_len;                     // positions in the cache before this step
   int nh, nkv, P;
   float scale;                            // T(sqrt(HD)) widened
+  PrefetchArgs pf;                        // weights of later launches to pull into L2
 };
 template <class T, int HD>
 __global__ void __launch_bounds__(256) attn_decode_kernel(AttnArgs a, unsigned* err) {
@@ -346,6 +372,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnArgs a, unsigned* 
   constexpr int half = HD / 2;
   const int h = blockIdx.x, b = blockIdx.y;
   const int rep = a.nh / a.nkv, kvh = h / rep;
+  l2_prefetch_slices(a.pf);
   pdl_launch_dependents();
   pdl_wait();
   const int pos = *a.ctx_len;          // the new token's position

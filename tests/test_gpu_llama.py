@@ -163,3 +163,43 @@ def test_runner_refuses_bad_use(gpu):
         r.forward(bad)                       # token id outside the vocabulary: reported, not trapped
     r.reset(1)
     assert r.forward(ids[:, :8]).shape == (1,)
+
+
+def test_persistent_decode_kernel_matches_the_multi_kernel_plan(gpu):
+    """With CATGRAD_B200_MEGA set at creation, batch <= 4 decode steps run as one persistent kernel instead of the
+    graph of per-sub-graph kernels.  Same rounding points, different summation order: logits agree to
+    bf16 resolution (teacher-forced so that one flipped argmax cannot compound), and the KV caches they build are
+    interchangeable."""
+    import os
+    cfg, wb, ids = small_bf16_model()
+    pg = cb.upload_weights(gpu, wb, Dtype.BF16)
+    os.environ["CATGRAD_B200_MEGA"] = "1"
+    try:
+        mega = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=2, max_positions=64)
+    finally:
+        del os.environ["CATGRAD_B200_MEGA"]
+    plain = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=2, max_positions=64)
+    mega.reset(2)
+    plain.reset(2)
+    ta = mega.forward(ids)
+    tb = plain.forward(ids)
+    np.testing.assert_array_equal(ta, tb)           # the prefill is the same code in both
+    tok = ta
+    for _ in range(8):
+        ta = mega.forward(tok.reshape(2, 1))
+        tb = plain.forward(tok.reshape(2, 1))
+        la, lb = mega.last_logits(), plain.last_logits()
+        assert np.abs(la - lb).max() <= ABS_BF16
+        tok = tb
+    # on-device loop of the persistent kernel == stepping it from the host
+    mega.reset(2)
+    first = mega.forward(ids)
+    out = mega.decode(6)
+    mega.reset(2)
+    t = mega.forward(ids)
+    cols = []
+    for _ in range(6):
+        t = mega.forward(t.reshape(2, 1))
+        cols.append(t)
+    np.testing.assert_array_equal(out, np.stack(cols, 1))
+    assert mega.launch_count < plain.launch_count   # one launch per decode step
