@@ -189,13 +189,84 @@ def cpu_baseline_sample(cfg, weights_f32, prompt_len=8, steps=2):
             "prefill_tok_s": prompt_len / times[0]}
 
 
+def timed_op(be, fn, iters=10, flush_bytes=256 << 20):
+    """Median CUDA-event time of fn() over `iters` runs, L2 flushed (256 MiB written) before each."""
+    for _ in range(3):
+        fn()
+    ms = []
+    for _ in range(iters):
+        be._ns.flush_l2(be._ctx, flush_bytes)
+        be._ns.event_record(be._ctx, 10)
+        out = fn()
+        be._ns.event_record(be._ctx, 11)
+        be.synchronize()
+        ms.append(event_ms(be, 10, 11))
+        del out
+    return float(np.median(ms))
+
+
+def run_op_sweep(be):
+    """Baseline config 2: op-level sweep on random tensors (seed 2), f32 and bf16, through the Backend entry
+    points.  Bytes are the algorithmic ones: inputs read once + output written once; a broadcast operand counts
+    its source only."""
+    rng = np.random.default_rng(2)
+    hbm, tflops_peak, _ = measured_peaks()
+    rows = []
+    x_np = rng.uniform(-4, 4, (4096, 8192)).astype(np.float32)
+    v_np = rng.uniform(-4, 4, (8192,)).astype(np.float32)
+    r_np = rng.uniform(-4, 4, (8192, 4096)).astype(np.float32)
+    table_np = rng.standard_normal((32000, 2048)).astype(np.float32)
+    idx_np = rng.integers(0, 32000, 4096, dtype=np.uint32)
+    am_np = rng.standard_normal((64, 32000)).astype(np.float32)
+    a_np = rng.standard_normal((16, 1024, 1024)).astype(np.float32)
+    b_np = rng.standard_normal((16, 1024, 1024)).astype(np.float32)
+    for dt, es, name in ((cb.Dtype.F32, 4, "f32"), (cb.Dtype.BF16, 2, "bf16")):
+        x, v = be.from_numpy(x_np, dt), be.from_numpy(v_np, dt)
+        vb = be.broadcast(v, x.shape)                      # explicit Broadcast: the trait never broadcasts implicitly
+        n = x_np.size
+
+        def add_row(op, ms, nbytes, flops=None):
+            row = {"op": op, "dtype": name, "ms": ms, "GB/s": nbytes / ms / 1e6, "frac_hbm_measured": nbytes / ms / 1e6 / hbm}
+            if flops:
+                row["TFLOP/s"] = flops / ms / 1e9
+                if name == "bf16":
+                    row["frac_bf16_tensor_measured"] = flops / ms / 1e9 / tflops_peak
+            rows.append(row)
+
+        add_row("exp [4096,8192]", timed_op(be, lambda: be.exp(x)), 2 * n * es)
+        for op in ("add", "mul", "div"):
+            add_row(f"{op} [4096,8192] x row vector", timed_op(be, lambda: getattr(be, op)(x, vb)), 2 * n * es + 8192 * es)
+        r = be.from_numpy(r_np, dt)
+        add_row("sum [8192,4096]", timed_op(be, lambda: be.sum(r)), (r_np.size + 8192) * es)
+        add_row("max [8192,4096]", timed_op(be, lambda: be.max(r)), (r_np.size + 8192) * es)
+
+        def softmax_graph():
+            xf = be.cast(r, cb.Dtype.F32)
+            m = be.max(xf)
+            e = be.exp(be.sub(xf, be.broadcast(m, xf.shape)))
+            s = be.sum(e)
+            return be.cast(be.div(e, be.broadcast(s, xf.shape)), dt)
+        add_row("softmax [8192,4096] (nn::softmax op graph)", timed_op(be, softmax_graph), 2 * r_np.size * es)
+        a, b = be.from_numpy(a_np, dt), be.from_numpy(b_np, dt)
+        add_row("matmul [16,1024,1024]x[16,1024,1024]", timed_op(be, lambda: be.matmul(a, b)), 3 * a_np.size * es,
+                flops=2 * 16 * 1024 ** 3)
+        bt = be.transpose(be.from_numpy(np.ascontiguousarray(b_np.transpose(0, 2, 1)), dt), 1, 2)
+        add_row("matmul [16,1024,1024]x[16,1024,1024], right operand stored K-contiguous",
+                timed_op(be, lambda: be.matmul(a, bt)), 3 * a_np.size * es, flops=2 * 16 * 1024 ** 3)
+        table, idx = be.from_numpy(table_np, dt), be.from_numpy(idx_np)
+        add_row("index 4096 rows of [32000,2048]", timed_op(be, lambda: be.index(table, 0, idx)), 2 * 4096 * 2048 * es + 16384)
+        am = be.from_numpy(am_np, dt)
+        add_row("argmax [64,32000]", timed_op(be, lambda: be.argmax(am)), am_np.size * es)
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="auto", choices=["auto", "c3", "c4", "tiny"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "c3", "c4", "tiny", "sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-c4", action="store_true", help="N=1 only: do not time the batch-sharded workload as well")
     args = ap.parse_args()
@@ -206,6 +277,15 @@ def main():
     cfg = cb.TINY if args.workload == "tiny" else cb.LLAMA_1B
     model_name = "tiny-llama" if args.workload == "tiny" else "Llama-3.2-1B shape"
 
+    if args.workload == "sweep":
+        # baseline config 2 (op-level sweep); not the headline metric, printed as its own JSON line
+        if rank == 0:
+            be = cb.Backend(local_rank)
+            hbm, tfl, src = measured_peaks()
+            print(json.dumps({"metric": "op sweep", "unit": "GB/s", "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src},
+                              "timing": "median of 10 CUDA-event timings, 256 MiB written between runs to evict L2",
+                              "ops": run_op_sweep(be)}))
+        return
     if args.impl == "reference":
         if rank != 0:
             return
@@ -223,6 +303,7 @@ def main():
 
     dist = None
     if world > 1:
+        os.environ["NCCL_DEBUG"] = os.environ.get("NCCL_DEBUG_FOR_BENCH", "WARN")   # keep stdout to the one JSON line
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)

@@ -395,8 +395,12 @@ Tensor CudaBackend::matmul(const Tensor& a, const Tensor& b) {
   }
   CG_CHECK(batch <= 65535, ERR_INVALID_ARG, "matmul: more than 65535 batch entries");
   int64_t sam = a.strides[r - 2], sak = a.strides[r - 1], sbk = b.strides[r - 2], sbn = b.strides[r - 1];
+  // bf16 products with K-contiguous A go to the tensor cores; the right operand may be K-contiguous (x @ W^T) or
+  // N-contiguous (the trait's row-major [.., K, N])
+  const bool b_n_contig = sbk != 1 && sbn == 1;
   if (a.dt == Dtype::BF16 && cgk::tcgen05_gemm_applicable(bt, batch, a.raw(), b.raw(), M, N, K, sam, sak, sbk, sbn) &&
-      cgk::launch_tcgen05_gemm(bt, batch, a.raw(), b.raw(), t.raw(), M, N, K, sam, sbn, dev_words_, sm_count_, stream_)) {
+      cgk::launch_tcgen05_gemm(bt, batch, a.raw(), b.raw(), t.raw(), M, N, K, sam, b_n_contig ? sbk : sbn, dev_words_,
+                               sm_count_, stream_, b_n_contig)) {
     check_launch("matmul(tcgen05)");
     return t;
   }

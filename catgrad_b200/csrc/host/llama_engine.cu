@@ -61,7 +61,7 @@ struct cg_llama {
   bool mega_enabled = false;
   unsigned long long bar_base = 0;
   int mega_grid = 0;
-  bool use_pdl = false;       // programmatic dependent launch between the kernels of a step (opt-in)
+  bool use_pdl = true;        // programmatic dependent launch between the kernels of a step
   bool l2_prefetch = false;   // decode kernels pull the weights of later launches into L2 (opt-in)
   int64_t out_cap_steps = 0;
   // activation buffers sized for `cap_tokens` tokens
@@ -123,7 +123,7 @@ struct Plan {
   int ks_for(int n_pairs, int K) const {
     int nvec = K / (int)(16 / sizeof(T));
     int ks = 1;
-    while (ks < 8 && (long long)n_pairs * ks < (long long)sm * 16 && nvec / (ks * 2) >= 64) ks *= 2;
+    while (ks < 8 && (long long)n_pairs * ks < (long long)sm * 16 && nvec / (ks * 2) >= 64) ks *= 2;  // 16 warps per SM
     return ks;
   }
 
@@ -139,7 +139,7 @@ struct Plan {
     int pairs = EPI == cgk::EPI_SILU_MUL ? a.N : (a.N + 1) / 2;
     a.ks = ks_for(pairs, a.K);
     int ppc = 8 / a.ks;
-    int ctas_per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
+    int ctas_per_sm = smem > 100 * 1024 ? 1 : 2;  // 128 registers x 256 threads: two CTAs per SM
     int grid = std::min((pairs + ppc - 1) / ppc, sm * ctas_per_sm);
     launch(kern, dim3(grid), dim3(256), smem, a);
     launched("gemv");
@@ -645,8 +645,8 @@ int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const c
   m->logits = be.zeros({m->max_batch, V}, m->dt);
   m->argmax_chunks = (int)((V + cgk::ARGMAX_CHUNK - 1) / cgk::ARGMAX_CHUNK);
   m->partials = be.zeros({m->max_batch * m->argmax_chunks * 2}, Dtype::U32);
-  // measured slower than plain graph edges on B200 for this chain (waiting CTAs hold SM resources): opt-in
-  m->use_pdl = std::getenv("CATGRAD_B200_PDL") != nullptr;
+  // programmatic dependent launch: the next kernel starts streaming its first weight rows while this one drains
+  m->use_pdl = std::getenv("CATGRAD_B200_NO_PDL") == nullptr;
   // measured neutral-to-slower on B200 for this chain (the launches are latency-bound, not HBM-bound): opt-in
   m->l2_prefetch = std::getenv("CATGRAD_B200_L2_PREFETCH") != nullptr;
   m->out_cap_steps = 0;

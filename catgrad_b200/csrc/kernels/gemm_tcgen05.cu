@@ -8,6 +8,8 @@
 // Structure of one CTA (192 threads), one 128 x BN output tile:
 //   warp 0, one lane : TMA producer.  cp.async.bulk.tensor loads 128x64 (A) and BNx64 (B) bf16 boxes with the
 //                      128-byte swizzle into a ring of shared-memory stages; completion lands on an mbarrier.
+//                      BN is 16..256: wide tiles for large products, narrow ones so that a product with a
+//                      single row tile (a decode batch) still spreads the weight stream over all SMs.
 //   warp 1, one lane : issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) from shared-memory descriptors into a
 //                      TMEM accumulator; tcgen05.commit releases each stage and finally signals the epilogue.
 //                      Warp 1 also allocates/frees the TMEM columns.
@@ -99,9 +101,23 @@ __device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
   return d;
 }
 
+// Same for an MN-major operand tile (the row-major [K, N] right operand of the trait's matmul: N contiguous).
+// TMA writes it as blocks of 64 columns x BK rows (rows of 128 bytes, swizzled); the next 64-column block starts
+// BK * 128 bytes later (leading byte offset), groups of 8 K-rows are 1024 bytes apart (stride byte offset).
+__device__ __forceinline__ uint64_t make_smem_desc_mn(const void* tile) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
+  d |= (uint64_t)((BK * 128) >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16: D = f32, A = B = bf16, both K-major, shape M x N.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
 }
 
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
@@ -135,17 +151,19 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 template <int BN>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;  // BN >= 16: a multiple of 1024, so every tile base stays 1024-aligned
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 };
 
-// grid: (ceil(N/BN), ceil(M/BM), batch).  BATCHED selects 3-D tensor maps {K, rows, batch}.
-template <int BN, int STAGES, bool BATCHED>
+// grid: (ceil(N/BN), ceil(M/BM), batch).  BATCHED selects 3-D tensor maps {K, rows, batch}.  B_MN: the right
+// operand is stored [K, N] with N contiguous (tensor map dims {N, K}); otherwise [N, K] with K contiguous.
+template <int BN, int STAGES, bool BATCHED, bool B_MN>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                                            const __grid_constant__ CUtensorMap tmB,
                                                            __nv_bfloat16* __restrict__ C, int M, int N, int K,
                                                            long long c_batch_stride, unsigned* err) {
   using L = SmemLayout<BN>;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // allocations are powers of two >= 32 columns
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
@@ -169,7 +187,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   tc_fence_before();
@@ -187,12 +205,18 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
       unsigned char* a_dst = smem + s * L::STAGE_BYTES;
       unsigned char* b_dst = a_dst + L::A_BYTES;
       mbar_expect_tx(&full[s], L::STAGE_BYTES);
-      if (BATCHED) {
-        tma_load_3d(a_dst, &tmA, &full[s], k * BK, m0, bz);
-        tma_load_3d(b_dst, &tmB, &full[s], k * BK, n0, bz);
+      if (BATCHED) tma_load_3d(a_dst, &tmA, &full[s], k * BK, m0, bz);
+      else tma_load_2d(a_dst, &tmA, &full[s], k * BK, m0);
+      if (B_MN) {
+        // one 64-column x BK-row box per 64 columns of the tile
+#pragma unroll
+        for (int nb = 0; nb < BN / 64; ++nb) {
+          if (BATCHED) tma_load_3d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, k * BK, bz);
+          else tma_load_2d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, k * BK);
+        }
       } else {
-        tma_load_2d(a_dst, &tmA, &full[s], k * BK, m0);
-        tma_load_2d(b_dst, &tmB, &full[s], k * BK, n0);
+        if (BATCHED) tma_load_3d(b_dst, &tmB, &full[s], k * BK, n0, bz);
+        else tma_load_2d(b_dst, &tmB, &full[s], k * BK, n0);
       }
       issued = k + 1;
     }
@@ -206,7 +230,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
-    constexpr uint32_t idesc = make_idesc(BM, BN);
+    constexpr uint32_t idesc = make_idesc(BM, BN, B_MN);
     bool ok = true;
     for (int k = 0; k < num_k && ok; ++k) {
       const int s = k % STAGES;
@@ -215,11 +239,13 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
       tc_fence_after();
       const unsigned char* a_tile = smem + s * L::STAGE_BYTES;
       const uint64_t adesc = make_smem_desc(a_tile);
-      const uint64_t bdesc = make_smem_desc(a_tile + L::A_BYTES);
+      const uint64_t bdesc = B_MN ? make_smem_desc_mn(a_tile + L::A_BYTES) : make_smem_desc(a_tile + L::A_BYTES);
 #pragma unroll
       for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-        // advancing 16 bf16 = 32 bytes along K inside the swizzle row: +2 in the 16-byte address field
-        umma_bf16(tmem_base, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (k | kk) != 0 ? 1u : 0u);
+        // K-major: 16 bf16 = 32 bytes along K inside the swizzle row: +2 in the 16-byte address field.
+        // MN-major: 16 K-rows of 128 bytes: +128.
+        const uint64_t bstep = B_MN ? (uint64_t)(kk * (UMMA_K * 128 / 16)) : (uint64_t)(kk * 2);
+        umma_bf16(tmem_base, adesc + (uint64_t)(kk * 2), bdesc + bstep, idesc, (k | kk) != 0 ? 1u : 0u);
       }
       umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
     }
@@ -242,7 +268,8 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
         tmem_ld_wait();
         if (row < M) {
           const int col = n0 + c0;
-          if (vec_ok && col + 32 <= N) {
+          const int width = BN - c0 < 32 ? BN - c0 : 32;  // columns of this tile in the 32 just loaded
+          if (width == 32 && vec_ok && col + 32 <= N) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint32_t w[4];
@@ -254,7 +281,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
               *reinterpret_cast<uint4*>(crow + col + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
           } else {
-            for (int j = 0; j < 32; ++j)
+            for (int j = 0; j < width; ++j)
               if (col + j < N) crow[col + j] = __float2bfloat16_rn(__uint_as_float(r[j]));
           }
         }
@@ -265,7 +292,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
   }
 }
 
@@ -304,18 +331,44 @@ bool make_map(CUtensorMap* map, const void* base, long long K, long long rows, l
   return r == CUDA_SUCCESS;
 }
 
+// [K, N] matrix with N contiguous and a row pitch of ld elements: tensor map dims {N, K}, boxes of 64 x BK.
+bool make_map_mn(CUtensorMap* map, const void* base, long long K, long long N, long long ld, long long batch,
+                 long long batch_stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)K, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)batch_stride * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)BK, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  int rank = batch > 1 ? 3 : 2;
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 struct Problem {
   bool ok = false;
+  bool b_mn = false;               // right operand stored [K, N], N contiguous
   long long M, batch, a_bs, b_bs;  // after folding a shared-B batch into M
 };
 
 Problem analyse(const View4& bt, long long batch, const void* A, const void* B, long long M, long long N, long long K,
                 long long sam, long long sak, long long sbk, long long sbn) {
   Problem p;
-  if (sak != 1 || sbk != 1) return p;
-  if (K < 16 || K % 8 != 0 || sam % 8 != 0 || sbn % 8 != 0) return p;
+  if (sak != 1) return p;
+  if (sbk == 1) {
+    if (sbn % 8 != 0 || sbn < K) return p;
+  } else if (sbn == 1) {
+    // MN-major right operand: 64-column boxes, so keep it to products with at least one full box
+    if (sbk % 8 != 0 || sbk < N || N < 64 || N % 8 != 0) return p;
+    p.b_mn = true;
+  } else {
+    return p;
+  }
+  if (K < 16 || K % 8 != 0 || sam % 8 != 0) return p;
   if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return p;
-  if (sam < K || sbn < K) return p;
+  if (sam < K) return p;
   if (N < 16) return p;
   p.M = M;
   p.batch = 1;
@@ -338,12 +391,12 @@ Problem analyse(const View4& bt, long long batch, const void* A, const void* B, 
   return p;
 }
 
-template <int BN, int STAGES, bool BATCHED>
+template <int BN, int STAGES, bool BATCHED, bool B_MN = false>
 void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K,
               long long batch, unsigned* err, cudaStream_t st) {
   using L = SmemLayout<BN>;
   size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 /* alignment slack */ + (2 * STAGES + 1) * 8 + 16;
-  auto kern = gemm_tcgen05_kernel<BN, STAGES, BATCHED>;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, BATCHED, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -363,21 +416,38 @@ bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, co
 
 bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
                          long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
-                         cudaStream_t st) {
-  Problem p = analyse(bt, batch, A, B, M, N, K, lda, 1, 1, ldb);
+                         cudaStream_t st, bool b_n_contiguous) {
+  Problem p = b_n_contiguous ? analyse(bt, batch, A, B, M, N, K, lda, 1, ldb, 1) : analyse(bt, batch, A, B, M, N, K, lda, 1, 1, ldb);
   if (!p.ok) return false;
   CUtensorMap ta, tb;
-  // 128x256 tiles only when 128x128 tiles would already give every SM two CTAs
-  const long long tiles128 = ((p.M + BM - 1) / BM) * ((N + 127) / 128) * p.batch;
-  const bool wide = N >= 256 && tiles128 >= 2ll * sm_count;
-  const int bn = wide ? 256 : 128;
+  // Tile width: as wide as possible while the grid still covers every SM about twice; narrow tiles (down to 16
+  // columns) keep all SMs streaming W when M fits one row tile (decode of a batch).
+  const long long mtiles = ((p.M + BM - 1) / BM) * p.batch;
+  const bool streaming = mtiles <= 2;                 // one or two row tiles: a pass over W, HBM-bound
+  const int min_bn = streaming ? 16 : 64;             // compute-bound products keep the MMA reasonably wide
+  const long long want = streaming ? sm_count : (3ll * sm_count) / 4;
+  int bn = 256;
+  while (bn > min_bn && mtiles * ((N + bn - 1) / bn) < want) bn >>= 1;
+  if (p.b_mn) {
+    if (bn < 64) bn = 64;
+    if (!make_map(&ta, A, K, p.M, lda, p.batch, p.a_bs, BM) || !make_map_mn(&tb, B, K, N, ldb, p.batch, p.b_bs)) return false;
+    const bool b3 = p.batch > 1;
+    switch (bn) {
+      case 256: b3 ? launch_t<256, 4, true, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<256, 4, false, true>(ta, tb, C, p.M, N, K, 1, err, st); break;
+      case 128: b3 ? launch_t<128, 6, true, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<128, 6, false, true>(ta, tb, C, p.M, N, K, 1, err, st); break;
+      default: b3 ? launch_t<64, 8, true, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<64, 8, false, true>(ta, tb, C, p.M, N, K, 1, err, st); break;
+    }
+    return true;
+  }
+  if (bn > N) bn = N >= 256 ? 256 : (N >= 128 ? 128 : (N >= 64 ? 64 : (N >= 32 ? 32 : 16)));
   if (!make_map(&ta, A, K, p.M, lda, p.batch, p.a_bs, BM) || !make_map(&tb, B, K, N, ldb, p.batch, p.b_bs, bn)) return false;
-  if (p.batch > 1) {
-    if (wide) launch_t<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, st);
-    else launch_t<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, st);
-  } else {
-    if (wide) launch_t<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, st);
-    else launch_t<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, st);
+  const bool bt3 = p.batch > 1;
+  switch (bn) {
+    case 256: bt3 ? launch_t<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
+    case 128: bt3 ? launch_t<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
+    case 64: bt3 ? launch_t<64, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<64, 8, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
+    case 32: bt3 ? launch_t<32, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<32, 8, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
+    default: bt3 ? launch_t<16, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<16, 8, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
   }
   return true;
 }

@@ -3,8 +3,9 @@
 #include "common.cuh"
 
 namespace cgk {
-// True when the product can run on the tensor-core kernel: bf16, A rows K-contiguous, B K-contiguous
-// ("x @ W^T" layout), 16-byte aligned bases and row pitches, M >= 128.
+// True when the product can run on the tensor-core kernel: bf16, A rows K-contiguous, B either K-contiguous
+// ("x @ W^T" layout, sbk == 1) or N-contiguous (a row-major [K, N] right operand, sbn == 1), 16-byte aligned
+// bases and row pitches, more than 16 rows in total.
 bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, const void* B, long long M, long long N,
                              long long K, long long sam, long long sak, long long sbk, long long sbn);
 // C[batch, M, N] (contiguous bf16) = A x B^T-layout; f32 accumulation in TMEM, one rounding to bf16.
@@ -12,5 +13,5 @@ bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, co
 // Returns false (nothing launched) if the tensor maps cannot be made; the caller then uses the SIMT kernel.
 bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
                          long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
-                         cudaStream_t st);
+                         cudaStream_t st, bool b_n_contiguous = false);
 }  // namespace cgk

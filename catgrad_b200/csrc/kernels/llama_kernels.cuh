@@ -146,7 +146,7 @@ __device__ __forceinline__ const T* gemv_row(const GemvArgs& a, int n) {
 // EPI_SILU_MUL); `ks` consecutive warps share one pair, each streaming a 1/ks slice of K with 16-byte loads;
 // partial sums meet in shared memory in a fixed order.  The M input rows sit in shared memory as T.
 template <class T, int MT, int PRO, int EPI>
-__global__ void __launch_bounds__(256) gemv_fused_kernel(GemvArgs a) {
+__global__ void __launch_bounds__(256, 2) gemv_fused_kernel(GemvArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* xs = reinterpret_cast<T*>(smem_raw);  // [MT][K]
   __shared__ float scratch[8];
@@ -155,10 +155,84 @@ __global__ void __launch_bounds__(256) gemv_fused_kernel(GemvArgs a) {
   const int K = a.K;
   const T* xin = (const T*)a.x;
   l2_prefetch_slices(a.pf);
-  pdl_launch_dependents();
-  pdl_wait();
 
-  if (PRO == PRO_NORM) {
+  // ---- this warp's first work item: start streaming its weights before the input vector is even ready ----
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ks = a.ks, ppc = 8 / ks;            // pairs per CTA per iteration
+  const int split = warp % ks, slot = warp / ks;
+  const int n_pairs = EPI == EPI_SILU_MUL ? a.N : (a.N + 1) / 2;
+  const int nvec = K / VEC;
+  const int v_lo = (int)((long long)nvec * split / ks), v_hi = (int)((long long)nvec * (split + 1) / ks);
+  const int iters = (n_pairs + gridDim.x * ppc - 1) / (gridDim.x * ppc);
+  constexpr int PRE = 4;
+  VecT<T, VEC> pre0[PRE], pre1[PRE];
+  {
+    const int p = blockIdx.x * ppc + slot;
+    if (p < n_pairs) {
+      const T *w0, *w1;
+      if (EPI == EPI_SILU_MUL) {
+        w0 = (const T*)a.w[0] + (long long)p * K;
+        w1 = (const T*)a.w[1] + (long long)p * K;
+      } else {
+        w0 = gemv_row<T>(a, 2 * p);
+        w1 = gemv_row<T>(a, 2 * p + 1 < a.N ? 2 * p + 1 : 2 * p);
+      }
+#pragma unroll
+      for (int j = 0; j < PRE; ++j) {
+        const int v = v_lo + lane + 32 * j;
+        if (v < v_hi) {
+          pre0[j] = *reinterpret_cast<const VecT<T, VEC>*>(w0 + v * VEC);
+          pre1[j] = *reinterpret_cast<const VecT<T, VEC>*>(w1 + v * VEC);
+        }
+      }
+    }
+  }
+
+  // weights do not depend on the previous launch; everything below does
+  pdl_wait();
+  pdl_launch_dependents();
+
+  // ---- input rows into shared memory (as T); PRO_NORM applies RMSNorm (helpers/tensors.rs:82-111) ----
+  if (PRO == PRO_NORM && nvec <= 4 * 256) {
+    // one pass: every thread keeps its 16-byte groups of x and of the gain in registers across the reduction
+    const T* g = (const T*)a.gain;
+#pragma unroll 1
+    for (int m = 0; m < MT; ++m) {
+      VecT<T, VEC> xv[4], gv[4];
+      float ss = 0.f;
+      if (m < a.M) {
+        const T* x = xin + m * a.x_row_stride;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int v = threadIdx.x + 256 * j;
+          if (v < nvec) {
+            xv[j] = *reinterpret_cast<const VecT<T, VEC>*>(x + v * VEC);
+            gv[j] = *reinterpret_cast<const VecT<T, VEC>*>(g + v * VEC);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+              float f = Elem<T>::load(xv[j].v[i]);
+              ss += f * f;
+            }
+          }
+        }
+      }
+      ss = block_sum_256(ss, scratch);
+      const float rms = sqrtf(ss / (float)K + a.eps);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int v = threadIdx.x + 256 * j;
+        if (v < nvec) {
+          VecT<T, VEC> o;
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            float nrm = m < a.M ? rt<T>(Elem<T>::load(xv[j].v[i]) / rms) : 0.f;
+            o.v[i] = Elem<T>::store(m < a.M ? nrm * Elem<T>::load(gv[j].v[i]) : 0.f);
+          }
+          *reinterpret_cast<VecT<T, VEC>*>(xs + m * K + v * VEC) = o;
+        }
+      }
+    }
+  } else if (PRO == PRO_NORM) {
     const T* g = (const T*)a.gain;
     for (int m = 0; m < MT; ++m) {
       if (m < a.M) {
@@ -189,13 +263,6 @@ __global__ void __launch_bounds__(256) gemv_fused_kernel(GemvArgs a) {
   }
   __syncthreads();
 
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int ks = a.ks, ppc = 8 / ks;            // pairs per CTA per iteration
-  const int split = warp % ks, slot = warp / ks;
-  const int n_pairs = EPI == EPI_SILU_MUL ? a.N : (a.N + 1) / 2;
-  const int nvec = K / VEC;
-  const int v_lo = (int)((long long)nvec * split / ks), v_hi = (int)((long long)nvec * (split + 1) / ks);
-  const int iters = (n_pairs + gridDim.x * ppc - 1) / (gridDim.x * ppc);
   for (int it = 0; it < iters; ++it) {
     const int p = (it * gridDim.x + blockIdx.x) * ppc + slot;
     const bool valid = p < n_pairs;
@@ -215,8 +282,29 @@ __global__ void __launch_bounds__(256) gemv_fused_kernel(GemvArgs a) {
         w0 = gemv_row<T>(a, n0);
         w1 = gemv_row<T>(a, n1);
       }
-#pragma unroll 4
-      for (int v = v_lo + lane; v < v_hi; v += 32) {
+      int vstart = v_lo + lane;
+      if (it == 0) {
+        // the vectors fetched before the input was ready
+#pragma unroll
+        for (int j = 0; j < PRE; ++j) {
+          const int v = v_lo + lane + 32 * j;
+          if (v < v_hi) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+              VecT<T, VEC> xv = *reinterpret_cast<const VecT<T, VEC>*>(xs + m * K + v * VEC);
+#pragma unroll
+              for (int i = 0; i < VEC; ++i) {
+                float xf = Elem<T>::load(xv.v[i]);
+                acc0[m] = fmaf(xf, Elem<T>::load(pre0[j].v[i]), acc0[m]);
+                acc1[m] = fmaf(xf, Elem<T>::load(pre1[j].v[i]), acc1[m]);
+              }
+            }
+          }
+        }
+        vstart += 32 * PRE;
+      }
+#pragma unroll 8
+      for (int v = vstart; v < v_hi; v += 32) {
         VecT<T, VEC> a0 = *reinterpret_cast<const VecT<T, VEC>*>(w0 + v * VEC);
         VecT<T, VEC> a1 = *reinterpret_cast<const VecT<T, VEC>*>(w1 + v * VEC);
         float f0[VEC], f1[VEC];
@@ -416,8 +504,8 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnArgs a, unsigned* 
   float qf[VEC];
 #pragma unroll
   for (int i = 0; i < VEC; ++i) qf[i] = q_s[sub * VEC + i];
-  // scores over the cached keys: 4 independent 16-byte loads in flight per lane
-  constexpr int UN = 4;
+  // scores over the cached keys: 8 independent 16-byte loads in flight per lane
+  constexpr int UN = 8;
   for (int t0 = warp * KPW * UN; t0 < pos; t0 += 8 * KPW * UN) {
     VecT<T, VEC> kv[UN];
 #pragma unroll

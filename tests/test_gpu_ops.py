@@ -318,7 +318,8 @@ def _bf16_round(a):
 
 
 @pytest.mark.parametrize("mnk", [(128, 128, 64), (300, 200, 264), (17, 2048, 512), (512, 384, 2048), (1000, 136, 72),
-                                 (129, 257, 1032), (64, 16, 16)], ids=str)
+                                 (129, 257, 1032), (64, 16, 16), (128, 4096, 256), (100, 8200, 128), (32, 40, 64),
+                                 (2048, 2048, 512)], ids=str)
 def test_tensor_core_gemm_against_f32_path(gpu, mnk):
     """bf16 `x @ W^T` products (both operands K-contiguous) run on the tcgen05 kernel; the same bf16-rounded
     operands multiplied by the exact-f32 SIMT kernel give the reference.  Only the accumulation order differs, so
@@ -355,3 +356,29 @@ def test_tensor_core_gemm_batched_and_shared_weight(oracle, gpu):
     np.testing.assert_allclose(res[1], res[0], rtol=2e-2, atol=6e-2)
     ref64 = np.einsum("bmk,bnk->bmn", q.astype(np.float64), kk.astype(np.float64))
     np.testing.assert_allclose(res[1], ref64, rtol=2e-2, atol=8e-2)
+
+
+@pytest.mark.parametrize("mnk", [(128, 128, 64), (300, 200, 264), (512, 384, 2048), (129, 264, 1032), (1024, 64, 128),
+                                 (40, 4096, 256)], ids=str)
+def test_tensor_core_gemm_row_major_right_operand(gpu, mnk):
+    """The trait's own layout: lhs [M,K] @ rhs [K,N], both row-major (rhs is N-contiguous, an MN-major tensor-core
+    operand).  Reference: the exact-f32 kernel on the same bf16-rounded values."""
+    m, n, k = mnk
+    rng = np.random.default_rng(m + 5 * n + 11 * k)
+    x = _bf16_round(rng.standard_normal((m, k)).astype(np.float32))
+    w = _bf16_round((rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32))
+    got = gpu.to_f32(gpu.matmul(gpu.from_numpy(x, Dtype.BF16), gpu.from_numpy(w, Dtype.BF16)))
+    ref = gpu.to_numpy(gpu.matmul(gpu.from_numpy(x), gpu.from_numpy(w)))
+    np.testing.assert_allclose(got, ref, rtol=1e-2, atol=1e-2)
+    assert helpers.rel_err(got, ref) < 6e-3
+    ref64 = x[-8:].astype(np.float64) @ w[:, :8].astype(np.float64)
+    np.testing.assert_allclose(got[-8:, :8], ref64, rtol=1e-2, atol=1e-2)
+
+
+def test_tensor_core_gemm_row_major_batched(gpu):
+    rng = np.random.default_rng(33)
+    a = _bf16_round(rng.standard_normal((5, 160, 96)).astype(np.float32))
+    b = _bf16_round((rng.standard_normal((5, 96, 192)) / 10).astype(np.float32))
+    got = gpu.to_f32(gpu.matmul(gpu.from_numpy(a, Dtype.BF16), gpu.from_numpy(b, Dtype.BF16)))
+    ref64 = np.einsum("bmk,bkn->bmn", a.astype(np.float64), b.astype(np.float64))
+    np.testing.assert_allclose(got, ref64, rtol=2e-2, atol=3e-2)
