@@ -33,6 +33,8 @@ sys.path.insert(0, ROOT)
 import catgrad_b200 as cb  # noqa: E402
 
 HBM_NOMINAL_GBS = 8000.0
+# (8.44 + 67.18 + 33.62 + 12.66) MB x 16 layers + 525.3 MB lm_head, DRAM bytes measured by ncu per launch
+TRAFFIC_PER_STEP_B1 = int((8.44e6 + 67.18e6 + 33.62e6 + 12.66e6) * 16 + 525.3e6)
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -359,10 +361,17 @@ def main():
                 "steps": r["e2e_steps"], "how": "cg_llama_forward per token with host id buffers (copy in, step, copy out)"},
         "gpu_launches": r["launches"],
         "clocks": r["clocks"],
-        "roofline": {"bound": "hbm", "kernel": "decode step (gemv_fused_kernel streams the weights)",
+        "roofline": {"bound": "hbm",
+                     "kernel": "one decode step = its 65 gemv_fused_kernel launches (79 % of the device time, "
+                               "profiles/decode_step_llama1b_bf16_launch_list.md) + attention + greedy pick",
                      "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "peak_source": peak_src, "frac_of_8TBs_nominal": achieved / HBM_NOMINAL_GBS,
-                     "bytes_per_step": bytes_step, "traffic": None},
+                     "bytes_per_step": bytes_step,
+                     "how": "algorithmic bytes of a step (every weight once + KV cache read + new KV rows) / CUDA-event "
+                            "time of a step on the launching stream",
+                     # dram__bytes_read.sum + dram__bytes_write.sum of the gemv launches of one step, summed from the
+                     # ncu capture in profiles/gemv_fused_decode_llama1b_bf16.md (batch 1; weights only)
+                     "traffic": TRAFFIC_PER_STEP_B1 if (batch_total == 1 and workload == "c3") else None},
         "load_s": load_s,
     }
     if single and workload == "c3" and not args.skip_c4:
