@@ -350,6 +350,29 @@ struct Plan {
         a.cos_t = (const float*)m.cos_t.raw(); a.sin_t = (const float*)m.sin_t.raw();
         a.ctx_len = ctx_len; a.nh = (int)nh; a.nkv = (int)nkv; a.P = (int)m.P; a.scale = scale;
         constexpr int VEC = 16 / sizeof(T);
+        const int64_t rep = nh / nkv;
+        if (B * nh >= 4 * (int64_t)sm && rep <= 8) {
+          // many sequences: one warp per query head, one CTA per (kv head, sequence)
+          size_t smem = (size_t)rep * (m.P + 1) * 4 + (size_t)rep * hd * 4 + 2 * hd * sizeof(T);
+          dim3 grid((unsigned)nkv, (unsigned)B);
+          if (hd == 64) {
+            auto kern = cgk::attn_decode_warp_kernel<T, 64>;
+            static size_t smem_set = 0;
+            if (smem > 48 * 1024 && smem > smem_set) {
+              cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+              smem_set = smem;
+            }
+            launch(kern, grid, dim3((unsigned)(32 * rep)), smem, a, err);
+          } else {
+            auto kern = cgk::attn_decode_warp_kernel<T, 128>;
+            static size_t smem_set = 0;
+            if (smem > 48 * 1024 && smem > smem_set) {
+              cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+              smem_set = smem;
+            }
+            launch(kern, grid, dim3((unsigned)(32 * rep)), smem, a, err);
+          }
+        } else {
         size_t smem = (size_t)(m.P + 1) * 4 + (size_t)(256 / (hd / VEC)) * hd * 4;
         dim3 grid((unsigned)nh, (unsigned)B);
         if (hd == 64) {
@@ -368,6 +391,7 @@ struct Plan {
             smem_set = smem;
           }
           launch(kern, grid, dim3(256), smem, a, err);
+        }
         }
         launched("attn_decode");
       } else {

@@ -425,7 +425,9 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
   const long long mtiles = ((p.M + BM - 1) / BM) * p.batch;
   const bool streaming = mtiles <= 2;                 // one or two row tiles: a pass over W, HBM-bound
   const int min_bn = streaming ? 16 : 64;             // compute-bound products keep the MMA reasonably wide
-  const long long want = streaming ? sm_count : (3ll * sm_count) / 4;
+  // enough tiles to occupy ~60 % of the SMs, but do not cut tiles finer than that: a second wave of CTAs costs more
+  // than narrower tiles gain
+  const long long want = streaming ? (3ll * sm_count) / 5 : (3ll * sm_count) / 4;
   int bn = 256;
   while (bn > min_bn && mtiles * ((N + bn - 1) / bn) < want) bn >>= 1;
   if (p.b_mn) {
@@ -446,8 +448,8 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
     case 256: bt3 ? launch_t<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
     case 128: bt3 ? launch_t<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
     case 64: bt3 ? launch_t<64, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<64, 8, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
-    case 32: bt3 ? launch_t<32, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<32, 8, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
-    default: bt3 ? launch_t<16, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<16, 8, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
+    case 32: bt3 ? launch_t<32, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<32, 5, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
+    default: bt3 ? launch_t<16, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<16, 5, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
   }
   return true;
 }

@@ -584,6 +584,121 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(AttnArgs a, unsigned* 
   }
 }
 
+// ---- decode attention for many sequences: one warp per query head, one CTA per (kv head, sequence) ---------
+// Same sub-graph and rounding points as attn_decode_kernel; used when batch x heads is large enough to fill the
+// GPU with warps.  The `rep` query heads of a GQA group sit in one CTA, so each K/V row is fetched from L2 once
+// and served to the other heads by L1.  No block-wide reduction: scores, softmax and P.v of a head stay in its
+// warp (lane = key in the score pass, lane = slice of the head dimension in the P.v pass).
+template <class T, int HD>
+__global__ void __launch_bounds__(256) attn_decode_warp_kernel(AttnArgs a, unsigned* err) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int half = HD / 2;
+  constexpr int DPL = HD / 32;  // head-dim elements per lane in the P.v pass
+  const int rep = a.nh / a.nkv;
+  const int kvh = blockIdx.x, b = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = kvh * rep + warp;
+  // the new k row is read with 16-byte loads like a cache row, so it sits first (16-byte aligned)
+  T* k_new = reinterpret_cast<T*>(smem_raw);                          // [HD]
+  T* v_new = k_new + HD;                                              // [HD]
+  float* q_all = reinterpret_cast<float*>(v_new + HD);                // [rep][HD]
+  float* sc_all = q_all + (size_t)rep * HD;                           // [rep][P + 1]
+  float* sc = sc_all + (size_t)warp * (a.P + 1);
+  float* q_s = q_all + (size_t)warp * HD;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pos = *a.ctx_len;
+  if (pos >= a.P) {
+    if (threadIdx.x == 0) atomicOr(err, DEV_ERR_INDEX_OOB);
+    return;
+  }
+  const int total = pos + 1;
+  T* kc = (T*)a.kc + ((long long)b * a.nkv + kvh) * a.P * HD;
+  T* vc = (T*)a.vc + ((long long)b * a.nkv + kvh) * a.P * HD;
+  const float* ct = a.cos_t + (long long)pos * half;
+  const float* st = a.sin_t + (long long)pos * half;
+
+  // RoPE of this warp's q; warp 0 also rotates the new k row and copies the new v row
+  {
+    const T* qsrc = (const T*)a.q + (long long)b * a.q_row_stride + h * HD;
+    for (int i = lane; i < half; i += 32) {
+      float x1 = Elem<T>::load(qsrc[i]), x2 = Elem<T>::load(qsrc[i + half]);
+      float c = ct[i], sn = st[i];
+      q_s[i] = rt<T>(c * x1 + sn * (-x2));
+      q_s[i + half] = rt<T>(c * x2 + sn * x1);
+    }
+    if (warp == 0) {
+      const T* ksrc = (const T*)a.k + (long long)b * a.k_row_stride + kvh * HD;
+      const T* vsrc = (const T*)a.v + (long long)b * a.v_row_stride + kvh * HD;
+      for (int i = lane; i < half; i += 32) {
+        float x1 = Elem<T>::load(ksrc[i]), x2 = Elem<T>::load(ksrc[i + half]);
+        float c = ct[i], sn = st[i];
+        T o1 = Elem<T>::store(c * x1 + sn * (-x2)), o2 = Elem<T>::store(c * x2 + sn * x1);
+        k_new[i] = o1;
+        k_new[i + half] = o2;
+        kc[(long long)pos * HD + i] = o1;
+        kc[(long long)pos * HD + i + half] = o2;
+      }
+      for (int i = lane; i < HD; i += 32) {
+        T vv = vsrc[i];
+        v_new[i] = vv;
+        vc[(long long)pos * HD + i] = vv;
+      }
+    }
+  }
+  __syncthreads();
+
+  // scores: lane = key
+  float mx = -FLT_MAX;
+  for (int t = lane; t < total; t += 32) {
+    const T* krow = t == pos ? k_new : kc + (long long)t * HD;
+    float d = 0.f;
+#pragma unroll
+    for (int c = 0; c < HD / VEC; ++c) {
+      VecT<T, VEC> kv = *reinterpret_cast<const VecT<T, VEC>*>(krow + c * VEC);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) d = fmaf(q_s[c * VEC + i], Elem<T>::load(kv.v[i]), d);
+    }
+    float sres = rt<T>(rt<T>(d) / a.scale);
+    sc[t] = sres;
+    mx = fmaxf(mx, sres);
+  }
+  mx = warp_max(mx);  // `max` folds from f32::MIN (ndarray.rs:656-661): at least one key exists
+  float sum = 0.f;
+  for (int t = lane; t < total; t += 32) {
+    float e = expf(sc[t] - mx);
+    sc[t] = e;
+    sum += e;
+  }
+  sum = warp_sum(sum);
+  for (int t = lane; t < total; t += 32) sc[t] = rt<T>(sc[t] / sum);
+  __syncwarp();
+
+  // P.v: lane = DPL consecutive elements of the head dimension, keys in order
+  float acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+  const int d0 = lane * DPL;
+#pragma unroll 8
+  for (int t = 0; t < pos; ++t) {
+    const float p = sc[t];
+    const VecT<T, DPL> vv = *reinterpret_cast<const VecT<T, DPL>*>(vc + (long long)t * HD + d0);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p, Elem<T>::load(vv.v[i]), acc[i]);
+  }
+  {
+    const float p = sc[pos];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = fmaf(p, Elem<T>::load(v_new[d0 + i]), acc[i]);
+  }
+  // `out` is an allocator-aligned buffer whose rows are a multiple of HD elements; h * HD + d0 is a multiple of DPL
+  VecT<T, DPL> ov;
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) ov.v[i] = Elem<T>::store(acc[i]);
+  *reinterpret_cast<VecT<T, DPL>*>((T*)a.out + (long long)b * a.out_row_stride + h * HD + d0) = ov;
+}
+
 // ---- prefill: scale + causal mask + softmax over score rows (llama.rs:330-339) ------------------------
 // Row r = ((b*nh + h)*S + s) of scores [.., S, Tt] (T, in place): x = T(x / scale); x = T(x + mask) where the
 // mask is T(f32::MIN) for keys after position T0+s (in bf16 that is -inf) and -0.0 otherwise; softmax in f32.

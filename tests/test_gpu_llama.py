@@ -83,6 +83,48 @@ def test_fused_runner_batch_and_graph_replay_match_stepwise(gpu):
         np.testing.assert_array_equal(solo.generate(ids[b:b + 1], 12)[0], out[b])
 
 
+def test_many_sequences_use_the_warp_per_head_attention_and_match_solo_runs(gpu):
+    """With batch x heads above four CTAs per SM the decode step switches to the warp-per-head attention kernel
+    (one CTA per kv head and sequence).  Every sequence must still equal running it alone, which goes through the
+    CTA-per-head kernel: same ids, logits to f32 round-off."""
+    cfg, w, _ = tiny_inputs()
+    B = 160
+    ids = np.random.default_rng(5).integers(0, cfg.vocab_size, size=(B, 12), dtype=np.uint32)
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    runner = cb.LlamaRunner(gpu, cfg, params, Dtype.F32, max_batch=B, max_positions=48)
+    out = runner.generate(ids, 9)
+    logits = runner.last_logits()
+    solo = cb.LlamaRunner(gpu, cfg, params, Dtype.F32, max_batch=1, max_positions=48)
+    for b in (0, 1, 77, 159):
+        np.testing.assert_array_equal(solo.generate(ids[b:b + 1], 9)[0], out[b])
+        assert helpers.rel_err(solo.last_logits()[0], logits[b]) <= REL_F32
+
+
+def test_many_sequences_bf16_gqa(gpu):
+    """Same check in bf16 with grouped heads (4 query heads per kv head share one CTA)."""
+    cfg, wb, _ = small_bf16_model()
+    B = 96
+    ids = np.random.default_rng(6).integers(0, cfg.vocab_size, size=(B, 20), dtype=np.uint32)
+    pg = cb.upload_weights(gpu, wb, Dtype.BF16)
+    runner = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=B, max_positions=40)
+    runner.reset(B)
+    tok = runner.forward(ids)
+    picks = (0, 50, 95)
+    solos = {}
+    for b in picks:
+        solos[b] = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=1, max_positions=40)
+        solos[b].reset(1)
+        solos[b].forward(ids[b:b + 1])
+    for _ in range(5):
+        nxt = runner.forward(tok.reshape(B, 1))
+        lg = runner.last_logits()
+        for b in picks:
+            # the solo run is fed the batch's ids, so both see the same history
+            solos[b].forward(np.array([[tok[b]]], dtype=np.uint32))
+            assert np.abs(solos[b].last_logits()[0] - lg[b]).max() <= ABS_BF16
+        tok = nxt
+
+
 def small_bf16_model():
     # Llama-3.2-1B proportions (GQA 4:1, head_dim 64, tied head, theta 5e5) at 2 layers / hidden 512
     cfg = cb.LlamaConfig(512, 1536, 2, 8, 2, 4096, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=True)
