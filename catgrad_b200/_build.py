@@ -24,6 +24,7 @@ SOURCES = [
     "kernels/argmax_noalloc.cu",
     "host/cuda_backend.cu",
     "host/llama_engine.cu",
+    "host/tp_comm.cu",
     "host/c_api.cc",
     "host/interp.cc",
     "host/llama_term.cc",

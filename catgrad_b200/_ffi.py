@@ -109,6 +109,18 @@ CUDA_ONLY = {
     "llama_create": (C.c_int, [_CTX, C.POINTER(LlamaConfigStruct), C.c_int, C.c_void_p, C.c_uint64, C.c_uint64,
                                c_void_pp]),
     "llama_free": (None, [C.c_void_p]),
+    "llama_create_tp": (C.c_int, [_CTX, C.POINTER(LlamaConfigStruct), C.c_int, C.c_void_p, C.c_uint64, C.c_uint64,
+                                  C.c_void_p, C.c_uint64, c_void_pp]),
+    "comm_create": (C.c_int, [_CTX, C.c_int, C.c_int, C.c_uint64, c_void_pp]),
+    "comm_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "comm_attach": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "comm_attach_local": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "comm_set_timeout_ms": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "comm_write": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),
+    "comm_read": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),
+    "comm_data": (C.c_int, [C.c_void_p, c_void_pp, C.POINTER(C.c_uint64)]),
+    "comm_allreduce": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int]),
+    "comm_free": (None, [C.c_void_p]),
     "llama_reset": (C.c_int, [C.c_void_p, C.c_uint64]),
     "llama_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p]),
     "llama_decode": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),

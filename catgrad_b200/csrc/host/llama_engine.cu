@@ -24,6 +24,7 @@
 #include "../kernels/matmul.h"
 #include "c_api_internal.h"
 #include "cuda_backend.h"
+#include "tp_comm.h"
 
 using namespace cg;
 
@@ -40,7 +41,13 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 struct cg_llama {
   CudaBackend* be = nullptr;
   cg_ctx* ctx = nullptr;
-  LlamaConfig cfg;
+  LlamaConfig cfg;            // heads and FFN width are this rank's share under tensor parallelism
+  int64_t hd = 0;             // head dimension (of the unsharded model)
+  // tensor parallelism: q/k/v/gate/up hold this rank's rows, o/down this rank's columns; the partial products
+  // of o/down are summed over the ranks through `comm`, whose data area holds x and the partial buffer
+  cg_comm* comm = nullptr;
+  int64_t comm_tokens = 0;
+  size_t comm_part_off = 0;
   Dtype dt = Dtype::BF16;
   size_t es = 2;
   int64_t max_batch = 0, P = 0;
@@ -196,6 +203,12 @@ struct Plan {
     launched("add");
   }
 
+  // x += sum over the tensor-parallel ranks of the partial product in `tmp` (both live in the symmetric buffer)
+  void reduce_partials(int64_t n) {
+    m.comm->allreduce(m.dt, 0, m.comm_part_off, n, /*residual=*/true, sm, st, m.be->dev_err());
+    ++m.launches;
+  }
+
   // ---- the one-kernel decode step (llama_mega.cuh) ----
   static int mega_mt(int64_t B) { return B <= 1 ? 1 : (B <= 2 ? 2 : 4); }
   struct MegaGeom { bool ok = false; int nslots = 0; int xs_bytes = 0; size_t smem = 0; };
@@ -204,9 +217,9 @@ struct Plan {
     const LlamaConfig& c = m.cfg;
     if (!m.mega_enabled || B > 4) return g;
     const int mt = mega_mt(B);
-    const int64_t kmax = std::max<int64_t>(std::max<int64_t>(c.hidden_size, c.intermediate_size), c.num_attention_heads * c.head_dim());
+    const int64_t kmax = std::max<int64_t>(std::max<int64_t>(c.hidden_size, c.intermediate_size), c.num_attention_heads * m.hd);
     constexpr int VEC = 16 / sizeof(T);
-    const int64_t hd = c.head_dim();
+    const int64_t hd = m.hd;
     int64_t attn_bytes = (m.P + 1 + (256 / (hd / VEC)) * hd) * 4;
     int64_t xs = std::max<int64_t>(mt * kmax * (int64_t)sizeof(T), attn_bytes);
     xs = (xs + 127) / 128 * 128;
@@ -267,15 +280,15 @@ struct Plan {
     const LlamaConfig& c = m.cfg;
     cgk::MegaArgs a{};
     a.L = (int)c.num_hidden_layers; a.H = (int)c.hidden_size; a.F = (int)c.intermediate_size;
-    a.NQ = (int)(c.num_attention_heads * c.head_dim()); a.NKV = (int)(c.num_key_value_heads * c.head_dim());
+    a.NQ = (int)(c.num_attention_heads * m.hd); a.NKV = (int)(c.num_key_value_heads * m.hd);
     a.V = (int)c.vocab_size; a.nh = (int)c.num_attention_heads; a.nkv = (int)c.num_key_value_heads;
     a.P = (int)m.P; a.B = (int)B; a.G = m.mega_grid; a.nslots = g.nslots;
-    a.eps = c.rms_norm_eps; a.scale = cgk_host_round((float)std::sqrt((float)c.head_dim()));
+    a.eps = c.rms_norm_eps; a.scale = cgk_host_round((float)std::sqrt((float)m.hd));
     a.embed = m.embed; a.final_norm = m.final_norm; a.head = m.head;
     a.layers = (const cgk::MegaLayer*)m.mega_layers.raw();
     a.x = m.x.raw(); a.qkv = m.qkv.raw(); a.attn = m.attn.raw(); a.h = m.h.raw(); a.logits = m.logits.raw();
     a.kc = m.kc.raw(); a.vc = m.vc.raw();
-    a.kv_layer_stride = m.max_batch * c.num_key_value_heads * m.P * c.head_dim();
+    a.kv_layer_stride = m.max_batch * c.num_key_value_heads * m.P * m.hd;
     a.cos_t = (const float*)m.cos_t.raw(); a.sin_t = (const float*)m.sin_t.raw();
     a.ids_cur = (unsigned*)m.ids_cur.raw(); a.out_ids = (unsigned*)m.ids_out.raw();
     a.ctx_len = (int*)m.words.raw(); a.step_no = (int*)m.words.raw() + 1; a.out_cap_steps = (int)m.out_cap_steps;
@@ -285,7 +298,7 @@ struct Plan {
     a.err = m.be->dev_err(); a.abort_word = (unsigned*)m.words.raw() + 2;
     a.prof = m.mega_prof.defined() ? (unsigned long long*)m.mega_prof.raw() : nullptr;
     const int mt = mega_mt(B);
-    const bool hd64 = c.head_dim() == 64;
+    const bool hd64 = m.hd == 64;
     bool ok;
     if (mt == 1) ok = hd64 ? mega_launch_t<1, 64>(a, g) : mega_launch_t<1, 128>(a, g);
     else if (mt == 2) ok = hd64 ? mega_launch_t<2, 64>(a, g) : mega_launch_t<2, 128>(a, g);
@@ -300,7 +313,7 @@ struct Plan {
   void step(const unsigned* ids, int64_t B, int64_t S) {
     const LlamaConfig& c = m.cfg;
     const int64_t H = c.hidden_size, F = c.intermediate_size, nh = c.num_attention_heads, nkv = c.num_key_value_heads,
-                  hd = c.head_dim(), V = c.vocab_size, L = c.num_hidden_layers;
+                  hd = m.hd, V = c.vocab_size, L = c.num_hidden_layers;
     const int64_t M = B * S, NQ = nh * hd, NKV = nkv * hd, NQKV = NQ + 2 * NKV;
     int* ctx_len = (int*)m.words.raw();
     unsigned* err = m.be->dev_err();
@@ -409,11 +422,17 @@ struct Plan {
         a.w[0] = w.o; a.n_end[0] = a.n_end[1] = a.n_end[2] = (int)H;
         a.x = attn; a.x_row_stride = NQ; a.out = x; a.res = x; a.M = (int)M; a.N = (int)H; a.K = (int)NQ;
         region(a.pf, 0, w.down, H * F);
-        gemv(cgk::PRO_NONE, cgk::EPI_RESIDUAL, a);
+        if (m.comm) {
+          a.out = m.tmp.raw(); a.res = nullptr;
+          gemv(cgk::PRO_NONE, cgk::EPI_STORE, a);
+        } else {
+          gemv(cgk::PRO_NONE, cgk::EPI_RESIDUAL, a);
+        }
       } else {
         gemm(attn, NQ, w.o, m.tmp.raw(), M, H, NQ);
-        add_inplace(x, m.tmp.raw(), M * H);
+        if (!m.comm) add_inplace(x, m.tmp.raw(), M * H);
       }
+      if (m.comm) reduce_partials(M * H);
       // ---- MLP ----
       T* hbuf = (T*)m.h.raw();
       if (gemv_ok(M, H)) {
@@ -440,11 +459,17 @@ struct Plan {
         cgk::GemvArgs a{};
         a.w[0] = w.down; a.n_end[0] = a.n_end[1] = a.n_end[2] = (int)H;
         a.x = hbuf; a.x_row_stride = F; a.out = x; a.res = x; a.M = (int)M; a.N = (int)H; a.K = (int)F;
-        gemv(cgk::PRO_NONE, cgk::EPI_RESIDUAL, a);
+        if (m.comm) {
+          a.out = m.tmp.raw(); a.res = nullptr;
+          gemv(cgk::PRO_NONE, cgk::EPI_STORE, a);
+        } else {
+          gemv(cgk::PRO_NONE, cgk::EPI_RESIDUAL, a);
+        }
       } else {
         gemm(hbuf, F, w.down, m.tmp.raw(), M, H, F);
-        add_inplace(x, m.tmp.raw(), M * H);
+        if (!m.comm) add_inplace(x, m.tmp.raw(), M * H);
       }
+      if (m.comm) reduce_partials(M * H);
     }
     // ---- final norm + lm_head on the last position of each sequence, argmax ----
     T* logits = (T*)m.logits.raw();
@@ -483,7 +508,7 @@ struct Plan {
   // scores[b,kvh,r] = Q[b,:,kvh*rep+r,:] x K[b,kvh]^T ; softmax ; out = P x V[b,kvh].
   void prefill_attention(T* q, int64_t qs, T* kcl, T* vcl, T* attn_out, int64_t B, int64_t S) {
     const LlamaConfig& c = m.cfg;
-    const int64_t nh = c.num_attention_heads, nkv = c.num_key_value_heads, hd = c.head_dim(), rep = nh / nkv;
+    const int64_t nh = c.num_attention_heads, nkv = c.num_key_value_heads, hd = m.hd, rep = nh / nkv;
     const int64_t T0 = m.host_ctx_len, Tt = T0 + S;
     T* scores = (T*)m.scores.raw();
     cgk::View4 bt;
@@ -531,7 +556,7 @@ const Tensor& find_param(const cg_params* p, const std::string& key, Dtype dt, c
 void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
   const LlamaConfig& c = m.cfg;
   int64_t M = B * S;
-  int64_t H = c.hidden_size, F = c.intermediate_size, nh = c.num_attention_heads, hd = c.head_dim(),
+  int64_t H = c.hidden_size, F = c.intermediate_size, nh = c.num_attention_heads, hd = m.hd,
           NQKV = (c.num_attention_heads + 2 * c.num_key_value_heads) * hd;
   if (M > m.cap_tokens) {
     if (m.graph) {
@@ -540,12 +565,36 @@ void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
       m.graph_batch = -1;
     }
     m.be->synchronize();
-    m.x = m.be->empty({M, H}, m.dt);
+    if (m.comm) {
+      CG_CHECK(M <= m.comm_tokens, ERR_INVALID_ARG,
+               "batch x sequence exceeds the max_tokens the tensor-parallel runner was created with");
+      // x and the partial products live in the symmetric buffer (not owned: no deleter)
+      auto wrap = [&](size_t off) {
+        Tensor t;
+        t.st = std::make_shared<Storage>(m.comm->data() + off, (size_t)(M * H) * m.es, nullptr);
+        t.dt = m.dt;
+        t.shape = {M, H};
+        t.strides = contiguous_strides(t.shape);
+        return t;
+      };
+      m.x = wrap(0);
+    } else {
+      m.x = m.be->empty({M, H}, m.dt);
+    }
     m.xn = m.be->empty({M, H}, m.dt);
     m.qkv = m.be->empty({M, NQKV}, m.dt);
     m.attn = m.be->empty({M, nh * hd}, m.dt);
     m.h = m.be->empty({M, F}, m.dt);
-    m.tmp = m.be->empty({M, H}, m.dt);
+    if (m.comm) {
+      Tensor t;
+      t.st = std::make_shared<Storage>(m.comm->data() + m.comm_part_off, (size_t)(M * H) * m.es, nullptr);
+      t.dt = m.dt;
+      t.shape = {M, H};
+      t.strides = contiguous_strides(t.shape);
+      m.tmp = t;
+    } else {
+      m.tmp = m.be->empty({M, H}, m.dt);
+    }
     if (M > 16 || (size_t)16 * H * m.es > 160 * 1024) {  // gate/up buffers of the GEMM path
       m.g = m.be->empty({M, F}, m.dt);
       m.u = m.be->empty({M, F}, m.dt);
@@ -595,8 +644,14 @@ typedef struct {
   int tie_word_embeddings;
 } api_llama_config;
 
-int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const cg_params* params, uint64_t max_batch,
-                    uint64_t max_positions, cg_llama** out) {
+}  // extern "C"
+
+namespace {
+// comm == nullptr: the whole model on this GPU.  Otherwise `params` holds rank comm->rank's shard of a model whose
+// unsharded shape is `cfg`: rows [r*n/size, (r+1)*n/size) of q/k/v/gate/up, the same range of columns of o/down;
+// norms, embedding and lm_head whole.
+int create_runner(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const cg_params* params, uint64_t max_batch,
+                  uint64_t max_positions, cg_comm* comm, uint64_t max_tokens, cg_llama** out) {
   CG_API_BEGIN
   CG_CHECK(ctx && ctx->be && cfg && params && out, ERR_BAD_HANDLE, "null argument");
   CG_CHECK(dtype == (int)Dtype::F32 || dtype == (int)Dtype::BF16, ERR_UNSUPPORTED_DTYPE,
@@ -621,8 +676,26 @@ int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const c
            ERR_INVALID_ARG, "inconsistent Llama config");
   const int64_t hd = c.head_dim();
   CG_CHECK(hd == 64 || hd == 128, ERR_INVALID_ARG, "the fused runner supports head_dim 64 and 128");
+  m->hd = hd;
   m->dt = (Dtype)dtype;
   m->es = dtype_size(m->dt);
+  if (comm) {
+    const int64_t tp = comm->size;
+    CG_CHECK(comm->ctx == ctx, ERR_INVALID_ARG, "communicator belongs to another context");
+    CG_CHECK(comm->attached, ERR_INVALID_ARG, "communicator is not attached to its peers");
+    CG_CHECK(c.num_key_value_heads % tp == 0 && c.intermediate_size % tp == 0, ERR_INVALID_ARG,
+             "kv heads and intermediate size must divide by the number of tensor-parallel ranks");
+    CG_CHECK(max_tokens >= max_batch, ERR_INVALID_ARG, "max_tokens must cover at least one token per sequence");
+    // from here on the config describes this rank's share; the hidden size stays whole
+    c.num_attention_heads /= tp;
+    c.num_key_value_heads /= tp;
+    c.intermediate_size /= tp;
+    m->comm = comm;
+    m->comm_tokens = (int64_t)max_tokens;
+    m->comm_part_off = align_up((size_t)max_tokens * (size_t)c.hidden_size * m->es, 256);
+    CG_CHECK(2 * m->comm_part_off <= comm->data_bytes, ERR_INVALID_ARG,
+             "symmetric buffer too small: need 2 x align256(max_tokens x hidden x element size) bytes");
+  }
   const int64_t vec = 16 / (int64_t)m->es;
   CG_CHECK(c.hidden_size % vec == 0 && c.intermediate_size % vec == 0, ERR_INVALID_ARG,
            "hidden and intermediate sizes must be multiples of 16 bytes");
@@ -630,7 +703,8 @@ int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const c
   m->max_batch = (int64_t)max_batch;
   m->P = (int64_t)max_positions;
 
-  const int64_t H = c.hidden_size, F = c.intermediate_size, NKV = c.num_key_value_heads * hd, V = c.vocab_size;
+  const int64_t H = c.hidden_size, F = c.intermediate_size, NQ = c.num_attention_heads * hd,
+                NKV = c.num_key_value_heads * hd, V = c.vocab_size;
   auto get = [&](const std::string& key, const Shape& shape) {
     const Tensor& t = find_param(params, key, m->dt, shape);
     m->keep.push_back(t);
@@ -641,10 +715,10 @@ int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const c
     std::string p = "model.layers." + std::to_string(l) + ".";
     LayerW w;
     w.in_norm = get(p + "input_layernorm.weight", {H});
-    w.q = get(p + "self_attn.q_proj.weight", {H, H});
+    w.q = get(p + "self_attn.q_proj.weight", {NQ, H});
     w.k = get(p + "self_attn.k_proj.weight", {NKV, H});
     w.v = get(p + "self_attn.v_proj.weight", {NKV, H});
-    w.o = get(p + "self_attn.o_proj.weight", {H, H});
+    w.o = get(p + "self_attn.o_proj.weight", {H, NQ});
     w.post_norm = get(p + "post_attention_layernorm.weight", {H});
     w.gate = get(p + "mlp.gate_proj.weight", {F, H});
     w.up = get(p + "mlp.up_proj.weight", {F, H});
@@ -687,12 +761,26 @@ int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const c
     int coop = 0;
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, be.device());
     // opt-in: at the current tuning the graph of per-sub-graph kernels is faster
-    m->mega_enabled = coop != 0 && std::getenv("CATGRAD_B200_MEGA") != nullptr;
+    m->mega_enabled = coop != 0 && comm == nullptr && std::getenv("CATGRAD_B200_MEGA") != nullptr;
     // CATGRAD_B200_MEGA_PROF: per-CTA cycle counters of the persistent kernel, printed by cg_llama_free
     if (std::getenv("CATGRAD_B200_MEGA_PROF")) m->mega_prof = be.zeros({(int64_t)m->mega_grid * 8 * 2}, Dtype::U32);
   }
   *out = m.release();
   CG_API_END(ctx)
+}
+}  // namespace
+
+extern "C" {
+
+int cg_llama_create(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const cg_params* params, uint64_t max_batch,
+                    uint64_t max_positions, cg_llama** out) {
+  return create_runner(ctx, cfg, dtype, params, max_batch, max_positions, nullptr, 0, out);
+}
+
+int cg_llama_create_tp(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const cg_params* params, uint64_t max_batch,
+                       uint64_t max_positions, cg_comm* comm, uint64_t max_tokens, cg_llama** out) {
+  if (!comm) return cg::record_error(ctx, (int)ERR_BAD_HANDLE, "null communicator");
+  return create_runner(ctx, cfg, dtype, params, max_batch, max_positions, comm, max_tokens, out);
 }
 
 void cg_llama_free(cg_llama* m) {

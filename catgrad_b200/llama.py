@@ -139,17 +139,25 @@ def generate_with_interpreter(backend, term, params, cfg, prompt_ids, steps, dty
 class LlamaRunner:
     """Fused Llama plan with a device-resident KV cache (`cg_llama_*`)."""
 
-    def __init__(self, backend, cfg, params, dtype, max_batch, max_positions):
+    def __init__(self, backend, cfg, params, dtype, max_batch, max_positions, comm=None, max_tokens=None):
+        """comm: a `catgrad_b200.tp.TpComm`; then `params` is this rank's shard (`tp.shard_weights`) of the model
+        `cfg` describes, and max_tokens bounds batch x seq of any forward call."""
         if not hasattr(backend._ns, "llama_create"):
             raise BackendError(Status.CUDA, "the fused runner exists only in the CUDA library")
         self._be = backend
         self.cfg = cfg
         self.max_batch = max_batch
         self.max_positions = max_positions
+        self._comm = comm
         h = C.c_void_p()
         st = cfg.to_struct()
-        backend._check(backend._ns.llama_create(backend._ctx, C.byref(st), int(dtype), params.handle, max_batch,
-                                                max_positions, C.byref(h)))
+        if comm is None:
+            backend._check(backend._ns.llama_create(backend._ctx, C.byref(st), int(dtype), params.handle, max_batch,
+                                                    max_positions, C.byref(h)))
+        else:
+            backend._check(backend._ns.llama_create_tp(backend._ctx, C.byref(st), int(dtype), params.handle, max_batch,
+                                                       max_positions, comm.handle, int(max_tokens or max_batch),
+                                                       C.byref(h)))
         self._h = h
         self._params = params
         self._batch = 0

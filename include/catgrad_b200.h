@@ -183,6 +183,38 @@ cg_status cg_interp_run(cg_ctx*, const cg_term* term, const cg_params* params, c
 cg_status cg_llama_create(cg_ctx*, const cg_llama_config* cfg, cg_dtype dtype, const cg_params* params,
                           uint64_t max_batch, uint64_t max_positions, cg_llama** out);
 void cg_llama_free(cg_llama* m);
+
+/* ---- tensor parallelism (B200 only; the reference has no multi-GPU path) ---------------------
+ * One process per GPU.  Every rank creates a communicator (a symmetric device buffer), the ranks exchange the
+ * 64-byte handles over any host channel and attach; after that the all-reduce is a single kernel per call that
+ * sums over plain peer loads (NVLink), in rank order with f32 accumulation, so every rank holds bit-identical
+ * results.  Device-side waits are bounded (5 s): a rank that never arrives turns into CG_ERR_TIMEOUT at the next
+ * synchronising call, and the communicator stays unusable after that. */
+typedef struct cg_comm cg_comm;
+cg_status cg_comm_create(cg_ctx*, int rank, int size, uint64_t data_bytes, cg_comm** out);
+cg_status cg_comm_handle(cg_comm*, void* out64);
+cg_status cg_comm_attach(cg_comm*, const void* handles /* size x 64 bytes, rank order */);
+/* Same-process alternative to cg_comm_attach (one process driving several GPUs, where IPC handles cannot be used):
+ * `all` = the communicators of all ranks in rank order. */
+cg_status cg_comm_attach_local(cg_comm*, cg_comm* const* all);
+/* Limit of the device-side waits (default 5000 ms). */
+cg_status cg_comm_set_timeout_ms(cg_comm*, uint64_t ms);
+cg_status cg_comm_data(cg_comm*, void** device_ptr, uint64_t* bytes);
+/* Host <-> data area copies at byte offset `off` (both synchronise the context's stream). */
+cg_status cg_comm_write(cg_comm*, uint64_t off, const void* src, uint64_t bytes);
+cg_status cg_comm_read(cg_comm*, uint64_t off, void* dst, uint64_t bytes);
+/* x (+)= sum over ranks of part; x_off/part_off are byte offsets into the data area (same on every rank),
+ * n elements of dtype CG_F32 or CG_BF16.  residual != 0: x = round(x + round(sum)); else x = round(sum). */
+cg_status cg_comm_allreduce(cg_comm*, cg_dtype dtype, uint64_t x_off, uint64_t part_off, uint64_t n, int residual);
+void cg_comm_free(cg_comm*);
+/* Tensor-parallel fused runner: `cfg` is the unsharded model, `params` holds this rank's shard (rows
+ * [r*n/size, (r+1)*n/size) of q/k/v/gate/up_proj, the same range of columns of o/down_proj, everything else
+ * whole).  The partial products of o_proj and down_proj are all-reduced into the residual stream (llama.rs:303-385
+ * with the projections split over heads / FFN columns).  The communicator's data area must hold
+ * 2 x align256(max_tokens x hidden x element size) bytes; max_tokens bounds batch x seq of any forward call. */
+cg_status cg_llama_create_tp(cg_ctx*, const cg_llama_config* cfg, cg_dtype dtype, const cg_params* params,
+                             uint64_t max_batch, uint64_t max_positions, cg_comm* comm, uint64_t max_tokens,
+                             cg_llama** out);
 /* Clears the KV cache (context length 0) for a new batch of `batch` sequences. */
 cg_status cg_llama_reset(cg_llama* m, uint64_t batch);
 /* Runs one step of the term on `ids` (host memory, [batch, seq] u32, row-major) at the current context

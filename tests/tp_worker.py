@@ -1,0 +1,93 @@
+"""One rank of the 2-GPU tensor-parallel parity test (launched by tests/test_gpu_tp.py through torch.distributed.run).
+
+Every rank runs its shard of the same model on its own GPU; rank 0 also runs the unsharded model on its GPU and
+compares.  Exit code 0 = all checks passed."""
+import datetime
+import os
+import sys
+
+import numpy as np
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import catgrad_b200 as cb  # noqa: E402
+from catgrad_b200 import Dtype, tp  # noqa: E402
+
+REL_F32 = 1e-4      # f32 logits, relative to the largest logit
+ABS_BF16 = 2e-2     # bf16 logits, max-abs
+
+
+def rel_err(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def run_case(be, rank, size, cfg, weights, dtype, batch, prompt, steps, what):
+    es = 4 if dtype == Dtype.F32 else 2
+    ids = np.random.default_rng(21).integers(0, cfg.vocab_size, size=(batch, prompt), dtype=np.uint32)
+    max_tokens = batch * prompt
+    comm = tp.connect(be, tp.comm_bytes(cfg, max_tokens, es))
+    shard = cb.upload_weights(be, tp.shard_weights(cfg, weights, rank, size), dtype)
+    runner = cb.LlamaRunner(be, cfg, shard, dtype, max_batch=batch, max_positions=prompt + steps + 1, comm=comm,
+                            max_tokens=max_tokens)
+    runner.reset(batch)
+    first = runner.forward(ids)
+    logits0 = runner.last_logits()
+    rest = runner.decode(steps)               # captured graph: the all-reduce replays inside it
+    logits1 = runner.last_logits()
+    out = np.concatenate([first[:, None], rest], 1)
+    # every rank must hold the same ids
+    gathered = [None] * size
+    dist.all_gather_object(gathered, out.tobytes())
+    assert all(g == gathered[0] for g in gathered), f"{what}: ranks disagree on the generated ids"
+    if rank == 0:
+        full = cb.upload_weights(be, weights, dtype)
+        ref = cb.LlamaRunner(be, cfg, full, dtype, max_batch=batch, max_positions=prompt + steps + 1)
+        ref.reset(batch)
+        rfirst = ref.forward(ids)
+        rlogits0 = ref.last_logits()
+        if dtype == Dtype.F32:
+            e = rel_err(logits0, rlogits0)
+            assert e <= REL_F32, f"{what}: prefill logits rel err {e}"
+            np.testing.assert_array_equal(first, rfirst)
+            rrest = ref.decode(steps)
+            np.testing.assert_array_equal(rest, rrest)
+            e = rel_err(logits1, ref.last_logits())
+            assert e <= REL_F32, f"{what}: decode logits rel err {e}"
+        else:
+            e = float(np.abs(logits0 - rlogits0).max())
+            assert e <= ABS_BF16, f"{what}: prefill logits max-abs {e}"
+            # teacher-force the unsharded run with the sharded run's ids so both see the same history
+            tok = first
+            for s in range(steps):
+                ref.forward(tok.reshape(batch, 1))
+                tok = rest[:, s]
+            e = float(np.abs(logits1 - ref.last_logits()).max())
+            assert e <= ABS_BF16, f"{what}: decode logits max-abs {e}"
+        print(f"[tp_worker] {what}: ok", flush=True)
+    dist.barrier()
+    del runner
+    comm.close()
+
+
+def main():
+    rank, size = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", rank=rank, world_size=size, timeout=datetime.timedelta(seconds=120))
+    be = cb.Backend(int(os.environ.get("LOCAL_RANK", rank)))
+    tiny = cb.LlamaConfig(256, 688, 2, 4, 4, 1024, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    w = cb.random_weights(tiny, seed=0)
+    run_case(be, rank, size, tiny, w, Dtype.F32, 1, 24, 6, "tiny f32 batch 1 (GEMV path, one-shot all-reduce)")
+    run_case(be, rank, size, tiny, w, Dtype.F32, 20, 12, 4, "tiny f32 batch 20 (GEMM path)")
+    # Llama-3 proportions (GQA 4:1, head_dim 128): 2 layers, hidden 1024; the prefill of 48 x 96 tokens moves
+    # 9 MiB per all-reduce (two-shot path)
+    small = cb.LlamaConfig(1024, 3584, 2, 8, 2, 4096, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    wb = cb.random_weights(small, seed=1)
+    wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in wb.items()}
+    run_case(be, rank, size, small, wb, Dtype.BF16, 2, 40, 5, "small bf16 batch 2 (GEMV path)")
+    run_case(be, rank, size, small, wb, Dtype.BF16, 48, 96, 4, "small bf16 batch 48 (tcgen05 GEMM path, two-shot)")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
