@@ -510,36 +510,77 @@ struct Plan {
     const LlamaConfig& c = m.cfg;
     const int64_t nh = c.num_attention_heads, nkv = c.num_key_value_heads, hd = m.hd, rep = nh / nkv;
     const int64_t T0 = m.host_ctx_len, Tt = T0 + S;
+    const int64_t Tp = score_pitch(Tt);  // row pitch of the score matrix
     T* scores = (T*)m.scores.raw();
-    cgk::View4 bt;
-    std::memset(&bt, 0, sizeof(bt));
-    bt.rank = 3;
-    bt.shape[0] = B; bt.shape[1] = nkv; bt.shape[2] = rep;
-    bt.total = B * nh;
-    bt.sa[0] = S * qs; bt.sa[1] = rep * hd; bt.sa[2] = hd;            // Q[b, s, h, :] with h = kvh*rep + r
-    bt.sb[0] = nkv * m.P * hd; bt.sb[1] = m.P * hd; bt.sb[2] = 0;     // K[b, kvh, t, :]
-    // scores: A = Q rows (pitch qs, K-contiguous), B = K^T: k-stride 1, n-stride hd
-    cgk::launch_matmul((int)m.dt, bt, B * nh, q, kcl, scores, S, Tt, hd, qs, 1, 1, hd, sm, st);
-    launched("scores");
     const float scale = cgk_host_round((float)std::sqrt((float)hd));
-    if ((size_t)Tt * 4 > 48 * 1024)
-      cudaFuncSetAttribute(cgk::softmax_mask_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(Tt * 4));
-    cgk::softmax_mask_kernel<T><<<(unsigned)(B * nh * S), 256, (size_t)Tt * 4, st>>>(scores, (int)S, (int)Tt, (int)T0, scale);
+    unsigned* err = m.be->dev_err();
+    bool tc = false;
+    if (std::is_same<T, __nv_bfloat16>::value) {
+      // tensor cores: scores[b, h] = Q[b, :, h, :] x K[b, h / rep]^T over 4-D tensor maps
+      cgk::GroupedGemm g{};
+      g.A = q; g.a_row = qs; g.a_head = hd; g.a_outer = S * qs;
+      g.B = kcl; g.b_row = hd; g.b_head = m.P * hd; g.b_outer = nkv * m.P * hd; g.b_n_contiguous = false;
+      g.C = scores; g.ldc = Tp; g.c_head = S * Tp; g.c_outer = nh * S * Tp;
+      g.M = S; g.N = Tt; g.K = hd; g.heads = nh; g.outer = B; g.b_div = rep;
+      tc = cgk::launch_tcgen05_gemm_grouped(g, err, st);
+    }
+    if (tc) {
+      launched("scores(tcgen05)");
+    } else {
+      cgk::View4 bt;
+      std::memset(&bt, 0, sizeof(bt));
+      bt.rank = 3;
+      bt.shape[0] = B; bt.shape[1] = nkv; bt.shape[2] = rep;
+      bt.total = B * nh;
+      bt.sa[0] = S * qs; bt.sa[1] = rep * hd; bt.sa[2] = hd;            // Q[b, s, h, :] with h = kvh*rep + r
+      bt.sb[0] = nkv * m.P * hd; bt.sb[1] = m.P * hd; bt.sb[2] = 0;     // K[b, kvh, t, :]
+      // scores: A = Q rows (pitch qs, K-contiguous), B = K^T: k-stride 1, n-stride hd; C rows Tt apart
+      CG_CHECK(Tp == Tt, ERR_INVALID_ARG, "internal: padded score rows need the tensor-core path");
+      cgk::launch_matmul((int)m.dt, bt, B * nh, q, kcl, scores, S, Tt, hd, qs, 1, 1, hd, sm, st);
+      launched("scores");
+    }
+    if (std::is_same<T, __nv_bfloat16>::value && Tp <= 1024 && Tp % 8 == 0) {
+      const long long rows = B * nh * S;
+      cgk::softmax_mask_rows_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(scores, rows, (int)S, (int)Tt, (int)Tp,
+                                                                                  (int)T0, scale);
+    } else {
+      if ((size_t)Tt * 4 > 48 * 1024)
+        cudaFuncSetAttribute(cgk::softmax_mask_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(Tt * 4));
+      cgk::softmax_mask_kernel<T><<<(unsigned)(B * nh * S), 256, (size_t)Tt * 4, st>>>(scores, (int)S, (int)Tt, (int)Tp, (int)T0, scale);
+    }
     launched("softmax_mask");
-    // out[b,h,s,:] = P[b,h,s,:] x V[b,kvh]  (V: k-stride hd, n-stride 1)
+    // out[b, s, h, :] = P[b, h, s, :] x V[b, h / rep]  (V rows are keys: K rows hd apart, N contiguous)
+    tc = false;
+    if (std::is_same<T, __nv_bfloat16>::value) {
+      cgk::GroupedGemm g{};
+      g.A = scores; g.a_row = Tp; g.a_head = S * Tp; g.a_outer = nh * S * Tp;
+      g.B = vcl; g.b_row = hd; g.b_head = m.P * hd; g.b_outer = nkv * m.P * hd; g.b_n_contiguous = true;
+      g.C = attn_out; g.ldc = nh * hd; g.c_head = hd; g.c_outer = S * nh * hd;   // straight into [B, S, nh*hd]
+      g.M = S; g.N = hd; g.K = Tt; g.heads = nh; g.outer = B; g.b_div = rep;
+      tc = cgk::launch_tcgen05_gemm_grouped(g, err, st);
+    }
+    if (tc) {
+      launched("pv(tcgen05)");
+      return;
+    }
     cgk::View4 bp;
     std::memset(&bp, 0, sizeof(bp));
     bp.rank = 3;
     bp.shape[0] = B; bp.shape[1] = nkv; bp.shape[2] = rep;
     bp.total = B * nh;
-    bp.sa[0] = nh * S * Tt; bp.sa[1] = rep * S * Tt; bp.sa[2] = S * Tt;
+    bp.sa[0] = nh * S * Tp; bp.sa[1] = rep * S * Tp; bp.sa[2] = S * Tp;
     bp.sb[0] = nkv * m.P * hd; bp.sb[1] = m.P * hd; bp.sb[2] = 0;
     T* obhsd = (T*)m.attn_bhsd.raw();
-    cgk::launch_matmul((int)m.dt, bp, B * nh, scores, vcl, obhsd, S, hd, Tt, Tt, 1, hd, 1, sm, st);
+    cgk::launch_matmul((int)m.dt, bp, B * nh, scores, vcl, obhsd, S, hd, Tt, Tp, 1, hd, 1, sm, st);
     launched("pv");
     cgk::bhsd_to_bshd_kernel<T><<<grid_for(B * nh * S * (hd / (16 / sizeof(T)))), 256, 0, st>>>(obhsd, attn_out, (int)B,
                                                                                               (int)nh, (int)S, (int)hd);
     launched("bhsd_to_bshd");
+  }
+
+  // bf16 score rows are padded to a multiple of 16 bytes so that they can be tensor-map rows
+  static int64_t score_pitch(int64_t Tt) {
+    return std::is_same<T, __nv_bfloat16>::value && cgk::tcgen05_available() ? (Tt + 7) / 8 * 8 : Tt;
   }
 };
 
@@ -604,7 +645,7 @@ void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
   }
   if (S > 1) {
     int64_t Tt = m.host_ctx_len + S;
-    int64_t need = B * nh * S * Tt;
+    int64_t need = B * nh * S * ((Tt + 7) / 8 * 8);
     if (!m.scores.defined() || m.scores.size() < need) m.scores = m.be->empty({need}, m.dt);
     int64_t need2 = B * nh * S * hd;
     if (!m.attn_bhsd.defined() || m.attn_bhsd.size() < need2) m.attn_bhsd = m.be->empty({need2}, m.dt);

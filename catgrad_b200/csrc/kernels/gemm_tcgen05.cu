@@ -88,6 +88,14 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor for a K-major operand tile written by TMA with the 128-byte swizzle:
 // rows are 128 bytes, groups of 8 rows are 1024 bytes apart (stride byte offset), descriptor version 1,
 // layout type 2 (SWIZZLE_128B).  The tile base is 1024-byte aligned.
@@ -155,13 +163,22 @@ struct SmemLayout {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 };
 
-// grid: (ceil(N/BN), ceil(M/BM), batch).  BATCHED selects 3-D tensor maps {K, rows, batch}.  B_MN: the right
+// Where a product of a batch sits: z = blockIdx.z.  BMODE 1: 3-D tensor maps {K, rows, z}.  BMODE 2: 4-D maps
+// {K, rows, head, outer} with z = outer * heads + head; the right operand's head coordinate is head / b_div (grouped
+// heads share it), and C may be strided: base + outer * c_outer + head * c_inner, rows ldc apart.
+struct BatchGeom {
+  int heads, b_div;
+  long long c_outer, c_inner;
+  int ldc;
+};
+
+// grid: (ceil(N/BN), ceil(M/BM), batch).  BMODE: 0 = one product, 1/2 = see BatchGeom.  B_MN: the right
 // operand is stored [K, N] with N contiguous (tensor map dims {N, K}); otherwise [N, K] with K contiguous.
-template <int BN, int STAGES, bool BATCHED, bool B_MN>
+template <int BN, int STAGES, int BMODE, bool B_MN>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                                            const __grid_constant__ CUtensorMap tmB,
                                                            __nv_bfloat16* __restrict__ C, int M, int N, int K,
-                                                           long long c_batch_stride, unsigned* err) {
+                                                           BatchGeom g, unsigned* err) {
   using L = SmemLayout<BN>;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // allocations are powers of two >= 32 columns
   extern __shared__ unsigned char smem_raw[];
@@ -174,6 +191,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, bz = blockIdx.z;
+  const int zo = BMODE == 2 ? bz / g.heads : 0, zh = BMODE == 2 ? bz % g.heads : 0;
   const int num_k = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -205,17 +223,20 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
       unsigned char* a_dst = smem + s * L::STAGE_BYTES;
       unsigned char* b_dst = a_dst + L::A_BYTES;
       mbar_expect_tx(&full[s], L::STAGE_BYTES);
-      if (BATCHED) tma_load_3d(a_dst, &tmA, &full[s], k * BK, m0, bz);
+      if (BMODE == 2) tma_load_4d(a_dst, &tmA, &full[s], k * BK, m0, zh, zo);
+      else if (BMODE == 1) tma_load_3d(a_dst, &tmA, &full[s], k * BK, m0, bz);
       else tma_load_2d(a_dst, &tmA, &full[s], k * BK, m0);
       if (B_MN) {
         // one 64-column x BK-row box per 64 columns of the tile
 #pragma unroll
         for (int nb = 0; nb < BN / 64; ++nb) {
-          if (BATCHED) tma_load_3d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, k * BK, bz);
+          if (BMODE == 2) tma_load_4d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, k * BK, zh / g.b_div, zo);
+          else if (BMODE == 1) tma_load_3d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, k * BK, bz);
           else tma_load_2d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, k * BK);
         }
       } else {
-        if (BATCHED) tma_load_3d(b_dst, &tmB, &full[s], k * BK, n0, bz);
+        if (BMODE == 2) tma_load_4d(b_dst, &tmB, &full[s], k * BK, n0, zh / g.b_div, zo);
+        else if (BMODE == 1) tma_load_3d(b_dst, &tmB, &full[s], k * BK, n0, bz);
         else tma_load_2d(b_dst, &tmB, &full[s], k * BK, n0);
       }
       issued = k + 1;
@@ -259,8 +280,10 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
       tc_fence_after();
       const int q = warp & 3;
       const int row = m0 + q * 32 + lane;
-      __nv_bfloat16* crow = C + (long long)bz * c_batch_stride + (long long)row * N;
-      const bool vec_ok = (N % 8 == 0) && (((uintptr_t)C & 15) == 0) && ((c_batch_stride % 8) == 0);
+      const long long c_off = BMODE == 2 ? (long long)zo * g.c_outer + (long long)zh * g.c_inner : (long long)bz * g.c_outer;
+      __nv_bfloat16* crow = C + c_off + (long long)row * g.ldc;
+      // 16-byte stores need every row start and every 32-column group aligned
+      const bool vec_ok = (g.ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (g.c_outer % 8 == 0) && (g.c_inner % 8 == 0);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -347,6 +370,34 @@ bool make_map_mn(CUtensorMap* map, const void* base, long long K, long long N, l
   return r == CUDA_SUCCESS;
 }
 
+// 4-D variants for grouped batches: element strides of the row, head and outer axes.
+bool make_map4(CUtensorMap* map, const void* base, long long K, long long rows, long long heads, long long outer,
+               long long s_row, long long s_head, long long s_outer, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)outer};
+  cuuint64_t strides[3] = {(cuuint64_t)s_row * 2, (cuuint64_t)s_head * 2, (cuuint64_t)s_outer * 2};
+  cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+bool make_map4_mn(CUtensorMap* map, const void* base, long long K, long long N, long long heads, long long outer,
+                  long long s_krow, long long s_head, long long s_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)K, (cuuint64_t)heads, (cuuint64_t)outer};
+  cuuint64_t strides[3] = {(cuuint64_t)s_krow * 2, (cuuint64_t)s_head * 2, (cuuint64_t)s_outer * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)BK, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 struct Problem {
   bool ok = false;
   bool b_mn = false;               // right operand stored [K, N], N contiguous
@@ -391,19 +442,32 @@ Problem analyse(const View4& bt, long long batch, const void* A, const void* B, 
   return p;
 }
 
-template <int BN, int STAGES, bool BATCHED, bool B_MN = false>
-void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K,
-              long long batch, unsigned* err, cudaStream_t st) {
+template <int BN, int STAGES, int BMODE, bool B_MN>
+void launch_g(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K,
+              long long batch, const BatchGeom& g, unsigned* err, cudaStream_t st) {
   using L = SmemLayout<BN>;
   size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 /* alignment slack */ + (2 * STAGES + 1) * 8 + 16;
-  auto kern = gemm_tcgen05_kernel<BN, STAGES, BATCHED, B_MN>;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, BMODE, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attr_set = true;
   }
   dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)batch);
-  kern<<<grid, 192, smem, st>>>(ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, M * N, err);
+  kern<<<grid, 192, smem, st>>>(ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, g, err);
+}
+
+// contiguous C[batch, M, N]
+template <int BN, int STAGES, bool BATCHED, bool B_MN = false>
+void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K,
+              long long batch, unsigned* err, cudaStream_t st) {
+  BatchGeom g;
+  g.heads = 1;
+  g.b_div = 1;
+  g.c_outer = M * N;
+  g.c_inner = 0;
+  g.ldc = (int)N;
+  launch_g<BN, STAGES, BATCHED ? 1 : 0, B_MN>(ta, tb, C, M, N, K, batch, g, err, st);
 }
 }  // namespace
 
@@ -450,6 +514,50 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
     case 64: bt3 ? launch_t<64, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<64, 8, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
     case 32: bt3 ? launch_t<32, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<32, 5, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
     default: bt3 ? launch_t<16, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<16, 5, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
+  }
+  return true;
+}
+
+bool tcgen05_available() {
+  static const bool disabled = std::getenv("CATGRAD_B200_NO_TCGEN05") != nullptr;
+  return !disabled && encode_fn() != nullptr;
+}
+
+bool launch_tcgen05_gemm_grouped(const GroupedGemm& p, unsigned* err, cudaStream_t st) {
+  if (!tcgen05_available()) return false;
+  auto ok8 = [](long long v) { return v > 0 && v % 8 == 0; };
+  if (p.M < 1 || p.N < 16 || p.K < 16 || p.heads < 1 || p.outer < 1 || p.b_div < 1 || p.heads % p.b_div != 0) return false;
+  if ((long long)p.heads * p.outer > 65535) return false;
+  if (!ok8(p.a_row) || !ok8(p.a_head) || !ok8(p.a_outer) || !ok8(p.b_row) || !ok8(p.b_head) || !ok8(p.b_outer)) return false;
+  if (!ok8(p.ldc) || p.c_head % 8 != 0 || p.c_outer % 8 != 0) return false;
+  if (((uintptr_t)p.A & 15) || ((uintptr_t)p.B & 15) || ((uintptr_t)p.C & 15)) return false;
+  if (p.b_n_contiguous && (p.N < 64 || p.N % 8 != 0)) return false;
+  BatchGeom g;
+  g.heads = (int)p.heads;
+  g.b_div = (int)p.b_div;
+  g.c_outer = p.c_outer;
+  g.c_inner = p.c_head;
+  g.ldc = (int)p.ldc;
+  const long long z = (long long)p.heads * p.outer;
+  CUtensorMap ta, tb;
+  if (!make_map4(&ta, p.A, p.K, p.M, p.heads, p.outer, p.a_row, p.a_head, p.a_outer, BM)) return false;
+  const long long kv_heads = p.heads / p.b_div;
+  if (p.b_n_contiguous) {
+    if (!make_map4_mn(&tb, p.B, p.K, p.N, kv_heads, p.outer, p.b_row, p.b_head, p.b_outer)) return false;
+    if (p.N >= 128) launch_g<128, 6, 2, true>(ta, tb, p.C, p.M, p.N, p.K, z, g, err, st);
+    else launch_g<64, 8, 2, true>(ta, tb, p.C, p.M, p.N, p.K, z, g, err, st);
+    return true;
+  }
+  const int bn = p.N >= 256 ? 256 : (p.N >= 128 ? 128 : (p.N >= 64 ? 64 : (p.N >= 32 ? 32 : 16)));
+  if (!make_map4(&tb, p.B, p.K, p.N, kv_heads, p.outer, p.b_row, p.b_head, p.b_outer, bn)) return false;
+  // short reductions (K = head dimension) need two stages only, which leaves room for several CTAs per SM
+  const bool short_k = p.K <= 2 * BK;
+  switch (bn) {
+    case 256: short_k ? launch_g<256, 2, 2, false>(ta, tb, p.C, p.M, p.N, p.K, z, g, err, st) : launch_g<256, 4, 2, false>(ta, tb, p.C, p.M, p.N, p.K, z, g, err, st); break;
+    case 128: short_k ? launch_g<128, 2, 2, false>(ta, tb, p.C, p.M, p.N, p.K, z, g, err, st) : launch_g<128, 6, 2, false>(ta, tb, p.C, p.M, p.N, p.K, z, g, err, st); break;
+    case 64: short_k ? launch_g<64, 2, 2, false>(ta, tb, p.C, p.M, p.N, p.K, z, g, err, st) : launch_g<64, 8, 2, false>(ta, tb, p.C, p.M, p.N, p.K, z, g, err, st); break;
+    case 32: launch_g<32, 2, 2, false>(ta, tb, p.C, p.M, p.N, p.K, z, g, err, st); break;
+    default: launch_g<16, 2, 2, false>(ta, tb, p.C, p.M, p.N, p.K, z, g, err, st); break;
   }
   return true;
 }

@@ -14,4 +14,20 @@ bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, co
 bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
                          long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
                          cudaStream_t st, bool b_n_contiguous = false);
+// False when the tensor-core kernels are switched off (CATGRAD_B200_NO_TCGEN05) or the driver entry point is missing.
+bool tcgen05_available();
+// A batch of products laid out as outer x heads (attention): product (o, h) multiplies
+//   A + o*a_outer + h*a_head           rows a_row apart, K contiguous, M rows
+//   B + o*b_outer + (h/b_div)*b_head   K-major: N rows b_row apart, K contiguous; or, with b_n_contiguous, K rows
+//                                      b_row apart with N contiguous.  Grouped heads (b_div > 1) share it.
+// into C + o*c_outer + h*c_head, rows ldc apart.  Strides are in elements and must be multiples of 8 (16 bytes).
+// Rows/columns outside M, N, K are zero-filled on the way in, so K need not be a multiple of the tile.
+struct GroupedGemm {
+  const void* A; long long a_row, a_head, a_outer;
+  const void* B; long long b_row, b_head, b_outer; bool b_n_contiguous;
+  void* C; long long ldc, c_head, c_outer;
+  long long M, N, K, heads, outer, b_div;
+};
+// Returns false (nothing launched) when the layout does not fit the tensor-core kernel.
+bool launch_tcgen05_gemm_grouped(const GroupedGemm& p, unsigned* err, cudaStream_t st);
 }  // namespace cgk

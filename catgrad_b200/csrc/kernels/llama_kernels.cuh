@@ -703,11 +703,12 @@ __global__ void __launch_bounds__(256) attn_decode_warp_kernel(AttnArgs a, unsig
 // Row r = ((b*nh + h)*S + s) of scores [.., S, Tt] (T, in place): x = T(x / scale); x = T(x + mask) where the
 // mask is T(f32::MIN) for keys after position T0+s (in bf16 that is -inf) and -0.0 otherwise; softmax in f32.
 template <class T>
-__global__ void __launch_bounds__(256) softmax_mask_kernel(T* __restrict__ scores, int S, int Tt, int T0, float scale) {
+__global__ void __launch_bounds__(256) softmax_mask_kernel(T* __restrict__ scores, int S, int Tt, int pitch, int T0,
+                                                           float scale) {
   __shared__ float scratch[8];
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* row = reinterpret_cast<float*>(smem_raw);  // [Tt]
-  T* x = scores + (long long)blockIdx.x * Tt;
+  T* x = scores + (long long)blockIdx.x * pitch;
   const int s = blockIdx.x % S;
   const float masked = rt<T>(-FLT_MAX);
   float mx = -FLT_MAX;
@@ -726,6 +727,65 @@ __global__ void __launch_bounds__(256) softmax_mask_kernel(T* __restrict__ score
   }
   sum = block_sum_256(sum, scratch);
   for (int t = threadIdx.x; t < Tt; t += 256) x[t] = Elem<T>::store(row[t] / sum);
+}
+
+// Same for rows that are `pitch` elements apart (pitch a multiple of 16 bytes) and at most 1024 long: one warp per
+// row, the row held in registers, 16-byte loads and stores.  Columns [Tt, pitch) are written as zeros.
+template <class T>
+__global__ void __launch_bounds__(256) softmax_mask_rows_kernel(T* __restrict__ scores, long long rows, int S, int Tt,
+                                                                int pitch, int T0, float scale) {
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int MAXV = 1024 / (32 * VEC);
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  T* x = scores + row * pitch;
+  const int s = (int)(row % S);
+  const float masked = rt<T>(-FLT_MAX);
+  const int nv = (pitch + 32 * VEC - 1) / (32 * VEC);
+  float v[MAXV][VEC];
+  float mx = -FLT_MAX;
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int t0 = (j * 32 + lane) * VEC;
+    if (j < nv && t0 < pitch) {
+      VecT<T, VEC> in = *reinterpret_cast<const VecT<T, VEC>*>(x + t0);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const int t = t0 + i;
+        float y = rt<T>(Elem<T>::load(in.v[i]) / scale);
+        y = rt<T>(y + (t > T0 + s ? masked : -0.0f));
+        y = t < Tt ? y : -FLT_MAX;
+        v[j][i] = y;
+        mx = fmaxf(mx, y);
+      }
+    }
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int t0 = (j * 32 + lane) * VEC;
+    if (j < nv && t0 < pitch) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        float e = t0 + i < Tt ? expf(v[j][i] - mx) : 0.f;
+        v[j][i] = e;
+        sum += e;
+      }
+    }
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int t0 = (j * 32 + lane) * VEC;
+    if (j < nv && t0 < pitch) {
+      VecT<T, VEC> o;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o.v[i] = Elem<T>::store(v[j][i] / sum);
+      *reinterpret_cast<VecT<T, VEC>*>(x + t0) = o;
+    }
+  }
 }
 
 // out[b, s, h, :] = in[b, h, s, :]  (the transpose(1,2) + reshape after attention, llama.rs:342-344)
