@@ -1,6 +1,6 @@
 """Benchmark of the hot path: greedy Llama decoding (and prefill) through the C ABI.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|c3|c4|tiny]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|c3|c4|c5|tiny|sweep]
 
 One "step" is one decode step of the whole batch (one new token per sequence).
   N = 1  : Llama-3.2-1B shape, bf16, batch 1, 512-token prompt, then K timed decode steps (baseline config 3).
@@ -13,6 +13,10 @@ device); `e2e` is the same loop driven like the reference's runner, one host rou
 ids are copied host->device, the step runs, the new ids are read back (examples/llama/main.rs:1016-1037).
 Weights are synthetic (N(0,0.02), seed 0), prompts are uniform random ids (seed 1); the 2.47 GB of weights read
 per step exceed the 126 MB L2, so no flush is needed between steps.
+
+`--workload c5` (any N in 1, 2, 4, 8): baseline config 5, the Llama-3-8B shape run tensor-parallel over the N ranks
+(q/k/v/gate/up split by rows, o/down by columns, their partial products all-reduced over NVLink by the library's own
+peer-memory kernel), batch 32, 1024-token prompt; weights are drawn on the device, shard by shard.
 
 `--impl reference` times the CPU restatement of the reference's ndarray path (oracle/ndarray_ref.cc,
 single-threaded like the reference's tensor ops) on a bounded sample of the same workload.
@@ -114,10 +118,12 @@ def decode_bytes(cfg, batch, ctx_len):
     return 2 * n_weights + batch * kv_per_tok * ctx_len + batch * kv_per_tok
 
 
-def run_decode_workload(be, cfg, params, batch, prompt_len, steps, warmup, dev_index, e2e_steps=None, name=""):
+def run_decode_workload(be, cfg, params, batch, prompt_len, steps, warmup, dev_index, e2e_steps=None, name="",
+                        comm=None):
     """Prefill, then W warm-up + K timed decode steps (device-resident), then the same through host round trips."""
     P = prompt_len + 2 * (warmup + steps) + 16
-    runner = cb.LlamaRunner(be, cfg, params, cb.Dtype.BF16, max_batch=batch, max_positions=P)
+    runner = cb.LlamaRunner(be, cfg, params, cb.Dtype.BF16, max_batch=batch, max_positions=P, comm=comm,
+                            max_tokens=batch * prompt_len)
     prompts = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(batch, prompt_len), dtype=np.uint32)
     res = {}
     # ---- prefill (reported beside the headline) ----
@@ -268,7 +274,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="auto", choices=["auto", "c3", "c4", "tiny", "sweep"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "c3", "c4", "c5", "tiny", "sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-c4", action="store_true", help="N=1 only: do not time the batch-sharded workload as well")
     args = ap.parse_args()
@@ -276,8 +282,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    cfg = cb.TINY if args.workload == "tiny" else cb.LLAMA_1B
-    model_name = "tiny-llama" if args.workload == "tiny" else "Llama-3.2-1B shape"
+    cfg = cb.TINY if args.workload == "tiny" else (cb.LLAMA_8B if args.workload == "c5" else cb.LLAMA_1B)
+    model_name = {"tiny": "tiny-llama", "c5": "Llama-3-8B shape"}.get(args.workload, "Llama-3.2-1B shape")
 
     if args.workload == "sweep":
         # baseline config 2 (op-level sweep); not the headline metric, printed as its own JSON line
@@ -312,21 +318,36 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     be = cb.Backend(local_rank)
-    params, w, load_s = build_model(be, cfg, cb.Dtype.BF16)
     hbm_peak, _, peak_src = measured_peaks()
-
     single = world == 1
     workload = args.workload if args.workload != "auto" else ("c3" if single else "c4")
-    if workload in ("c3", "tiny"):
-        batch_total, prompt_len = 1, (512 if workload == "c3" else 64)
+    tensor_parallel = workload == "c5"
+    comm = None
+    if tensor_parallel:
+        from catgrad_b200 import tp
+        batch_total, prompt_len = 32, 1024
+        batch = batch_total                       # every rank sees the whole batch
+        t0 = time.time()
+        params, w = tp.random_shard_device(be, cfg, rank, world, cb.Dtype.BF16, seed=0), None
+        be.synchronize()
+        load_s = time.time() - t0
+        nbytes = tp.comm_bytes(cfg, batch_total * prompt_len, 2)
+        if dist is not None:
+            comm = tp.connect(be, nbytes)
+        else:
+            comm = tp.TpComm(be, 0, 1, nbytes)
     else:
-        batch_total, prompt_len = 256, 128
-    assert batch_total % world == 0
-    batch = batch_total // world
+        params, w, load_s = build_model(be, cfg, cb.Dtype.BF16)
+        if workload in ("c3", "tiny"):
+            batch_total, prompt_len = 1, (512 if workload == "c3" else 64)
+        else:
+            batch_total, prompt_len = 256, 128
+        assert batch_total % world == 0
+        batch = batch_total // world
 
     if dist is not None:
         dist.barrier()
-    r = run_decode_workload(be, cfg, params, batch, prompt_len, args.steps, args.warmup, local_rank)
+    r = run_decode_workload(be, cfg, params, batch, prompt_len, args.steps, args.warmup, local_rank, comm=comm)
     ms, e2e_ms, pre_ms = r["ms"], r["e2e_ms"], r["prefill_ms"]
     if dist is not None:
         import torch
@@ -345,7 +366,14 @@ def main():
     tok_per_step = batch_total
     value = tok_per_step * args.steps / (ms / 1e3)
     e2e_value = tok_per_step * r["e2e_steps"] / (e2e_ms / 1e3)
-    bytes_step = decode_bytes(cfg, batch, r["ctx_mid"])
+    if tensor_parallel:
+        # per GPU: its share of the layer weights + the replicated embedding row gather (negligible) and lm_head,
+        # its share of the KV cache (heads are split)
+        layer_params = cfg.num_params() - 2 * cfg.vocab_size * cfg.hidden_size
+        kv_per_tok = 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim * 2 // world
+        bytes_step = 2 * (layer_params // world + cfg.vocab_size * cfg.hidden_size) + batch * kv_per_tok * (r["ctx_mid"] + 1)
+    else:
+        bytes_step = decode_bytes(cfg, batch, r["ctx_mid"])
     achieved = bytes_step / (ms / args.steps / 1e3) / 1e9
     line = {
         "metric": "decode tokens/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
@@ -353,27 +381,33 @@ def main():
         "scaling": "weak" if single else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{model_name} bf16, {batch_total} sequence(s) x {prompt_len}-token prompt, greedy decode, "
                                f"context {int(r['ctx_mid'] - args.steps / 2)}..{int(r['ctx_mid'] + args.steps / 2)}",
-                   "global_batch": batch_total, "prompt_len": prompt_len, "parallelism": f"batch-sharded x{world}",
-                   "l2": "inputs larger than L2 (2.47 GB of weights per step vs 126 MB)"},
+                   "global_batch": batch_total, "prompt_len": prompt_len,
+                   "parallelism": f"tensor-parallel x{world}" if tensor_parallel else f"batch-sharded x{world}",
+                   "l2": "inputs larger than L2 (weights read per step exceed 126 MB many times over)"},
         "prefill": {"tok_s": batch_total * prompt_len / (pre_ms / 1e3), "ms": pre_ms,
                     "note": "lm_head on the last position of each sequence only"},
-        "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4 * batch, "d2h_bytes_per_step": 4 * batch,
+        "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4 * batch * (world if tensor_parallel else 1),
+                "d2h_bytes_per_step": 4 * batch * (world if tensor_parallel else 1),
                 "steps": r["e2e_steps"], "how": "cg_llama_forward per token with host id buffers (copy in, step, copy out)"},
         "gpu_launches": r["launches"],
         "clocks": r["clocks"],
         "roofline": {"bound": "hbm",
-                     "kernel": "one decode step = its 65 gemv_fused_kernel launches (79 % of the device time, "
-                               "profiles/decode_step_llama1b_bf16_launch_list.md) + attention + greedy pick",
+                     "kernel": ("one decode step of one rank: tcgen05 GEMMs over its weight shard, attention, 64 all-reduces"
+                                if tensor_parallel else
+                                "one decode step = its 65 gemv_fused_kernel launches (79 % of the device time, "
+                                "profiles/decode_step_llama1b_bf16_launch_list.md) + attention + greedy pick"),
                      "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "peak_source": peak_src, "frac_of_8TBs_nominal": achieved / HBM_NOMINAL_GBS,
                      "bytes_per_step": bytes_step,
-                     "how": "algorithmic bytes of a step (every weight once + KV cache read + new KV rows) / CUDA-event "
-                            "time of a step on the launching stream",
+                     "how": "algorithmic bytes of a step on one GPU (every weight it holds once + KV cache read + new KV "
+                            "rows) / CUDA-event time of a step on the launching stream",
                      # dram__bytes_read.sum + dram__bytes_write.sum of the gemv launches of one step, summed from the
                      # ncu capture in profiles/gemv_fused_decode_llama1b_bf16.md (batch 1; weights only)
                      "traffic": TRAFFIC_PER_STEP_B1 if (batch_total == 1 and workload == "c3") else None},
         "load_s": load_s,
     }
+    if tensor_parallel:
+        del comm
     if single and workload == "c3" and not args.skip_c4:
         # the batch-sharded workload on one GPU: the N=1 point of the scaling runs
         c4_steps = min(args.steps, 64)
@@ -381,7 +415,7 @@ def main():
         line["c4"] = {"decode_tok_s": 256 * c4_steps / (r4["ms"] / 1e3), "ms_per_step": r4["ms"] / c4_steps,
                       "prefill_tok_s": r4["prefill_tok_s"], "e2e_tok_s": 256 * r4["e2e_steps"] / (r4["e2e_ms"] / 1e3),
                       "workload": "256 sequences x 128-token prompt on one GPU"}
-    if single and not args.no_cpu_baseline:
+    if single and not args.no_cpu_baseline and not tensor_parallel:
         del params
         wf = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
         line["cpu_baseline"] = cpu_baseline_sample(cfg, wf, prompt_len=8, steps=2)

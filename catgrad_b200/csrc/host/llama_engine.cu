@@ -1014,6 +1014,60 @@ __global__ void flush_kernel(uint4* p, long long n) {
     p[i] = make_uint4((unsigned)i, 0, 0, 0);
 }
 }  // namespace
+}  // extern "C"
+
+namespace {
+// Element i of a synthetic N(0, std) tensor: a hash of (seed, i) gives two uniforms, Box-Muller one normal.  The
+// value depends only on the element's index in the WHOLE matrix, so any slice of it can be produced in place.
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+template <class T>
+__global__ void random_normal_kernel(T* out, long long rows, long long cols, long long row0, long long col0,
+                                     long long full_cols, unsigned long long seed, float std) {
+  const long long n = rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols, c = i - r * cols;
+    const unsigned long long h = mix64(mix64(seed) ^ (unsigned long long)((row0 + r) * full_cols + col0 + c));
+    const float u1 = ((float)(unsigned)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);   // (0, 1)
+    const float u2 = (float)(unsigned)((h >> 8) & 0xFFFFFFu) * (1.0f / 16777216.0f);
+    const float z = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+    out[i] = cgk::Elem<T>::store(z * std);
+  }
+}
+}  // namespace
+
+extern "C" {
+
+// Synthetic weights without a host copy (benchmarks of models too large to draw on the host): a new [rows, cols]
+// tensor holding rows [row0, row0+rows) x columns [col0, col0+cols) of a virtual [*, full_cols] matrix of N(0, std)
+// values determined by `seed`.  Not part of the trait.
+int cg_random_normal(cg_ctx* ctx, uint64_t seed, float std, uint64_t rows, uint64_t cols, uint64_t row0, uint64_t col0,
+                     uint64_t full_cols, int dtype, cg_tensor** out) {
+  CG_API_BEGIN
+  CG_CHECK(ctx && ctx->be && out, ERR_BAD_HANDLE, "null argument");
+  CG_CHECK(dtype == (int)Dtype::F32 || dtype == (int)Dtype::BF16, ERR_UNSUPPORTED_DTYPE, "f32 or bf16");
+  CG_CHECK(rows >= 1 && cols >= 1 && col0 + cols <= full_cols, ERR_INVALID_ARG, "slice outside the matrix");
+  CudaBackend* be = static_cast<CudaBackend*>(ctx->be.get());
+  Tensor t = be->empty({(int64_t)rows, (int64_t)cols}, (Dtype)dtype);
+  const int grid = be->sm_count() * 8;
+  if (dtype == (int)Dtype::F32)
+    random_normal_kernel<float><<<grid, 256, 0, be->stream()>>>((float*)t.raw(), (long long)rows, (long long)cols, (long long)row0,
+                                                               (long long)col0, (long long)full_cols, seed, std);
+  else
+    random_normal_kernel<__nv_bfloat16><<<grid, 256, 0, be->stream()>>>((__nv_bfloat16*)t.raw(), (long long)rows, (long long)cols,
+                                                                       (long long)row0, (long long)col0, (long long)full_cols,
+                                                                       seed, std);
+  be->check_launch("random_normal");
+  cg_tensor* h = new cg_tensor();
+  h->t = t;
+  *out = h;
+  CG_API_END(ctx)
+}
+
 int cg_flush_l2(cg_ctx* ctx, uint64_t bytes) {
   CG_API_BEGIN
   CG_CHECK(ctx && ctx->be, ERR_BAD_HANDLE, "null context");

@@ -48,6 +48,76 @@ def shard_weights(cfg, weights, rank, size):
     return out
 
 
+SHARD_BLOCKS = 8   # a sharded axis is drawn in 8 independent blocks, so every size in {1, 2, 4, 8} sees the same model
+
+
+def _normal_bf16_bits(shape, seed_key, std):
+    """N(0, std) drawn as float32 and rounded to bf16 bit patterns (uint16), ~16 M values at a time."""
+    import zlib
+    rng = np.random.Generator(np.random.SFC64(zlib.crc32(seed_key.encode())))
+    n = int(np.prod(shape))
+    out = np.empty(n, dtype=np.uint16)
+    step = 1 << 24
+    for lo in range(0, n, step):
+        a = rng.standard_normal(min(step, n - lo), dtype=np.float32)
+        a *= np.float32(std)
+        u = a.view(np.uint32)
+        u += np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))
+        out[lo:lo + a.size] = (u >> np.uint32(16)).astype(np.uint16)
+    return out.reshape(shape)
+
+
+def random_shard_bf16(cfg, rank, size, seed=0, std=0.02):
+    """This rank's shard of a random-init bf16 model (bit patterns as uint16; gains are 1.0), generated without ever
+    materialising the whole model: a sharded axis is drawn block by block from seeds that depend only on (seed,
+    key, block), so the ranks of any tensor-parallel size in {1, 2, 4, 8} hold slices of one and the same model."""
+    check_divisible(cfg, size)
+    if SHARD_BLOCKS % size:
+        raise ValueError("tensor-parallel size must divide 8")
+    per = SHARD_BLOCKS // size
+    blocks = range(rank * per, (rank + 1) * per)
+    out = {}
+    for key, shape in cfg.param_shapes():
+        if len(shape) == 1:
+            out[key] = np.full(shape, 0x3F80, dtype=np.uint16)
+        elif key.endswith(ROW_SHARDED):
+            rows = shape[0] // SHARD_BLOCKS
+            out[key] = np.concatenate([_normal_bf16_bits((rows, shape[1]), f"{seed}/{key}/{b}", std) for b in blocks], 0)
+        elif key.endswith(COL_SHARDED):
+            cols = shape[1] // SHARD_BLOCKS
+            out[key] = np.ascontiguousarray(
+                np.concatenate([_normal_bf16_bits((shape[0], cols), f"{seed}/{key}/{b}", std) for b in blocks], 1))
+        else:
+            out[key] = _normal_bf16_bits(shape, f"{seed}/{key}", std)
+    return out
+
+
+def random_shard_device(backend, cfg, rank, size, dtype, seed=0, std=0.02):
+    """Parameters holding this rank's shard of a random-init model, drawn on the device (`cg_random_normal`): each
+    element depends only on (seed, key, its position in the unsharded matrix), so all ranks of any size hold slices
+    of the same model and nothing model-sized ever exists on the host.  Norm gains are 1."""
+    import zlib
+    from .ir import Parameters
+    check_divisible(cfg, size)
+    params = Parameters(backend)
+    for key, shape in cfg.param_shapes():
+        if len(shape) == 1:
+            params[key] = backend.from_numpy(np.ones(shape, dtype=np.float32), dtype)
+            continue
+        rows, cols = shape
+        row0 = col0 = 0
+        if key.endswith(ROW_SHARDED):
+            row0, hi = shard_slice(rows, rank, size)
+            rows = hi - row0
+        elif key.endswith(COL_SHARDED):
+            col0, hi = shard_slice(cols, rank, size)
+            cols = hi - col0
+        tseed = (int(seed) << 32) | zlib.crc32(key.encode())
+        params[key] = backend._out(backend._ns.random_normal, tseed, float(std), rows, cols, row0, col0, shape[1],
+                                   int(dtype))
+    return params
+
+
 def comm_bytes(cfg, max_tokens, element_size):
     """Size of the symmetric data area a tensor-parallel runner needs."""
     one = (max_tokens * cfg.hidden_size * element_size + 255) // 256 * 256

@@ -239,6 +239,12 @@ cg_status cg_event_record(cg_ctx*, int slot /* 0..63 */);
 cg_status cg_event_elapsed_ms(cg_ctx*, int slot_start, int slot_end, float* out_ms);
 /* bytes currently handed out / cached by the context's caching allocator, and launch counter */
 cg_status cg_ctx_stats(cg_ctx*, uint64_t stats[4] /* live bytes, cached bytes, cudaMalloc calls, kernel launches */);
+/* Synthetic weights without a host copy (for models too large to draw on the host): a new [rows, cols] tensor
+ * holding rows [row0, row0+rows) x columns [col0, col0+cols) of a virtual [*, full_cols] matrix of N(0, std)
+ * values determined by `seed` alone, so shards of one matrix can be made independently.  No reference counterpart. */
+cg_status cg_random_normal(cg_ctx*, uint64_t seed, float std, uint64_t rows, uint64_t cols, uint64_t row0,
+                           uint64_t col0, uint64_t full_cols, cg_dtype dtype, cg_tensor** out);
+
 /* Writes `bytes` of device memory on the context's stream (used by benchmarks to evict L2). */
 cg_status cg_flush_l2(cg_ctx*, uint64_t bytes);
 

@@ -69,6 +69,28 @@ def test_allreduce_entry_point_single_rank(gpu):
         comm.allreduce(Dtype.F32, 0, n * 4, 2 * n, residual=True)     # outside the buffer
 
 
+def test_device_drawn_shards_are_slices_of_one_model(gpu):
+    cfg = cb.LlamaConfig(128, 384, 1, 8, 4, 512, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    whole = tp.random_shard_device(gpu, cfg, 0, 1, Dtype.F32, seed=7)
+    for size in (2, 4):
+        shards = [tp.random_shard_device(gpu, cfg, r, size, Dtype.F32, seed=7) for r in range(size)]
+        for key, _ in cfg.param_shapes():
+            full = whole[key].numpy()
+            parts = [s[key].numpy() for s in shards]
+            if key.endswith(tp.ROW_SHARDED):
+                np.testing.assert_array_equal(np.concatenate(parts, 0), full)
+            elif key.endswith(tp.COL_SHARDED):
+                np.testing.assert_array_equal(np.concatenate(parts, 1), full)
+            else:
+                np.testing.assert_array_equal(parts[0], full)
+    g = whole["model.layers.0.mlp.gate_proj.weight"].numpy()
+    assert abs(float(g.std()) - 0.02) < 0.001 and abs(float(g.mean())) < 0.001
+    assert np.unique(g).size > 0.9 * g.size
+    other = tp.random_shard_device(gpu, cfg, 0, 1, Dtype.F32, seed=8)["model.layers.0.mlp.gate_proj.weight"].numpy()
+    assert not np.array_equal(other, g)
+    np.testing.assert_array_equal(whole["model.norm.weight"].numpy(), np.ones(128, dtype=np.float32))
+
+
 def test_peer_that_never_arrives_times_out_and_the_context_survives(gpu):
     """Two communicators of one process on one GPU; only rank 0 ever launches.  Its wait on rank 1's flag (which
     nothing sets) gives up after the 200 ms limit: the next synchronising call reports CG_ERR_TIMEOUT, later calls on

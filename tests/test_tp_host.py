@@ -88,6 +88,25 @@ def test_shard_shapes_and_coverage():
     assert tp.comm_bytes(cfg, 10, 2) == 2 * 2560
 
 
+def test_block_seeded_shards_are_slices_of_one_model():
+    cfg = small_cfg()    # 8 heads / 4 kv heads / FFN 384: every sharded axis divides by 8 blocks
+    whole = tp.random_shard_bf16(cfg, 0, 1, seed=5)
+    for size in (2, 4):
+        shards = [tp.random_shard_bf16(cfg, r, size, seed=5) for r in range(size)]
+        for key, full in whole.items():
+            parts = [s[key] for s in shards]
+            if key.endswith(tp.ROW_SHARDED):
+                np.testing.assert_array_equal(np.concatenate(parts, 0), full)
+            elif key.endswith(tp.COL_SHARDED):
+                np.testing.assert_array_equal(np.concatenate(parts, 1), full)
+                assert parts[0].flags.c_contiguous
+            else:
+                np.testing.assert_array_equal(parts[0], full)
+    q = cb.bf16_bits_to_f32(whole["model.layers.0.mlp.gate_proj.weight"])
+    assert abs(float(q.std()) - 0.02) < 0.002 and abs(float(q.mean())) < 0.002
+    assert whole["model.norm.weight"][0] == 0x3F80
+
+
 def test_indivisible_configs_are_refused():
     cfg = small_cfg()   # 4 kv heads
     with pytest.raises(ValueError):
