@@ -364,8 +364,9 @@ struct Plan {
         a.ctx_len = ctx_len; a.nh = (int)nh; a.nkv = (int)nkv; a.P = (int)m.P; a.scale = scale;
         constexpr int VEC = 16 / sizeof(T);
         const int64_t rep = nh / nkv;
-        if (B * nh >= 4 * (int64_t)sm && rep <= 8) {
-          // many sequences: one warp per query head, one CTA per (kv head, sequence)
+        if (B * nh >= 4 * (int64_t)sm && rep <= 8 && m.host_ctx_len <= 512) {
+          // many sequences with short contexts: one warp per query head, one CTA per (kv head, sequence); long
+          // contexts keep a whole CTA per head (a captured graph keeps the choice made at its first step)
           size_t smem = (size_t)rep * (m.P + 1) * 4 + (size_t)rep * hd * 4 + 2 * hd * sizeof(T);
           dim3 grid((unsigned)nkv, (unsigned)B);
           if (hd == 64) {

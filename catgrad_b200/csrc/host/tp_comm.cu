@@ -142,7 +142,10 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(CommDev c, size_t x_o
       *reinterpret_cast<uint4*>(x_local + (size_t)v * 16) = outv;
     }
   }
-  __threadfence_system();
+  // two-shot: the stores into the peers' x must be visible system-wide before the B flag; one-shot wrote only local
+  // memory, and its reads of the peers' partials completed when their values were consumed
+  if (two_shot) __threadfence_system();
+  else __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
     const unsigned old = atomicAdd(hdr + HDR_DONE, 1u);
@@ -150,7 +153,6 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(CommDev c, size_t x_o
       // every CTA of this launch has read the old sequence number and finished its stores
       atomicExch(hdr + HDR_DONE, 0u);
       st_release_sys(hdr + HDR_SEQ, seq);
-      __threadfence_system();
       for (int p = 0; p < c.size; ++p) st_release_sys(reinterpret_cast<unsigned*>(c.base[p]) + HDR_B + c.rank, seq);
     }
     if (!wait_flags(hdr + HDR_B, seq, c.size, c.wait_ns)) {

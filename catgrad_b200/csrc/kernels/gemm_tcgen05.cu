@@ -28,6 +28,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "gemm_tcgen05.h"
@@ -156,6 +157,18 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- thread-block cluster helpers (split-K: the CTAs of a cluster own consecutive K ranges of one tile) ----
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_cluster_f4(const void* local_smem, unsigned cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_smem)), "r"(cta_rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  return v;
+}
+
 template <int BN>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -174,7 +187,12 @@ struct BatchGeom {
 
 // grid: (ceil(N/BN), ceil(M/BM), batch).  BMODE: 0 = one product, 1/2 = see BatchGeom.  B_MN: the right
 // operand is stored [K, N] with N contiguous (tensor map dims {N, K}); otherwise [N, K] with K contiguous.
-template <int BN, int STAGES, int BMODE, bool B_MN>
+// SPLITK (BMODE 0 only): launched as clusters of gridDim.z CTAs along z; CTA z of a cluster accumulates k-blocks
+// [z*per, (z+1)*per) of the tile into its own TMEM, all CTAs park their f32 partial tile in shared memory, and after
+// a cluster barrier CTA z sums rows [z*128/Z, (z+1)*128/Z) over the cluster in rank order (distributed shared
+// memory reads), rounds once and stores.  A pass over a weight with few row tiles thus fills all SMs without
+// re-reading the activations per narrow column tile, and the result does not depend on timing.
+template <int BN, int STAGES, int BMODE, bool B_MN, bool SPLITK = false>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                                            const __grid_constant__ CUtensorMap tmB,
                                                            __nv_bfloat16* __restrict__ C, int M, int N, int K,
@@ -192,7 +210,13 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, bz = blockIdx.z;
   const int zo = BMODE == 2 ? bz / g.heads : 0, zh = BMODE == 2 ? bz % g.heads : 0;
-  const int num_k = (K + BK - 1) / BK;
+  const int num_k_total = (K + BK - 1) / BK;
+  int k_first = 0, num_k = num_k_total;
+  if (SPLITK) {
+    const int per = (num_k_total + (int)gridDim.z - 1) / (int)gridDim.z;
+    k_first = bz * per;
+    num_k = num_k_total - k_first < per ? num_k_total - k_first : per;   // the host keeps every range non-empty
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -223,21 +247,22 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
       unsigned char* a_dst = smem + s * L::STAGE_BYTES;
       unsigned char* b_dst = a_dst + L::A_BYTES;
       mbar_expect_tx(&full[s], L::STAGE_BYTES);
-      if (BMODE == 2) tma_load_4d(a_dst, &tmA, &full[s], k * BK, m0, zh, zo);
-      else if (BMODE == 1) tma_load_3d(a_dst, &tmA, &full[s], k * BK, m0, bz);
-      else tma_load_2d(a_dst, &tmA, &full[s], k * BK, m0);
+      const int kx = (k_first + k) * BK;
+      if (BMODE == 2) tma_load_4d(a_dst, &tmA, &full[s], kx, m0, zh, zo);
+      else if (BMODE == 1) tma_load_3d(a_dst, &tmA, &full[s], kx, m0, bz);
+      else tma_load_2d(a_dst, &tmA, &full[s], kx, m0);
       if (B_MN) {
         // one 64-column x BK-row box per 64 columns of the tile
 #pragma unroll
         for (int nb = 0; nb < BN / 64; ++nb) {
-          if (BMODE == 2) tma_load_4d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, k * BK, zh / g.b_div, zo);
-          else if (BMODE == 1) tma_load_3d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, k * BK, bz);
-          else tma_load_2d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, k * BK);
+          if (BMODE == 2) tma_load_4d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, kx, zh / g.b_div, zo);
+          else if (BMODE == 1) tma_load_3d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, kx, bz);
+          else tma_load_2d(b_dst + nb * (BK * 128), &tmB, &full[s], n0 + nb * 64, kx);
         }
       } else {
-        if (BMODE == 2) tma_load_4d(b_dst, &tmB, &full[s], k * BK, n0, zh / g.b_div, zo);
-        else if (BMODE == 1) tma_load_3d(b_dst, &tmB, &full[s], k * BK, n0, bz);
-        else tma_load_2d(b_dst, &tmB, &full[s], k * BK, n0);
+        if (BMODE == 2) tma_load_4d(b_dst, &tmB, &full[s], kx, n0, zh / g.b_div, zo);
+        else if (BMODE == 1) tma_load_3d(b_dst, &tmB, &full[s], kx, n0, bz);
+        else tma_load_2d(b_dst, &tmB, &full[s], kx, n0);
       }
       issued = k + 1;
     }
@@ -276,7 +301,22 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
     bool ok = mbar_wait(tmem_full, 0, abort_flag);
     // all lanes of the warp must agree before the warp-collective tcgen05.ld
     ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    if (ok && SPLITK) {
+      // park the f32 partial tile in the (now idle) operand ring: row r at r * (BN + 4) floats
+      tc_fence_after();
+      const int q = warp & 3;
+      float* prow = reinterpret_cast<float*>(smem) + (size_t)(q * 32 + lane) * (BN + 4);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          *reinterpret_cast<float4*>(prow + c0 + v * 4) = make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
+                                                                     __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
+      }
+    } else if (ok) {
       tc_fence_after();
       const int q = warp & 3;
       const int row = m0 + q * 32 + lane;
@@ -314,6 +354,38 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
   if (*abort_flag && threadIdx.x == 0) atomicOr(err, DEV_ERR_WAIT_TIMEOUT);
   tc_fence_before();
   __syncthreads();
+  if (SPLITK) {
+    // every thread of every CTA of the cluster passes both barriers, whatever happened before
+    cluster_sync_all();
+    const int Z = (int)gridDim.z;
+    const int rows_per = BM / Z;
+    if (warp >= 2 && !*abort_flag) {
+      const int t = threadIdx.x - 64;  // 0..127
+      const bool vec_ok = (g.ldc % 4 == 0) && (((uintptr_t)C & 7) == 0);
+      for (int item = t; item < rows_per * (BN / 4); item += 128) {
+        const int rr = bz * rows_per + item / (BN / 4), c4 = (item % (BN / 4)) * 4;
+        const float* src = reinterpret_cast<const float*>(smem) + (size_t)rr * (BN + 4) + c4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int pz = 0; pz < Z; ++pz) {
+          const float4 v = ld_cluster_f4(src, (unsigned)pz);
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int row = m0 + rr, col = n0 + c4;
+        if (row < M && col < N) {
+          __nv_bfloat16* dst = C + (long long)row * g.ldc + col;
+          if (vec_ok && col + 4 <= N) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          } else {
+            const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+            for (int j = 0; j < 4; ++j)
+              if (col + j < N) dst[j] = __float2bfloat16_rn(a4[j]);
+          }
+        }
+      }
+    }
+    cluster_sync_all();  // peers may still be reading this CTA's partial tile
+  }
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
   }
@@ -457,6 +529,41 @@ void launch_g(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M
   kern<<<grid, 192, smem, st>>>(ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, g, err);
 }
 
+// Split-K launch: grid (N tiles, M tiles, splits) in clusters of (1, 1, splits).
+template <int BN, int STAGES>
+bool launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K, int splits,
+                   unsigned* err, cudaStream_t st) {
+  using L = SmemLayout<BN>;
+  static_assert((size_t)STAGES * L::STAGE_BYTES >= (size_t)BM * (BN + 4) * 4, "partial tile must fit in the operand ring");
+  size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, 0, false, true>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  BatchGeom g;
+  g.heads = 1;
+  g.b_div = 1;
+  g.c_outer = 0;
+  g.c_inner = 0;
+  g.ldc = (int)N;
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)splits);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned)splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, g, err) == cudaSuccess;
+}
+
 // contiguous C[batch, M, N]
 template <int BN, int STAGES, bool BATCHED, bool B_MN = false>
 void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K,
@@ -504,6 +611,25 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
       default: b3 ? launch_t<64, 8, true, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<64, 8, false, true>(ta, tb, C, p.M, N, K, 1, err, st); break;
     }
     return true;
+  }
+  // One or two row tiles and too few 128-wide column tiles to fill the GPU: split K over a cluster instead of
+  // cutting the columns finer (narrow tiles re-read the activations once per tile).
+  static const bool no_splitk = std::getenv("CATGRAD_B200_NO_SPLITK") != nullptr;
+  if (streaming && !no_splitk && p.batch == 1 && N >= 64) {
+    const long long num_k = (K + BK - 1) / BK;
+    int sbn = 128;
+    if (N < 128 || mtiles * ((N + 127) / 128) * 8 < (3ll * sm_count) / 5) sbn = 64;
+    const long long tiles = mtiles * ((N + sbn - 1) / sbn);
+    int splits = 1;
+    while (splits < 8 && tiles * splits * 2 <= (long long)sm_count + sm_count / 8 && num_k / (splits * 2) >= 2) splits *= 2;
+    // every CTA of the cluster needs a non-empty K range
+    while (splits > 1 && (long long)(splits - 1) * ((num_k + splits - 1) / splits) >= num_k) splits /= 2;
+    if (splits > 1 && make_map(&ta, A, K, p.M, lda, 1, 0, BM) && make_map(&tb, B, K, N, ldb, 1, 0, sbn)) {
+      const bool launched = sbn == 128 ? launch_splitk<128, 6>(ta, tb, C, p.M, N, K, splits, err, st)
+                                       : launch_splitk<64, 8>(ta, tb, C, p.M, N, K, splits, err, st);
+      if (launched) return true;
+      cudaGetLastError();  // cluster launch refused: fall through to the plain tiles
+    }
   }
   if (bn > N) bn = N >= 256 ? 256 : (N >= 128 ? 128 : (N >= 64 ? 64 : (N >= 32 ? 32 : 16)));
   if (!make_map(&ta, A, K, p.M, lda, p.batch, p.a_bs, BM) || !make_map(&tb, B, K, N, ldb, p.batch, p.b_bs, bn)) return false;

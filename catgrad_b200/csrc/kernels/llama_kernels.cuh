@@ -730,7 +730,9 @@ __global__ void __launch_bounds__(256) softmax_mask_kernel(T* __restrict__ score
 }
 
 // Same for rows that are `pitch` elements apart (pitch a multiple of 16 bytes) and at most 1024 long: one warp per
-// row, the row held in registers, 16-byte loads and stores.  Columns [Tt, pitch) are written as zeros.
+// row, the row held in registers, 16-byte loads and stores.  Columns [Tt, pitch) are written as zeros.  Used for
+// bf16 only: the divisions and the exponential are the fast (~2 ulp of f32) forms, far below the bf16 rounding that
+// follows; with the IEEE forms this kernel is bound by the special-function and divide sequences, not by HBM.
 template <class T>
 __global__ void __launch_bounds__(256) softmax_mask_rows_kernel(T* __restrict__ scores, long long rows, int S, int Tt,
                                                                 int pitch, int T0, float scale) {
@@ -753,7 +755,7 @@ __global__ void __launch_bounds__(256) softmax_mask_rows_kernel(T* __restrict__ 
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
         const int t = t0 + i;
-        float y = rt<T>(Elem<T>::load(in.v[i]) / scale);
+        float y = rt<T>(__fdividef(Elem<T>::load(in.v[i]), scale));
         y = rt<T>(y + (t > T0 + s ? masked : -0.0f));
         y = t < Tt ? y : -FLT_MAX;
         v[j][i] = y;
@@ -769,20 +771,21 @@ __global__ void __launch_bounds__(256) softmax_mask_rows_kernel(T* __restrict__ 
     if (j < nv && t0 < pitch) {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        float e = t0 + i < Tt ? expf(v[j][i] - mx) : 0.f;
+        float e = t0 + i < Tt ? __expf(v[j][i] - mx) : 0.f;
         v[j][i] = e;
         sum += e;
       }
     }
   }
   sum = warp_sum(sum);
+  const float inv = 1.0f / sum;
 #pragma unroll
   for (int j = 0; j < MAXV; ++j) {
     const int t0 = (j * 32 + lane) * VEC;
     if (j < nv && t0 < pitch) {
       VecT<T, VEC> o;
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) o.v[i] = Elem<T>::store(v[j][i] / sum);
+      for (int i = 0; i < VEC; ++i) o.v[i] = Elem<T>::store(v[j][i] * inv);
       *reinterpret_cast<VecT<T, VEC>*>(x + t0) = o;
     }
   }
