@@ -203,6 +203,46 @@ struct Plan {
     launched("add");
   }
 
+  // Decode attention with one warp per (kv head, sequence): taken when that alone gives every SM four warps or
+  // more, for bf16, GQA groups of 1/2/4/8 and contexts up to 512 (a captured graph keeps the choice of its first step).
+  template <int HD, int REP>
+  void group_attention_launch(const cgk::AttnArgs& a, int64_t B, int64_t nkv, unsigned* err) {
+    size_t per_warp = (size_t)2 * HD * sizeof(T) + (size_t)REP * HD * 4 + (size_t)REP * (m.P + 1) * 4;
+    per_warp = (per_warp + 15) / 16 * 16;
+    size_t smem = 4 * per_warp;
+    auto kern = cgk::attn_decode_group_kernel<__nv_bfloat16, HD, REP>;
+    static size_t smem_set = 0;
+    if (smem > 48 * 1024 && smem > smem_set) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      smem_set = smem;
+    }
+    launch(kern, dim3((unsigned)((nkv + 3) / 4), (unsigned)B), dim3(128), smem, a, err);
+  }
+  bool launch_group_attention(const cgk::AttnArgs& a, int64_t B, int64_t nkv, int64_t rep, int64_t hd, unsigned* err) {
+    if (!std::is_same<T, __nv_bfloat16>::value) return false;
+    if (B * nkv < 4 * (int64_t)sm || m.host_ctx_len > 512) return false;
+    const size_t per_warp = (size_t)2 * hd * 2 + (size_t)rep * hd * 4 + (size_t)rep * (m.P + 1) * 4 + 16;
+    if (4 * per_warp > 200 * 1024) return false;
+    if (hd == 64) {
+      switch (rep) {
+        case 1: group_attention_launch<64, 1>(a, B, nkv, err); return true;
+        case 2: group_attention_launch<64, 2>(a, B, nkv, err); return true;
+        case 4: group_attention_launch<64, 4>(a, B, nkv, err); return true;
+        case 8: group_attention_launch<64, 8>(a, B, nkv, err); return true;
+        default: return false;
+      }
+    }
+    if (hd == 128) {
+      switch (rep) {
+        case 1: group_attention_launch<128, 1>(a, B, nkv, err); return true;
+        case 2: group_attention_launch<128, 2>(a, B, nkv, err); return true;
+        case 4: group_attention_launch<128, 4>(a, B, nkv, err); return true;
+        default: return false;
+      }
+    }
+    return false;
+  }
+
   // x += sum over the tensor-parallel ranks of the partial product in `tmp` (both live in the symmetric buffer)
   void reduce_partials(int64_t n) {
     m.comm->allreduce(m.dt, 0, m.comm_part_off, n, /*residual=*/true, sm, st, m.be->dev_err());
@@ -364,7 +404,9 @@ struct Plan {
         a.ctx_len = ctx_len; a.nh = (int)nh; a.nkv = (int)nkv; a.P = (int)m.P; a.scale = scale;
         constexpr int VEC = 16 / sizeof(T);
         const int64_t rep = nh / nkv;
-        if (B * nh >= 4 * (int64_t)sm && rep <= 8 && m.host_ctx_len <= 512) {
+        if (launch_group_attention(a, B, nkv, rep, hd, err)) {
+          // one warp per (kv head, sequence)
+        } else if (B * nh >= 4 * (int64_t)sm && rep <= 8 && m.host_ctx_len <= 512) {
           // many sequences with short contexts: one warp per query head, one CTA per (kv head, sequence); long
           // contexts keep a whole CTA per head (a captured graph keeps the choice made at its first step)
           size_t smem = (size_t)rep * (m.P + 1) * 4 + (size_t)rep * hd * 4 + 2 * hd * sizeof(T);

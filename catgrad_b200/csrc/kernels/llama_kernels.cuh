@@ -699,6 +699,162 @@ __global__ void __launch_bounds__(256) attn_decode_warp_kernel(AttnArgs a, unsig
   *reinterpret_cast<VecT<T, DPL>*>((T*)a.out + (long long)b * a.out_row_stride + h * HD + d0) = ov;
 }
 
+// ---- decode attention for very many sequences: one warp per (kv head, sequence), all its query heads --------
+// Same sub-graph and rounding points again.  Each K row is loaded once into registers and dotted with the REP query
+// heads of the group; in the P.v pass a lane owns 8 head-dim elements of every (32 / (HD/8))-th key, so every load
+// is 16 bytes and a warp keeps 4 KB in flight.  No block-level synchronisation: a warp is self-contained.
+template <class T, int HD, int REP>
+__global__ void __launch_bounds__(128) attn_decode_group_kernel(AttnArgs a, unsigned* err) {
+  static_assert(sizeof(T) == 2, "16-byte rows of 8 elements");
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int CH = HD / 8;    // 16-byte chunks per K/V row
+  constexpr int KG = 32 / CH;   // keys covered by one warp-wide load in the P.v pass
+  constexpr int half = HD / 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.x * 4 + warp, b = blockIdx.y;
+  // per warp: k_new[HD] T | v_new[HD] T | q[REP][HD] f32 | p[REP][P + 1] f32
+  const size_t per_warp = (size_t)2 * HD * sizeof(T) + (size_t)REP * HD * 4 + (size_t)REP * (a.P + 1) * 4;
+  unsigned char* base = smem_raw + (size_t)warp * ((per_warp + 15) / 16 * 16);
+  T* k_new = reinterpret_cast<T*>(base);
+  T* v_new = k_new + HD;
+  float* q_s = reinterpret_cast<float*>(v_new + HD);
+  float* p_s = q_s + REP * HD;
+  const int pp = a.P + 1;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (kvh >= a.nkv) return;
+  const int pos = *a.ctx_len;
+  if (pos >= a.P) {
+    if (lane == 0) atomicOr(err, DEV_ERR_INDEX_OOB);
+    return;
+  }
+  const int total = pos + 1;
+  T* kc = (T*)a.kc + ((long long)b * a.nkv + kvh) * a.P * HD;
+  T* vc = (T*)a.vc + ((long long)b * a.nkv + kvh) * a.P * HD;
+  const float* ct = a.cos_t + (long long)pos * half;
+  const float* st = a.sin_t + (long long)pos * half;
+
+  // RoPE of the group's query heads and of the new key; the new value row is copied
+  for (int i = lane; i < REP * half; i += 32) {
+    const int h = i / half, j = i - h * half;
+    const T* qsrc = (const T*)a.q + (long long)b * a.q_row_stride + (kvh * REP + h) * HD;
+    float x1 = Elem<T>::load(qsrc[j]), x2 = Elem<T>::load(qsrc[j + half]);
+    float c = ct[j], sn = st[j];
+    q_s[h * HD + j] = rt<T>(c * x1 + sn * (-x2));
+    q_s[h * HD + j + half] = rt<T>(c * x2 + sn * x1);
+  }
+  {
+    const T* ksrc = (const T*)a.k + (long long)b * a.k_row_stride + kvh * HD;
+    const T* vsrc = (const T*)a.v + (long long)b * a.v_row_stride + kvh * HD;
+    for (int i = lane; i < half; i += 32) {
+      float x1 = Elem<T>::load(ksrc[i]), x2 = Elem<T>::load(ksrc[i + half]);
+      float c = ct[i], sn = st[i];
+      T o1 = Elem<T>::store(c * x1 + sn * (-x2)), o2 = Elem<T>::store(c * x2 + sn * x1);
+      k_new[i] = o1;
+      k_new[i + half] = o2;
+      kc[(long long)pos * HD + i] = o1;
+      kc[(long long)pos * HD + i + half] = o2;
+    }
+    for (int i = lane; i < HD; i += 32) {
+      T vv = vsrc[i];
+      v_new[i] = vv;
+      vc[(long long)pos * HD + i] = vv;
+    }
+  }
+  __syncwarp();
+
+  // scores: lane = key; the row stays in registers for all REP heads
+  float mx[REP];
+#pragma unroll
+  for (int h = 0; h < REP; ++h) mx[h] = -FLT_MAX;
+  for (int t = lane; t < total; t += 32) {
+    const uint4* krow = reinterpret_cast<const uint4*>(t == pos ? k_new : kc + (long long)t * HD);
+    uint4 kr[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) kr[c] = krow[c];
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      float d = 0.f;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const T* e = reinterpret_cast<const T*>(&kr[c]);
+        const float4 qa = *reinterpret_cast<const float4*>(q_s + h * HD + c * 8);
+        const float4 qb = *reinterpret_cast<const float4*>(q_s + h * HD + c * 8 + 4);
+        d = fmaf(qa.x, Elem<T>::load(e[0]), d);
+        d = fmaf(qa.y, Elem<T>::load(e[1]), d);
+        d = fmaf(qa.z, Elem<T>::load(e[2]), d);
+        d = fmaf(qa.w, Elem<T>::load(e[3]), d);
+        d = fmaf(qb.x, Elem<T>::load(e[4]), d);
+        d = fmaf(qb.y, Elem<T>::load(e[5]), d);
+        d = fmaf(qb.z, Elem<T>::load(e[6]), d);
+        d = fmaf(qb.w, Elem<T>::load(e[7]), d);
+      }
+      const float sres = rt<T>(rt<T>(d) / a.scale);
+      p_s[h * pp + t] = sres;
+      mx[h] = fmaxf(mx[h], sres);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < REP; ++h) {
+    const float m = warp_max(mx[h]);
+    float sum = 0.f;
+    for (int t = lane; t < total; t += 32) {
+      const float e = expf(p_s[h * pp + t] - m);
+      p_s[h * pp + t] = e;
+      sum += e;
+    }
+    sum = warp_sum(sum);
+    for (int t = lane; t < total; t += 32) p_s[h * pp + t] = rt<T>(p_s[h * pp + t] / sum);
+  }
+  __syncwarp();
+
+  // P.v: lane = (key group g, chunk c)
+  const int g = lane / CH, c = lane % CH;
+  float acc[REP][8];
+#pragma unroll
+  for (int h = 0; h < REP; ++h)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[h][i] = 0.f;
+#pragma unroll 4
+  for (int t = g; t < pos; t += KG) {
+    const uint4 vv = *reinterpret_cast<const uint4*>(vc + (long long)t * HD + c * 8);
+    const T* e = reinterpret_cast<const T*>(&vv);
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      const float ph = p_s[h * pp + t];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[h][i] = fmaf(ph, Elem<T>::load(e[i]), acc[h][i]);
+    }
+  }
+  if (g == 0) {
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      const float ph = p_s[h * pp + pos];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[h][i] = fmaf(ph, Elem<T>::load(v_new[c * 8 + i]), acc[h][i]);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < REP; ++h)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float v = acc[h][i];
+#pragma unroll
+      for (int o = CH; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      acc[h][i] = v;
+    }
+  if (g == 0) {
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      uint4 ov;
+      T* o = reinterpret_cast<T*>(&ov);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = Elem<T>::store(acc[h][i]);
+      *reinterpret_cast<uint4*>((T*)a.out + (long long)b * a.out_row_stride + (kvh * REP + h) * HD + c * 8) = ov;
+    }
+  }
+}
+
 // ---- prefill: scale + causal mask + softmax over score rows (llama.rs:330-339) ------------------------
 // Row r = ((b*nh + h)*S + s) of scores [.., S, Tt] (T, in place): x = T(x / scale); x = T(x + mask) where the
 // mask is T(f32::MIN) for keys after position T0+s (in bf16 that is -inf) and -0.0 otherwise; softmax in f32.

@@ -100,16 +100,17 @@ def test_many_sequences_use_the_warp_per_head_attention_and_match_solo_runs(gpu)
         assert helpers.rel_err(solo.last_logits()[0], logits[b]) <= REL_F32
 
 
-def test_many_sequences_bf16_gqa(gpu):
-    """Same check in bf16 with grouped heads (4 query heads per kv head share one CTA)."""
+@pytest.mark.parametrize("B", [96, 304])
+def test_many_sequences_bf16_gqa(gpu, B):
+    """Same check in bf16 with grouped heads.  96 sequences: one warp per query head (the 4 heads of a kv head share a
+    CTA); 304 sequences x 2 kv heads: one warp per (kv head, sequence) computing its 4 query heads."""
     cfg, wb, _ = small_bf16_model()
-    B = 96
     ids = np.random.default_rng(6).integers(0, cfg.vocab_size, size=(B, 20), dtype=np.uint32)
     pg = cb.upload_weights(gpu, wb, Dtype.BF16)
     runner = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=B, max_positions=40)
     runner.reset(B)
     tok = runner.forward(ids)
-    picks = (0, 50, 95)
+    picks = (0, 50, B - 1)
     solos = {}
     for b in picks:
         solos[b] = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=1, max_positions=40)
