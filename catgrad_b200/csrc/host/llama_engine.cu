@@ -174,18 +174,21 @@ struct Plan {
   }
 
   // out[M,N] (row pitch ldo... contiguous) = xin[M,K] (row pitch ldx) @ W[N,K]^T
-  void gemm(const void* xin, int64_t ldx, const void* W, void* out, int64_t M, int64_t N, int64_t K) {
+  // With `res`: res[M,N] += T(xin @ W^T) (the residual add of a block), through `scratch` when the add cannot ride
+  // in the GEMM epilogue.
+  void gemm(const void* xin, int64_t ldx, const void* W, void* out, int64_t M, int64_t N, int64_t K, void* res = nullptr) {
     cgk::View4 bt;
     std::memset(&bt, 0, sizeof(bt));
     bt.rank = 0;
     bt.total = 1;
     if (std::is_same<T, __nv_bfloat16>::value && cgk::tcgen05_gemm_applicable(bt, 1, xin, W, M, N, K, ldx, 1, 1, K) &&
-        cgk::launch_tcgen05_gemm(bt, 1, xin, W, out, M, N, K, ldx, K, m.be->dev_err(), sm, st)) {
+        cgk::launch_tcgen05_gemm(bt, 1, xin, W, res ? res : out, M, N, K, ldx, K, m.be->dev_err(), sm, st, false, res)) {
       launched("gemm(tcgen05)");
       return;
     }
     cgk::launch_matmul((int)m.dt, bt, 1, xin, W, out, M, N, K, ldx, 1, 1, K, sm, st);
     launched("gemm");
+    if (res) add_inplace(res, out, M * N);
   }
 
   int grid_for(long long items) {
@@ -472,8 +475,7 @@ struct Plan {
           gemv(cgk::PRO_NONE, cgk::EPI_RESIDUAL, a);
         }
       } else {
-        gemm(attn, NQ, w.o, m.tmp.raw(), M, H, NQ);
-        if (!m.comm) add_inplace(x, m.tmp.raw(), M * H);
+        gemm(attn, NQ, w.o, m.tmp.raw(), M, H, NQ, m.comm ? nullptr : x);
       }
       if (m.comm) reduce_partials(M * H);
       // ---- MLP ----
@@ -509,8 +511,7 @@ struct Plan {
           gemv(cgk::PRO_NONE, cgk::EPI_RESIDUAL, a);
         }
       } else {
-        gemm(hbuf, F, w.down, m.tmp.raw(), M, H, F);
-        if (!m.comm) add_inplace(x, m.tmp.raw(), M * H);
+        gemm(hbuf, F, w.down, m.tmp.raw(), M, H, F, m.comm ? nullptr : x);
       }
       if (m.comm) reduce_partials(M * H);
     }

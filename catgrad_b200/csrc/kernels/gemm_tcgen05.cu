@@ -165,7 +165,8 @@ __device__ __forceinline__ float4 ld_cluster_f4(const void* local_smem, unsigned
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_smem)), "r"(cta_rank));
   float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  // volatile keeps it behind the cluster barrier; no memory clobber, so several of these can be in flight
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote));
   return v;
 }
 
@@ -183,7 +184,18 @@ struct BatchGeom {
   int heads, b_div;
   long long c_outer, c_inner;
   int ldc;
+  // optional residual with C's layout (may alias C): C = bf16(res + bf16(acc)), the `x + linear(...)` of a block
+  const __nv_bfloat16* res;
 };
+
+// bf16(r + bf16(a)) for two neighbouring elements
+__device__ __forceinline__ uint32_t add_res2(float a0, float a1, uint32_t r) {
+  const __nv_bfloat162 rv = *reinterpret_cast<const __nv_bfloat162*>(&r);
+  const __nv_bfloat162 av = __floats2bfloat162_rn(a0, a1);
+  const __nv_bfloat162 o = __floats2bfloat162_rn(__bfloat162float(rv.x) + __bfloat162float(av.x),
+                                                 __bfloat162float(rv.y) + __bfloat162float(av.y));
+  return *reinterpret_cast<const uint32_t*>(&o);
+}
 
 // grid: (ceil(N/BN), ceil(M/BM), batch).  BMODE: 0 = one product, 1/2 = see BatchGeom.  B_MN: the right
 // operand is stored [K, N] with N contiguous (tensor map dims {N, K}); otherwise [N, K] with K contiguous.
@@ -195,7 +207,7 @@ struct BatchGeom {
 template <int BN, int STAGES, int BMODE, bool B_MN, bool SPLITK = false>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                                            const __grid_constant__ CUtensorMap tmB,
-                                                           __nv_bfloat16* __restrict__ C, int M, int N, int K,
+                                                           __nv_bfloat16* C, int M, int N, int K,
                                                            BatchGeom g, unsigned* err) {
   using L = SmemLayout<BN>;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // allocations are powers of two >= 32 columns
@@ -322,8 +334,10 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
       const int row = m0 + q * 32 + lane;
       const long long c_off = BMODE == 2 ? (long long)zo * g.c_outer + (long long)zh * g.c_inner : (long long)bz * g.c_outer;
       __nv_bfloat16* crow = C + c_off + (long long)row * g.ldc;
+      const __nv_bfloat16* rrow = g.res ? g.res + c_off + (long long)row * g.ldc : nullptr;
       // 16-byte stores need every row start and every 32-column group aligned
-      const bool vec_ok = (g.ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (g.c_outer % 8 == 0) && (g.c_inner % 8 == 0);
+      const bool vec_ok = (g.ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (((uintptr_t)g.res & 15) == 0) &&
+                          (g.c_outer % 8 == 0) && (g.c_inner % 8 == 0);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -336,16 +350,28 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint32_t w[4];
+              if (rrow) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + col + v * 8);
+                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
-                w[j] = *reinterpret_cast<uint32_t*>(&h);
+                for (int j = 0; j < 4; ++j)
+                  w[j] = add_res2(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]), rw[j]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+                  w[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
               }
               *reinterpret_cast<uint4*>(crow + col + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
           } else {
             for (int j = 0; j < width; ++j)
-              if (col + j < N) crow[col + j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+              if (col + j < N) {
+                __nv_bfloat16 o = __float2bfloat16_rn(__uint_as_float(r[j]));
+                if (rrow) o = __float2bfloat16_rn(__bfloat162float(rrow[col + j]) + __bfloat162float(o));
+                crow[col + j] = o;
+              }
           }
         }
       }
@@ -365,21 +391,34 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
       for (int item = t; item < rows_per * (BN / 4); item += 128) {
         const int rr = bz * rows_per + item / (BN / 4), c4 = (item % (BN / 4)) * 4;
         const float* src = reinterpret_cast<const float*>(smem) + (size_t)rr * (BN + 4) + c4;
+        float4 part[8];
+#pragma unroll
+        for (int pz = 0; pz < 8; ++pz)
+          if (pz < Z) part[pz] = ld_cluster_f4(src, (unsigned)pz);   // all loads issued before the first use
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int pz = 0; pz < Z; ++pz) {
-          const float4 v = ld_cluster_f4(src, (unsigned)pz);
-          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
+#pragma unroll
+        for (int pz = 0; pz < 8; ++pz)
+          if (pz < Z) { acc.x += part[pz].x; acc.y += part[pz].y; acc.z += part[pz].z; acc.w += part[pz].w; }
         const int row = m0 + rr, col = n0 + c4;
         if (row < M && col < N) {
           __nv_bfloat16* dst = C + (long long)row * g.ldc + col;
-          if (vec_ok && col + 4 <= N) {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-            *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          const __nv_bfloat16* rsrc = g.res ? g.res + (long long)row * g.ldc + col : nullptr;
+          if (vec_ok && col + 4 <= N && (((uintptr_t)g.res & 7) == 0)) {
+            if (rsrc) {
+              const uint2 rv = *reinterpret_cast<const uint2*>(rsrc);
+              *reinterpret_cast<uint2*>(dst) = make_uint2(add_res2(acc.x, acc.y, rv.x), add_res2(acc.z, acc.w, rv.y));
+            } else {
+              __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+              *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            }
           } else {
             const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
             for (int j = 0; j < 4; ++j)
-              if (col + j < N) dst[j] = __float2bfloat16_rn(a4[j]);
+              if (col + j < N) {
+                __nv_bfloat16 o = __float2bfloat16_rn(a4[j]);
+                if (rsrc) o = __float2bfloat16_rn(__bfloat162float(rsrc[j]) + __bfloat162float(o));
+                dst[j] = o;
+              }
           }
         }
       }
@@ -532,7 +571,7 @@ void launch_g(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M
 // Split-K launch: grid (N tiles, M tiles, splits) in clusters of (1, 1, splits).
 template <int BN, int STAGES>
 bool launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K, int splits,
-                   unsigned* err, cudaStream_t st) {
+                   const void* res, unsigned* err, cudaStream_t st) {
   using L = SmemLayout<BN>;
   static_assert((size_t)STAGES * L::STAGE_BYTES >= (size_t)BM * (BN + 4) * 4, "partial tile must fit in the operand ring");
   size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
@@ -548,6 +587,7 @@ bool launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long l
   g.c_outer = 0;
   g.c_inner = 0;
   g.ldc = (int)N;
+  g.res = (const __nv_bfloat16*)res;
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)splits);
@@ -567,13 +607,14 @@ bool launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long l
 // contiguous C[batch, M, N]
 template <int BN, int STAGES, bool BATCHED, bool B_MN = false>
 void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K,
-              long long batch, unsigned* err, cudaStream_t st) {
+              long long batch, unsigned* err, cudaStream_t st, const void* res = nullptr) {
   BatchGeom g;
   g.heads = 1;
   g.b_div = 1;
   g.c_outer = M * N;
   g.c_inner = 0;
   g.ldc = (int)N;
+  g.res = (const __nv_bfloat16*)res;
   launch_g<BN, STAGES, BATCHED ? 1 : 0, B_MN>(ta, tb, C, M, N, K, batch, g, err, st);
 }
 }  // namespace
@@ -587,7 +628,7 @@ bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, co
 
 bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
                          long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
-                         cudaStream_t st, bool b_n_contiguous) {
+                         cudaStream_t st, bool b_n_contiguous, const void* residual) {
   Problem p = b_n_contiguous ? analyse(bt, batch, A, B, M, N, K, lda, 1, ldb, 1) : analyse(bt, batch, A, B, M, N, K, lda, 1, 1, ldb);
   if (!p.ok) return false;
   CUtensorMap ta, tb;
@@ -602,6 +643,7 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
   int bn = 256;
   while (bn > min_bn && mtiles * ((N + bn - 1) / bn) < want) bn >>= 1;
   if (p.b_mn) {
+    if (residual) return false;
     if (bn < 64) bn = 64;
     if (!make_map(&ta, A, K, p.M, lda, p.batch, p.a_bs, BM) || !make_map_mn(&tb, B, K, N, ldb, p.batch, p.b_bs)) return false;
     const bool b3 = p.batch > 1;
@@ -625,8 +667,8 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
     // every CTA of the cluster needs a non-empty K range
     while (splits > 1 && (long long)(splits - 1) * ((num_k + splits - 1) / splits) >= num_k) splits /= 2;
     if (splits > 1 && make_map(&ta, A, K, p.M, lda, 1, 0, BM) && make_map(&tb, B, K, N, ldb, 1, 0, sbn)) {
-      const bool launched = sbn == 128 ? launch_splitk<128, 6>(ta, tb, C, p.M, N, K, splits, err, st)
-                                       : launch_splitk<64, 8>(ta, tb, C, p.M, N, K, splits, err, st);
+      const bool launched = sbn == 128 ? launch_splitk<128, 6>(ta, tb, C, p.M, N, K, splits, residual, err, st)
+                                       : launch_splitk<64, 8>(ta, tb, C, p.M, N, K, splits, residual, err, st);
       if (launched) return true;
       cudaGetLastError();  // cluster launch refused: fall through to the plain tiles
     }
@@ -635,11 +677,11 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
   if (!make_map(&ta, A, K, p.M, lda, p.batch, p.a_bs, BM) || !make_map(&tb, B, K, N, ldb, p.batch, p.b_bs, bn)) return false;
   const bool bt3 = p.batch > 1;
   switch (bn) {
-    case 256: bt3 ? launch_t<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
-    case 128: bt3 ? launch_t<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
-    case 64: bt3 ? launch_t<64, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<64, 8, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
-    case 32: bt3 ? launch_t<32, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<32, 5, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
-    default: bt3 ? launch_t<16, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<16, 5, false>(ta, tb, C, p.M, N, K, 1, err, st); break;
+    case 256: bt3 ? launch_t<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual) : launch_t<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, st, residual); break;
+    case 128: bt3 ? launch_t<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual) : launch_t<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, st, residual); break;
+    case 64: bt3 ? launch_t<64, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual) : launch_t<64, 8, false>(ta, tb, C, p.M, N, K, 1, err, st, residual); break;
+    case 32: bt3 ? launch_t<32, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual) : launch_t<32, 5, false>(ta, tb, C, p.M, N, K, 1, err, st, residual); break;
+    default: bt3 ? launch_t<16, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual) : launch_t<16, 5, false>(ta, tb, C, p.M, N, K, 1, err, st, residual); break;
   }
   return true;
 }
@@ -664,6 +706,7 @@ bool launch_tcgen05_gemm_grouped(const GroupedGemm& p, unsigned* err, cudaStream
   g.c_outer = p.c_outer;
   g.c_inner = p.c_head;
   g.ldc = (int)p.ldc;
+  g.res = nullptr;
   const long long z = (long long)p.heads * p.outer;
   CUtensorMap ta, tb;
   if (!make_map4(&ta, p.A, p.K, p.M, p.heads, p.outer, p.a_row, p.a_head, p.a_outer, BM)) return false;
