@@ -32,6 +32,9 @@ namespace {
 
 struct LayerW {
   const void *in_norm, *q, *k, *v, *o, *post_norm, *gate, *up, *down;
+  // stacked copies for the GEMM path (made on its first use): [q; k; v] and [gate; up], so that the three / two
+  // projections of the same input are one product
+  const void *qkv = nullptr, *gate_up = nullptr;
 };
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -52,6 +55,7 @@ struct cg_llama {
   size_t es = 2;
   int64_t max_batch = 0, P = 0;
   std::vector<Tensor> keep;  // parameter tensors kept alive
+  std::vector<Tensor> stacked;  // [q; k; v] and [gate; up] per layer (GEMM path only)
   std::vector<LayerW> layers;
   const void *embed = nullptr, *final_norm = nullptr, *head = nullptr;
 
@@ -386,16 +390,13 @@ struct Plan {
         gemv(cgk::PRO_NORM, cgk::EPI_STORE, a);
       } else {
         rmsnorm(x, w.in_norm, m.xn.raw(), M, H, 1, 0);
-        // q | k | v packed per buffer: [M,NQ] then [M,NKV] then [M,NKV]
-        gemm(m.xn.raw(), H, w.q, qkv, M, NQ, H);
-        gemm(m.xn.raw(), H, w.k, qkv + M * NQ, M, NKV, H);
-        gemm(m.xn.raw(), H, w.v, qkv + M * (NQ + NKV), M, NKV, H);
+        gemm(m.xn.raw(), H, w.qkv, qkv, M, NQKV, H);   // one product over the stacked [q; k; v]
       }
-      const bool packed_rows = gemv_ok(M, H);  // rows interleave q|k|v (pitch NQKV) vs three dense matrices
+      // rows hold q | k | v side by side (pitch NQKV) on both paths
       T* q = qkv;
-      T* k = packed_rows ? qkv + NQ : qkv + M * NQ;
-      T* v = packed_rows ? qkv + NQ + NKV : qkv + M * (NQ + NKV);
-      const int64_t qs = packed_rows ? NQKV : NQ, ks = packed_rows ? NQKV : NKV;
+      T* k = qkv + NQ;
+      T* v = qkv + NQ + NKV;
+      const int64_t qs = NQKV, ks = NQKV;
       T* kcl = (T*)m.kc.raw() + l * m.max_batch * nkv * m.P * hd;
       T* vcl = (T*)m.vc.raw() + l * m.max_batch * nkv * m.P * hd;
       T* attn = (T*)m.attn.raw();
@@ -494,10 +495,8 @@ struct Plan {
         gemv(cgk::PRO_NORM, cgk::EPI_SILU_MUL, a);
       } else {
         rmsnorm(x, w.post_norm, m.xn.raw(), M, H, 1, 0);
-        gemm(m.xn.raw(), H, w.gate, m.g.raw(), M, F, H);
-        gemm(m.xn.raw(), H, w.up, m.u.raw(), M, F, H);
-        cgk::silu_mul_kernel<T><<<grid_for(M * F / (16 / sizeof(T))), 256, 0, st>>>((const T*)m.g.raw(), (const T*)m.u.raw(),
-                                                                                  hbuf, M * F);
+        gemm(m.xn.raw(), H, w.gate_up, m.g.raw(), M, 2 * F, H);   // one product over the stacked [gate; up]
+        cgk::silu_mul_packed_kernel<T><<<grid_for(M * F / (16 / sizeof(T))), 256, 0, st>>>((const T*)m.g.raw(), hbuf, M, (int)F);
         launched("silu_mul");
       }
       if (gemv_ok(M, F)) {
@@ -638,6 +637,32 @@ const Tensor& find_param(const cg_params* p, const std::string& key, Dtype dt, c
   return t;
 }
 
+// The GEMM path multiplies the normed input by [q; k; v] and by [gate; up] in one product each; the stacked
+// matrices are device-side copies made once (the originals, which the caller owns, keep serving the GEMV path).
+void ensure_stacked_weights(cg_llama& m) {
+  if (!m.stacked.empty()) return;
+  const LlamaConfig& c = m.cfg;
+  const int64_t H = c.hidden_size, F = c.intermediate_size, NQ = c.num_attention_heads * m.hd,
+                NKV = c.num_key_value_heads * m.hd;
+  cudaStream_t st = m.be->stream();
+  for (auto& w : m.layers) {
+    Tensor qkv = m.be->empty({NQ + 2 * NKV, H}, m.dt);
+    Tensor gu = m.be->empty({2 * F, H}, m.dt);
+    unsigned char* p = (unsigned char*)qkv.raw();
+    CG_CUDA(cudaMemcpyAsync(p, w.q, (size_t)NQ * H * m.es, cudaMemcpyDeviceToDevice, st));
+    CG_CUDA(cudaMemcpyAsync(p + (size_t)NQ * H * m.es, w.k, (size_t)NKV * H * m.es, cudaMemcpyDeviceToDevice, st));
+    CG_CUDA(cudaMemcpyAsync(p + (size_t)(NQ + NKV) * H * m.es, w.v, (size_t)NKV * H * m.es, cudaMemcpyDeviceToDevice, st));
+    unsigned char* g = (unsigned char*)gu.raw();
+    CG_CUDA(cudaMemcpyAsync(g, w.gate, (size_t)F * H * m.es, cudaMemcpyDeviceToDevice, st));
+    CG_CUDA(cudaMemcpyAsync(g + (size_t)F * H * m.es, w.up, (size_t)F * H * m.es, cudaMemcpyDeviceToDevice, st));
+    w.qkv = qkv.raw();
+    w.gate_up = gu.raw();
+    m.stacked.push_back(qkv);
+    m.stacked.push_back(gu);
+  }
+  CG_CUDA(cudaStreamSynchronize(st));
+}
+
 void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
   const LlamaConfig& c = m.cfg;
   int64_t M = B * S;
@@ -680,9 +705,9 @@ void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
     } else {
       m.tmp = m.be->empty({M, H}, m.dt);
     }
-    if (M > 16 || (size_t)16 * H * m.es > 160 * 1024) {  // gate/up buffers of the GEMM path
-      m.g = m.be->empty({M, F}, m.dt);
-      m.u = m.be->empty({M, F}, m.dt);
+    if (M > 16 || (size_t)16 * H * m.es > 160 * 1024) {  // gate | up buffer of the GEMM path
+      m.g = m.be->empty({M, 2 * F}, m.dt);
+      ensure_stacked_weights(m);
     }
     m.ids_in = m.be->empty({M}, Dtype::U32);
     m.cap_tokens = M;

@@ -986,6 +986,31 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gat
   }
 }
 
+// Same with gate and up side by side in one [rows, 2F] matrix (the output of one GEMM over the stacked weights):
+// gate = gu[r, 0:F], up = gu[r, F:2F]; out is [rows, F].  F is a multiple of 16 bytes.
+template <class T>
+__global__ void __launch_bounds__(256) silu_mul_packed_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows,
+                                                              int F) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int per = F / VEC;
+  const long long total = rows * per;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const long long r = t / per;
+    const int c = (int)(t - r * per) * VEC;
+    VecT<T, VEC> g = *reinterpret_cast<const VecT<T, VEC>*>(gu + r * 2 * F + c);
+    VecT<T, VEC> u = *reinterpret_cast<const VecT<T, VEC>*>(gu + r * 2 * F + F + c);
+    VecT<T, VEC> o;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      float gf = Elem<T>::load(g.v[i]);
+      float sg = 1.f / (1.f + expf(-gf));
+      float si = rt<T>(gf * sg);
+      o.v[i] = Elem<T>::store(si * Elem<T>::load(u.v[i]));
+    }
+    *reinterpret_cast<VecT<T, VEC>*>(out + r * F + c) = o;
+  }
+}
+
 // x = T(x + y)  (residual add for the GEMM path)
 template <class T>
 __global__ void __launch_bounds__(256) add_inplace_kernel(T* __restrict__ x, const T* __restrict__ y, long long n) {

@@ -28,6 +28,36 @@ def test_library_exports_every_declared_symbol():
     _ffi.bind(lib, "cg_")          # every symbol the host wrapper binds exists too
 
 
+def _param_count(arglist):
+    arglist = re.sub(r"/\*.*?\*/", "", arglist, flags=re.S).strip()
+    return 0 if arglist in ("", "void") else arglist.count(",") + 1
+
+
+def test_rust_shim_binds_existing_entry_points_with_matching_arity():
+    """shim/b200.rs cannot be compiled here (no Rust toolchain); at least every `cg_*` function it declares must be
+    exported by the library and take as many arguments as the header says."""
+    hdr = open(os.path.join(ROOT, "include", "catgrad_b200.h")).read()
+    rs = open(os.path.join(ROOT, "shim", "b200.rs")).read()
+    header_args = {m.group(1): _param_count(m.group(2))
+                   for m in re.finditer(r"\b(cg_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", hdr, flags=re.S)}
+    decls = re.findall(r"\bfn (cg_[a-z0-9_]+)\s*\(([^)]*)\)", rs)
+    assert len(decls) >= 45
+    lib = ctypes.CDLL(_ffi.library_path())
+    for name, args in decls:
+        assert hasattr(lib, name), name
+        assert name in header_args, name
+        assert _param_count(args) == header_args[name], (name, args, header_args[name])
+    # all 41 trait methods are implemented
+    trait_methods = ["zeros", "ndarray_from_vec_f32", "ndarray_from_vec_f16", "ndarray_from_vec_bf16",
+                     "ndarray_from_vec_fp8", "ndarray_from_vec_u32", "cast", "matmul", "add", "sub", "mul", "div", "pow",
+                     "lt", "gt", "gte", "lte", "eq", "where_cond", "sin", "cos", "exp", "log", "floor", "round", "neg",
+                     "broadcast", "reshape", "transpose", "max", "sum", "argmax", "topk", "compare", "concat", "index",
+                     "slice", "arange", "to_bool", "to_vec", "format_tensor"]
+    body = rs[rs.index("impl Backend for B200Backend"):]
+    for mth in trait_methods:
+        assert re.search(r"\bfn %s\s*\(" % mth, body), mth
+
+
 def test_no_cpu_fallback():
     """Without a GPU the product refuses to start; nothing silently computes on the host."""
     try:
