@@ -78,6 +78,7 @@ struct cg_llama {
   // activation buffers sized for `cap_tokens` tokens
   int64_t cap_tokens = 0;
   Tensor x, xn, qkv, attn, h, g, u, tmp, scores, attn_bhsd;
+  Tensor attn_scores, attn_partial, attn_counters;  // scratch of the key-split decode attention
   int64_t batch = 0;
   int64_t host_ctx_len = 0;   // mirror of words[0] (all steps are issued by this object)
   uint64_t launches = 0;
@@ -250,6 +251,51 @@ struct Plan {
     return false;
   }
 
+  // Decode attention with the keys split over CTAs (bf16, contexts above 512, GQA groups of 1/2/4/8).
+  template <int HD, int REP>
+  void split_attention_launch(const cgk::AttnSplitArgs& s, int64_t B, int64_t nkv, unsigned* err) {
+    dim3 grid((unsigned)s.chunks_max, (unsigned)nkv, (unsigned)B);
+    launch(cgk::attn_split_scores_kernel<__nv_bfloat16, HD, REP>, grid, dim3(128), 0, s, err);
+    ++m.launches;
+    launch(cgk::attn_split_pv_kernel<__nv_bfloat16, HD, REP>, grid, dim3(128), 0, s, err);
+  }
+  bool launch_split_attention(const cgk::AttnArgs& a, int64_t B, int64_t nkv, int64_t rep, int64_t hd, unsigned* err) {
+    if (!std::is_same<T, __nv_bfloat16>::value) return false;
+    if (m.host_ctx_len <= 512 || B > 65535) return false;
+    static const bool off = std::getenv("CATGRAD_B200_NO_SPLIT_ATTN") != nullptr;
+    if (off) return false;
+    const int64_t nh = nkv * rep;
+    const int chunks_max = (int)((m.P + cgk::ATTN_CHUNK - 1) / cgk::ATTN_CHUNK);
+    const int64_t need_scores = m.max_batch * nh * m.P, need_partial = m.max_batch * nh * chunks_max * hd;
+    if (!m.attn_scores.defined() || m.attn_scores.size() < need_scores) m.attn_scores = m.be->empty({need_scores}, Dtype::F32);
+    if (!m.attn_partial.defined() || m.attn_partial.size() < need_partial) m.attn_partial = m.be->empty({need_partial}, Dtype::F32);
+    if (!m.attn_counters.defined()) m.attn_counters = m.be->zeros({m.max_batch * nkv}, Dtype::U32);
+    cgk::AttnSplitArgs s;
+    s.a = a;
+    s.scores = (float*)m.attn_scores.raw();
+    s.partial = (float*)m.attn_partial.raw();
+    s.counters = (unsigned*)m.attn_counters.raw();
+    s.chunks_max = chunks_max;
+    if (hd == 64) {
+      switch (rep) {
+        case 1: split_attention_launch<64, 1>(s, B, nkv, err); return true;
+        case 2: split_attention_launch<64, 2>(s, B, nkv, err); return true;
+        case 4: split_attention_launch<64, 4>(s, B, nkv, err); return true;
+        case 8: split_attention_launch<64, 8>(s, B, nkv, err); return true;
+        default: return false;
+      }
+    }
+    if (hd == 128) {
+      switch (rep) {
+        case 1: split_attention_launch<128, 1>(s, B, nkv, err); return true;
+        case 2: split_attention_launch<128, 2>(s, B, nkv, err); return true;
+        case 4: split_attention_launch<128, 4>(s, B, nkv, err); return true;
+        default: return false;
+      }
+    }
+    return false;
+  }
+
   // x += sum over the tensor-parallel ranks of the partial product in `tmp` (both live in the symmetric buffer)
   void reduce_partials(int64_t n) {
     m.comm->allreduce(m.dt, 0, m.comm_part_off, n, /*residual=*/true, sm, st, m.be->dev_err());
@@ -410,6 +456,8 @@ struct Plan {
         const int64_t rep = nh / nkv;
         if (launch_group_attention(a, B, nkv, rep, hd, err)) {
           // one warp per (kv head, sequence)
+        } else if (launch_split_attention(a, B, nkv, rep, hd, err)) {
+          // long contexts: keys split over CTAs
         } else if (B * nh >= 4 * (int64_t)sm && rep <= 8 && m.host_ctx_len <= 512) {
           // many sequences with short contexts: one warp per query head, one CTA per (kv head, sequence); long
           // contexts keep a whole CTA per head (a captured graph keeps the choice made at its first step)

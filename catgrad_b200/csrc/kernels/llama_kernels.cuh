@@ -855,6 +855,192 @@ __global__ void __launch_bounds__(128) attn_decode_group_kernel(AttnArgs a, unsi
   }
 }
 
+// ---- decode attention for long contexts: keys split into chunks of 128 across CTAs ---------------------------
+// Two launches per layer, grid (chunk, kv head, sequence), 128 threads.  Same sub-graph and rounding points as
+// attn_decode_kernel (scores and probabilities are rounded to T exactly as there; only the f32 summation orders
+// differ).  The REP query heads of a kv head share every K/V row that is loaded.
+//   attn_split_scores_kernel : RoPE(q), RoPE(k) + cache append (by the CTA whose chunk holds the new position), one
+//                              key per thread: scaled scores of the group's heads -> scores[b, h, t] (f32 scratch).
+//   attn_split_pv_kernel     : row max and sum over all t (re-read from the scratch, L2-resident), probabilities of
+//                              the chunk's keys, partial P.v -> partial[b, h, chunk, :] (f32).  The last CTA of a
+//                              (sequence, kv head) to finish - an atomic counter, no waiting - adds the chunks'
+//                              partials in chunk order and stores the heads' outputs, so the result is deterministic.
+struct AttnSplitArgs {
+  AttnArgs a;
+  float* scores;      // [B, nh, P]
+  float* partial;     // [B, nh, chunks_max, HD]
+  unsigned* counters; // [B, nkv], zero between launches
+  int chunks_max;
+};
+constexpr int ATTN_CHUNK = 128;
+
+template <class T, int HD, int REP>
+__global__ void __launch_bounds__(128) attn_split_scores_kernel(AttnSplitArgs s, unsigned* err) {
+  static_assert(sizeof(T) == 2, "16-byte rows of 8 elements");
+  constexpr int CH = HD / 8, half = HD / 2;
+  __shared__ __align__(16) float q_s[REP * HD];
+  __shared__ __align__(16) T k_new[HD];
+  const AttnArgs& a = s.a;
+  const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pos = *a.ctx_len;
+  if (pos >= a.P) {
+    if (tid == 0 && chunk == 0) atomicOr(err, DEV_ERR_INDEX_OOB);
+    return;
+  }
+  const int total = pos + 1;
+  const int chunks = (total + ATTN_CHUNK - 1) / ATTN_CHUNK;
+  if (chunk >= chunks) return;
+  T* kc = (T*)a.kc + ((long long)b * a.nkv + kvh) * a.P * HD;
+  T* vc = (T*)a.vc + ((long long)b * a.nkv + kvh) * a.P * HD;
+  const float* ct = a.cos_t + (long long)pos * half;
+  const float* st = a.sin_t + (long long)pos * half;
+  for (int i = tid; i < REP * half; i += 128) {
+    const int h = i / half, j = i - h * half;
+    const T* qsrc = (const T*)a.q + (long long)b * a.q_row_stride + (kvh * REP + h) * HD;
+    float x1 = Elem<T>::load(qsrc[j]), x2 = Elem<T>::load(qsrc[j + half]);
+    float c = ct[j], sn = st[j];
+    q_s[h * HD + j] = rt<T>(c * x1 + sn * (-x2));
+    q_s[h * HD + j + half] = rt<T>(c * x2 + sn * x1);
+  }
+  if (chunk == chunks - 1) {  // this CTA owns position `pos`: it appends the new K/V rows
+    const T* ksrc = (const T*)a.k + (long long)b * a.k_row_stride + kvh * HD;
+    const T* vsrc = (const T*)a.v + (long long)b * a.v_row_stride + kvh * HD;
+    for (int i = tid; i < half; i += 128) {
+      float x1 = Elem<T>::load(ksrc[i]), x2 = Elem<T>::load(ksrc[i + half]);
+      float c = ct[i], sn = st[i];
+      T o1 = Elem<T>::store(c * x1 + sn * (-x2)), o2 = Elem<T>::store(c * x2 + sn * x1);
+      k_new[i] = o1;
+      k_new[i + half] = o2;
+      kc[(long long)pos * HD + i] = o1;
+      kc[(long long)pos * HD + i + half] = o2;
+    }
+    for (int i = tid; i < HD; i += 128) vc[(long long)pos * HD + i] = vsrc[i];
+  }
+  __syncthreads();
+  const int t = chunk * ATTN_CHUNK + tid;
+  if (t >= total) return;
+  const uint4* krow = reinterpret_cast<const uint4*>(t == pos ? k_new : kc + (long long)t * HD);
+  uint4 kr[CH];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) kr[c] = krow[c];
+#pragma unroll
+  for (int h = 0; h < REP; ++h) {
+    float d = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const T* e = reinterpret_cast<const T*>(&kr[c]);
+      const float4 qa = *reinterpret_cast<const float4*>(q_s + h * HD + c * 8);
+      const float4 qb = *reinterpret_cast<const float4*>(q_s + h * HD + c * 8 + 4);
+      d = fmaf(qa.x, Elem<T>::load(e[0]), d);
+      d = fmaf(qa.y, Elem<T>::load(e[1]), d);
+      d = fmaf(qa.z, Elem<T>::load(e[2]), d);
+      d = fmaf(qa.w, Elem<T>::load(e[3]), d);
+      d = fmaf(qb.x, Elem<T>::load(e[4]), d);
+      d = fmaf(qb.y, Elem<T>::load(e[5]), d);
+      d = fmaf(qb.z, Elem<T>::load(e[6]), d);
+      d = fmaf(qb.w, Elem<T>::load(e[7]), d);
+    }
+    s.scores[((long long)b * a.nh + kvh * REP + h) * a.P + t] = rt<T>(rt<T>(d) / a.scale);
+  }
+}
+
+template <class T, int HD, int REP>
+__global__ void __launch_bounds__(128) attn_split_pv_kernel(AttnSplitArgs s, unsigned* err) {
+  static_assert(sizeof(T) == 2, "16-byte rows of 8 elements");
+  constexpr int CH = HD / 8, KG = 32 / CH;
+  __shared__ float red[4];
+  __shared__ float p_s[REP][ATTN_CHUNK];
+  __shared__ __align__(16) float accw[4][REP][HD];
+  __shared__ int s_last;
+  const AttnArgs& a = s.a;
+  const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pos = *a.ctx_len;
+  if (pos >= a.P) return;
+  const int total = pos + 1;
+  const int chunks = (total + ATTN_CHUNK - 1) / ATTN_CHUNK;
+  if (chunk >= chunks) return;
+  const T* vc = (const T*)a.vc + ((long long)b * a.nkv + kvh) * a.P * HD;
+  const int t_mine = chunk * ATTN_CHUNK + tid;
+  for (int h = 0; h < REP; ++h) {
+    const float* sc = s.scores + ((long long)b * a.nh + kvh * REP + h) * a.P;
+    float mx = -FLT_MAX;
+    for (int t = tid; t < total; t += 128) mx = fmaxf(mx, sc[t]);
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    float sum = 0.f;
+    for (int t = tid; t < total; t += 128) sum += expf(sc[t] - mx);
+    sum = warp_sum(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    sum = (red[0] + red[1]) + (red[2] + red[3]);
+    __syncthreads();
+    p_s[h][tid] = t_mine < total ? rt<T>(expf(sc[t_mine] - mx) / sum) : 0.f;
+  }
+  __syncthreads();
+  // P.v over this warp's 32 keys: lane = (key group g, 16-byte chunk c)
+  const int g = lane / CH, c = lane % CH;
+  float acc[REP][8];
+#pragma unroll
+  for (int h = 0; h < REP; ++h)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[h][i] = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32 / KG; ++i) {
+    const int j = warp * 32 + g + KG * i;
+    const int t = chunk * ATTN_CHUNK + j;
+    if (t < total) {
+      const uint4 vv = *reinterpret_cast<const uint4*>(vc + (long long)t * HD + c * 8);
+      const T* e = reinterpret_cast<const T*>(&vv);
+#pragma unroll
+      for (int h = 0; h < REP; ++h) {
+        const float ph = p_s[h][j];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[h][k] = fmaf(ph, Elem<T>::load(e[k]), acc[h][k]);
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < REP; ++h)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float v = acc[h][k];
+#pragma unroll
+      for (int o = CH; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (g == 0) accw[warp][h][c * 8 + k] = v;
+    }
+  __syncthreads();
+  for (int i = tid; i < REP * HD; i += 128) {
+    const int h = i / HD, d = i - h * HD;
+    const float v = (accw[0][h][d] + accw[1][h][d]) + (accw[2][h][d] + accw[3][h][d]);
+    s.partial[(((long long)b * a.nh + kvh * REP + h) * s.chunks_max + chunk) * HD + d] = v;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned old = atomicAdd(s.counters + (long long)b * a.nkv + kvh, 1u);
+    s_last = old == (unsigned)(chunks - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int i = tid; i < REP * HD; i += 128) {
+    const int h = i / HD, d = i - h * HD;
+    const float* src = s.partial + (((long long)b * a.nh + kvh * REP + h) * s.chunks_max) * HD + d;
+    float v = 0.f;
+    for (int cc = 0; cc < chunks; ++cc) v += __ldcg(src + (long long)cc * HD);
+    ((T*)a.out)[(long long)b * a.out_row_stride + (kvh * REP + h) * HD + d] = Elem<T>::store(v);
+  }
+  if (tid == 0) s.counters[(long long)b * a.nkv + kvh] = 0u;
+}
+
 // ---- prefill: scale + causal mask + softmax over score rows (llama.rs:330-339) ------------------------
 // Row r = ((b*nh + h)*S + s) of scores [.., S, Tt] (T, in place): x = T(x / scale); x = T(x + mask) where the
 // mask is T(f32::MIN) for keys after position T0+s (in bf16 that is -inf) and -0.0 otherwise; softmax in f32.

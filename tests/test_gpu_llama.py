@@ -126,6 +126,44 @@ def test_many_sequences_bf16_gqa(gpu, B):
         tok = nxt
 
 
+@pytest.mark.parametrize("heads,kv_heads", [(8, 2), (4, 2)])
+def test_long_context_uses_key_split_attention(gpu, heads, kv_heads):
+    """Beyond 512 cached positions the bf16 decode step splits the keys of every (sequence, kv head) over CTAs (two
+    launches, partial sums combined in chunk order).  Held to the f32 model on the same weights, step by step with
+    the same history, like every bf16 path; head_dim 64 (8 heads) and 128 (4 heads)."""
+    cfg = cb.LlamaConfig(512, 1536, 2, heads, kv_heads, 4096, rope_theta=500000.0, rms_norm_eps=1e-5,
+                         tie_word_embeddings=True)
+    w = cb.random_weights(cfg, seed=0)
+    wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+    B, S = 3, 600
+    ids = np.random.default_rng(9).integers(0, cfg.vocab_size, size=(B, S), dtype=np.uint32)
+    run16 = cb.LlamaRunner(gpu, cfg, cb.upload_weights(gpu, wb, Dtype.BF16), Dtype.BF16, max_batch=B, max_positions=S + 140)
+    run32 = cb.LlamaRunner(gpu, cfg, cb.upload_weights(gpu, wb, Dtype.F32), Dtype.F32, max_batch=B, max_positions=S + 140)
+    run16.reset(B)
+    run32.reset(B)
+    tok = run16.forward(ids)
+    run32.forward(ids)
+    assert np.abs(run16.last_logits() - run32.last_logits()).max() <= ABS_BF16
+    for _ in range(3):
+        nxt = run16.forward(tok.reshape(B, 1))
+        run32.forward(tok.reshape(B, 1))
+        assert np.abs(run16.last_logits() - run32.last_logits()).max() <= ABS_BF16
+        tok = nxt
+    # the captured graph replays the same two launches while the context crosses a chunk boundary (640 = 5 x 128)
+    more = run16.decode(45)
+    assert run16.context_len == S + 3 + 45
+    again = cb.LlamaRunner(gpu, cfg, run16._params, Dtype.BF16, max_batch=B, max_positions=S + 140)
+    again.reset(B)
+    t2 = again.forward(ids)
+    for _ in range(3):
+        t2 = again.forward(t2.reshape(B, 1))
+    cols = []
+    for _ in range(45):
+        t2 = again.forward(t2.reshape(B, 1))
+        cols.append(t2)
+    np.testing.assert_array_equal(more, np.stack(cols, 1))
+
+
 def small_bf16_model():
     # Llama-3.2-1B proportions (GQA 4:1, head_dim 64, tied head, theta 5e5) at 2 layers / hidden 512
     cfg = cb.LlamaConfig(512, 1536, 2, 8, 2, 4096, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=True)
