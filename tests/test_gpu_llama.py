@@ -164,6 +164,24 @@ def test_long_context_uses_key_split_attention(gpu, heads, kv_heads):
     np.testing.assert_array_equal(more, np.stack(cols, 1))
 
 
+def test_graph_capture_right_at_the_attention_switch_point(gpu):
+    """A 512-token prompt: the first decode step (context 512) still takes the single-launch attention, the captured
+    step (context 513) the key-split one.  Nothing may allocate inside the capture, and the ids must equal stepping."""
+    cfg, wb, _ = small_bf16_model()
+    ids = np.random.default_rng(3).integers(0, cfg.vocab_size, size=(1, 512), dtype=np.uint32)
+    pg = cb.upload_weights(gpu, wb, Dtype.BF16)
+    runner = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=1, max_positions=560)
+    out = runner.generate(ids, 10)
+    step = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=1, max_positions=560)
+    step.reset(1)
+    tok = step.forward(ids)
+    cols = [tok]
+    for _ in range(9):
+        tok = step.forward(tok.reshape(1, 1))
+        cols.append(tok)
+    np.testing.assert_array_equal(out, np.stack(cols, 1))
+
+
 def small_bf16_model():
     # Llama-3.2-1B proportions (GQA 4:1, head_dim 64, tied head, theta 5e5) at 2 layers / hidden 512
     cfg = cb.LlamaConfig(512, 1536, 2, 8, 2, 4096, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=True)
