@@ -144,7 +144,7 @@ struct Plan {
     size_t smem = (size_t)MT * a.K * sizeof(T);
     auto kern = cgk::gemv_fused_kernel<T, MT, PRO, EPI>;
     static size_t smem_set = 0;  // per instantiation: raise the dynamic shared-memory limit once per size class
-    if (smem > 48 * 1024 && smem > smem_set) {
+    if (smem > 40 * 1024 && smem > smem_set) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       smem_set = smem;
     }
@@ -220,7 +220,7 @@ struct Plan {
     size_t smem = 4 * per_warp;
     auto kern = cgk::attn_decode_group_kernel<__nv_bfloat16, HD, REP>;
     static size_t smem_set = 0;
-    if (smem > 48 * 1024 && smem > smem_set) {
+    if (smem > 40 * 1024 && smem > smem_set) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       smem_set = smem;
     }
@@ -466,7 +466,7 @@ struct Plan {
           if (hd == 64) {
             auto kern = cgk::attn_decode_warp_kernel<T, 64>;
             static size_t smem_set = 0;
-            if (smem > 48 * 1024 && smem > smem_set) {
+            if (smem > 40 * 1024 && smem > smem_set) {
               cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
               smem_set = smem;
             }
@@ -474,7 +474,7 @@ struct Plan {
           } else {
             auto kern = cgk::attn_decode_warp_kernel<T, 128>;
             static size_t smem_set = 0;
-            if (smem > 48 * 1024 && smem > smem_set) {
+            if (smem > 40 * 1024 && smem > smem_set) {
               cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
               smem_set = smem;
             }
@@ -486,7 +486,7 @@ struct Plan {
         if (hd == 64) {
           auto kern = cgk::attn_decode_kernel<T, 64>;
           static size_t smem_set = 0;
-          if (smem > 48 * 1024 && smem > smem_set) {
+          if (smem > 40 * 1024 && smem > smem_set) {
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             smem_set = smem;
           }
@@ -494,7 +494,7 @@ struct Plan {
         } else {
           auto kern = cgk::attn_decode_kernel<T, 128>;
           static size_t smem_set = 0;
-          if (smem > 48 * 1024 && smem > smem_set) {
+          if (smem > 40 * 1024 && smem > smem_set) {
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             smem_set = smem;
           }
@@ -635,7 +635,7 @@ struct Plan {
       cgk::softmax_mask_rows_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(scores, rows, (int)S, (int)Tt, (int)Tp,
                                                                                   (int)T0, scale);
     } else {
-      if ((size_t)Tt * 4 > 48 * 1024)
+      if ((size_t)Tt * 4 > 40 * 1024)
         cudaFuncSetAttribute(cgk::softmax_mask_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(Tt * 4));
       cgk::softmax_mask_kernel<T><<<(unsigned)(B * nh * S), 256, (size_t)Tt * 4, st>>>(scores, (int)S, (int)Tt, (int)Tp, (int)T0, scale);
     }

@@ -135,7 +135,7 @@ def test_long_context_uses_key_split_attention(gpu, heads, kv_heads):
                          tie_word_embeddings=True)
     w = cb.random_weights(cfg, seed=0)
     wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
-    B, S = 3, 600
+    B, S = 16, 600     # 16 sequences x 2 kv heads: the smallest batch that takes the key-split path
     ids = np.random.default_rng(9).integers(0, cfg.vocab_size, size=(B, S), dtype=np.uint32)
     run16 = cb.LlamaRunner(gpu, cfg, cb.upload_weights(gpu, wb, Dtype.BF16), Dtype.BF16, max_batch=B, max_positions=S + 140)
     run32 = cb.LlamaRunner(gpu, cfg, cb.upload_weights(gpu, wb, Dtype.F32), Dtype.F32, max_batch=B, max_positions=S + 140)
@@ -168,16 +168,17 @@ def test_graph_capture_right_at_the_attention_switch_point(gpu):
     """A 512-token prompt: the first decode step (context 512) still takes the single-launch attention, the captured
     step (context 513) the key-split one.  Nothing may allocate inside the capture, and the ids must equal stepping."""
     cfg, wb, _ = small_bf16_model()
-    ids = np.random.default_rng(3).integers(0, cfg.vocab_size, size=(1, 512), dtype=np.uint32)
+    B = 16
+    ids = np.random.default_rng(3).integers(0, cfg.vocab_size, size=(B, 512), dtype=np.uint32)
     pg = cb.upload_weights(gpu, wb, Dtype.BF16)
-    runner = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=1, max_positions=560)
+    runner = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=B, max_positions=560)
     out = runner.generate(ids, 10)
-    step = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=1, max_positions=560)
-    step.reset(1)
+    step = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=B, max_positions=560)
+    step.reset(B)
     tok = step.forward(ids)
     cols = [tok]
     for _ in range(9):
-        tok = step.forward(tok.reshape(1, 1))
+        tok = step.forward(tok.reshape(B, 1))
         cols.append(tok)
     np.testing.assert_array_equal(out, np.stack(cols, 1))
 
