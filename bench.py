@@ -276,6 +276,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto", choices=["auto", "c3", "c4", "c5", "tiny", "sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="profiling aid: override the number of sequences (c3/c4)")
+    ap.add_argument("--prompt", type=int, default=0, help="profiling aid: override the prompt length (c3/c4)")
     ap.add_argument("--skip-c4", action="store_true", help="N=1 only: do not time the batch-sharded workload as well")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -342,6 +344,10 @@ def main():
             batch_total, prompt_len = 1, (512 if workload == "c3" else 64)
         else:
             batch_total, prompt_len = 256, 128
+        if args.batch:
+            batch_total = args.batch
+        if args.prompt:
+            prompt_len = args.prompt
         assert batch_total % world == 0
         batch = batch_total // world
 

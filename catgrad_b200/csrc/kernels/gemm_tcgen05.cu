@@ -568,6 +568,38 @@ void launch_g(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M
   kern<<<grid, 192, smem, st>>>(ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, g, err);
 }
 
+// How many clusters of `splits` CTAs of the split-K kernel the GPU can hold at once (0 if the query fails).  A grid
+// with more clusters than that runs a second, nearly empty wave, which doubles the duration of these short kernels.
+template <int BN, int STAGES>
+int splitk_max_clusters(int splits) {
+  static int cache[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+  if (splits < 1 || splits > 8) return 0;
+  if (cache[splits] >= 0) return cache[splits];
+  using L = SmemLayout<BN>;
+  size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, 0, false, true>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(1, 1, (unsigned)splits);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned)splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  cache[splits] = n;
+  return n;
+}
+
 // Split-K launch: grid (N tiles, M tiles, splits) in clusters of (1, 1, splits).
 template <int BN, int STAGES>
 bool launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K, int splits,
@@ -659,16 +691,30 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
   static const bool no_splitk = std::getenv("CATGRAD_B200_NO_SPLITK") != nullptr;
   if (streaming && !no_splitk && p.batch == 1 && N >= 64) {
     const long long num_k = (K + BK - 1) / BK;
-    int sbn = 128;
-    if (N < 128 || mtiles * ((N + 127) / 128) * 8 < (3ll * sm_count) / 5) sbn = 64;
-    const long long tiles = mtiles * ((N + sbn - 1) / sbn);
-    int splits = 1;
-    while (splits < 8 && tiles * splits * 2 <= (long long)sm_count + sm_count / 8 && num_k / (splits * 2) >= 2) splits *= 2;
-    // every CTA of the cluster needs a non-empty K range
-    while (splits > 1 && (long long)(splits - 1) * ((num_k + splits - 1) / splits) >= num_k) splits /= 2;
-    if (splits > 1 && make_map(&ta, A, K, p.M, lda, 1, 0, BM) && make_map(&tb, B, K, N, ldb, 1, 0, sbn)) {
-      const bool launched = sbn == 128 ? launch_splitk<128, 6>(ta, tb, C, p.M, N, K, splits, residual, err, st)
-                                       : launch_splitk<64, 8>(ta, tb, C, p.M, N, K, splits, residual, err, st);
+    // candidates: column tiles of 128 or 64, 2/4/8-way split; keep the one that occupies the most SMs in ONE wave
+    // of clusters (ties: wider tiles, then fewer splits)
+    int best_bn = 0, best_splits = 1;
+    long long best_ctas = mtiles * ((N + 127) / 128);   // what plain 128-wide tiles without a split would occupy
+    if (best_ctas > sm_count) best_ctas = sm_count;
+    for (int sbn = 128; sbn >= 64; sbn >>= 1) {
+      if (N < sbn) continue;
+      const long long tiles = mtiles * ((N + sbn - 1) / sbn);
+      for (int splits = 2; splits <= 8; splits <<= 1) {
+        if (num_k / splits < 2) break;                                              // at least two k-blocks per CTA
+        if ((long long)(splits - 1) * ((num_k + splits - 1) / splits) >= num_k) continue;  // no empty K range
+        const int room = sbn == 128 ? splitk_max_clusters<128, 6>(splits) : splitk_max_clusters<64, 8>(splits);
+        if (tiles > room) continue;
+        const long long ctas = tiles * splits;
+        if (ctas > best_ctas + best_ctas / 8) {   // a finer cut has to buy clearly more parallelism
+          best_ctas = ctas;
+          best_bn = sbn;
+          best_splits = splits;
+        }
+      }
+    }
+    if (best_bn && make_map(&ta, A, K, p.M, lda, 1, 0, BM) && make_map(&tb, B, K, N, ldb, 1, 0, best_bn)) {
+      const bool launched = best_bn == 128 ? launch_splitk<128, 6>(ta, tb, C, p.M, N, K, best_splits, residual, err, st)
+                                           : launch_splitk<64, 8>(ta, tb, C, p.M, N, K, best_splits, residual, err, st);
       if (launched) return true;
       cudaGetLastError();  // cluster launch refused: fall through to the plain tiles
     }
