@@ -186,6 +186,9 @@ struct BatchGeom {
   int ldc;
   // optional residual with C's layout (may alias C): C = bf16(res + bf16(acc)), the `x + linear(...)` of a block
   const __nv_bfloat16* res;
+  // BMODE 0 with a right operand that no earlier kernel of the stream writes (a weight): the kernel was launched
+  // with programmatic stream serialization and may fetch its first B tiles before the preceding kernel has finished
+  int early_b;
 };
 
 // bf16(r + bf16(a)) for two neighbouring elements
@@ -230,6 +233,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
     num_k = num_k_total - k_first < per ? num_k_total - k_first : per;   // the host keeps every range non-empty
   }
 
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -252,7 +256,23 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
   if (warp == 0 && lane == 0) {
     // ---- TMA producer ----
     int issued = 0;
-    for (int k = 0; k < num_k; ++k) {
+    int k_start = 0;
+    if (BMODE == 0 && !B_MN && g.early_b) {
+      // the weight tiles of the first ring-full of stages do not depend on the preceding kernel: fetch them, then
+      // wait for that kernel (its output is this kernel's A operand) and add the A tiles to the same stages
+      const int pre = num_k < STAGES ? num_k : STAGES;
+      for (int k = 0; k < pre; ++k) {
+        mbar_expect_tx(&full[k], L::STAGE_BYTES);
+        tma_load_2d(smem + k * L::STAGE_BYTES + L::A_BYTES, &tmB, &full[k], (k_first + k) * BK, n0);
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      for (int k = 0; k < pre; ++k) tma_load_2d(smem + k * L::STAGE_BYTES, &tmA, &full[k], (k_first + k) * BK, m0);
+      k_start = pre;
+      issued = pre;
+    } else {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+    for (int k = k_start; k < num_k; ++k) {
       const int s = k % STAGES;
       const uint32_t par = ((k / STAGES) & 1) ^ 1;
       if (!mbar_wait(&empty[s], par, abort_flag)) break;
@@ -310,6 +330,8 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
     if (ok) umma_commit(tmem_full);  // accumulator complete
   } else if (warp >= 2) {
     // ---- epilogue: warp w owns TMEM lanes 32*(w%4) .. +31 = rows m0 + 32*(w%4) + lane ----
+    // the epilogue reads the residual and writes C: order it after the preceding kernel like the producer
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     bool ok = mbar_wait(tmem_full, 0, abort_flag);
     // all lanes of the warp must agree before the warp-collective tcgen05.ld
     ok = __all_sync(0xffffffffu, ok);
@@ -565,7 +587,24 @@ void launch_g(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M
     attr_set = true;
   }
   dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)batch);
-  kern<<<grid, 192, smem, st>>>(ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, g, err);
+  if (BMODE == 0 && !B_MN && g.early_b) {
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, g, err) == cudaSuccess) return;
+    cudaGetLastError();
+  }
+  BatchGeom plain = g;
+  plain.early_b = 0;
+  kern<<<grid, 192, smem, st>>>(ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, plain, err);
 }
 
 // How many clusters of `splits` CTAs of the split-K kernel the GPU can hold at once (0 if the query fails).  A grid
@@ -603,7 +642,7 @@ int splitk_max_clusters(int splits) {
 // Split-K launch: grid (N tiles, M tiles, splits) in clusters of (1, 1, splits).
 template <int BN, int STAGES>
 bool launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K, int splits,
-                   const void* res, unsigned* err, cudaStream_t st) {
+                   const void* res, unsigned* err, cudaStream_t st, bool static_b) {
   using L = SmemLayout<BN>;
   static_assert((size_t)STAGES * L::STAGE_BYTES >= (size_t)BM * (BN + 4) * 4, "partial tile must fit in the operand ring");
   size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
@@ -620,26 +659,29 @@ bool launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long l
   g.c_inner = 0;
   g.ldc = (int)N;
   g.res = (const __nv_bfloat16*)res;
+  g.early_b = static_b ? 1 : 0;
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)splits);
   cfg.blockDim = dim3(192);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = (unsigned)splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = static_b ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kern, ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, g, err) == cudaSuccess;
 }
 
 // contiguous C[batch, M, N]
 template <int BN, int STAGES, bool BATCHED, bool B_MN = false>
 void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K,
-              long long batch, unsigned* err, cudaStream_t st, const void* res = nullptr) {
+              long long batch, unsigned* err, cudaStream_t st, const void* res = nullptr, bool static_b = false) {
   BatchGeom g;
   g.heads = 1;
   g.b_div = 1;
@@ -647,6 +689,7 @@ void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M
   g.c_inner = 0;
   g.ldc = (int)N;
   g.res = (const __nv_bfloat16*)res;
+  g.early_b = static_b ? 1 : 0;
   launch_g<BN, STAGES, BATCHED ? 1 : 0, B_MN>(ta, tb, C, M, N, K, batch, g, err, st);
 }
 }  // namespace
@@ -660,7 +703,7 @@ bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, co
 
 bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
                          long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
-                         cudaStream_t st, bool b_n_contiguous, const void* residual) {
+                         cudaStream_t st, bool b_n_contiguous, const void* residual, bool static_b) {
   Problem p = b_n_contiguous ? analyse(bt, batch, A, B, M, N, K, lda, 1, ldb, 1) : analyse(bt, batch, A, B, M, N, K, lda, 1, 1, ldb);
   if (!p.ok) return false;
   CUtensorMap ta, tb;
@@ -713,8 +756,8 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
       }
     }
     if (best_bn && make_map(&ta, A, K, p.M, lda, 1, 0, BM) && make_map(&tb, B, K, N, ldb, 1, 0, best_bn)) {
-      const bool launched = best_bn == 128 ? launch_splitk<128, 6>(ta, tb, C, p.M, N, K, best_splits, residual, err, st)
-                                           : launch_splitk<64, 8>(ta, tb, C, p.M, N, K, best_splits, residual, err, st);
+      const bool launched = best_bn == 128 ? launch_splitk<128, 6>(ta, tb, C, p.M, N, K, best_splits, residual, err, st, static_b)
+                                           : launch_splitk<64, 8>(ta, tb, C, p.M, N, K, best_splits, residual, err, st, static_b);
       if (launched) return true;
       cudaGetLastError();  // cluster launch refused: fall through to the plain tiles
     }
@@ -723,11 +766,11 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
   if (!make_map(&ta, A, K, p.M, lda, p.batch, p.a_bs, BM) || !make_map(&tb, B, K, N, ldb, p.batch, p.b_bs, bn)) return false;
   const bool bt3 = p.batch > 1;
   switch (bn) {
-    case 256: bt3 ? launch_t<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual) : launch_t<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, st, residual); break;
-    case 128: bt3 ? launch_t<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual) : launch_t<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, st, residual); break;
-    case 64: bt3 ? launch_t<64, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual) : launch_t<64, 8, false>(ta, tb, C, p.M, N, K, 1, err, st, residual); break;
-    case 32: bt3 ? launch_t<32, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual) : launch_t<32, 5, false>(ta, tb, C, p.M, N, K, 1, err, st, residual); break;
-    default: bt3 ? launch_t<16, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual) : launch_t<16, 5, false>(ta, tb, C, p.M, N, K, 1, err, st, residual); break;
+    case 256: bt3 ? launch_t<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual, static_b) : launch_t<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, st, residual, static_b); break;
+    case 128: bt3 ? launch_t<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual, static_b) : launch_t<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, st, residual, static_b); break;
+    case 64: bt3 ? launch_t<64, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual, static_b) : launch_t<64, 8, false>(ta, tb, C, p.M, N, K, 1, err, st, residual, static_b); break;
+    case 32: bt3 ? launch_t<32, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual, static_b) : launch_t<32, 5, false>(ta, tb, C, p.M, N, K, 1, err, st, residual, static_b); break;
+    default: bt3 ? launch_t<16, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual, static_b) : launch_t<16, 5, false>(ta, tb, C, p.M, N, K, 1, err, st, residual, static_b); break;
   }
   return true;
 }
@@ -753,6 +796,7 @@ bool launch_tcgen05_gemm_grouped(const GroupedGemm& p, unsigned* err, cudaStream
   g.c_inner = p.c_head;
   g.ldc = (int)p.ldc;
   g.res = nullptr;
+  g.early_b = 0;
   const long long z = (long long)p.heads * p.outer;
   CUtensorMap ta, tb;
   if (!make_map4(&ta, p.A, p.K, p.M, p.heads, p.outer, p.a_row, p.a_head, p.a_outer, BM)) return false;

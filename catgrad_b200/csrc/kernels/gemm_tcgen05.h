@@ -12,9 +12,12 @@ bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, co
 // Device-side waits are bounded; a timeout sets DEV_ERR_WAIT_TIMEOUT in *err and the kernel returns.
 // Returns false (nothing launched) if the tensor maps cannot be made; the caller then uses the SIMT kernel.
 // residual (optional, C's layout, may alias C; K-major B and a single product only): C = bf16(residual + bf16(A x B)).
+// static_b: no earlier kernel of the stream writes B (it is a weight); the kernel is then launched with programmatic
+// stream serialization and fetches its first B tiles while the preceding kernel drains.
 bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
                          long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
-                         cudaStream_t st, bool b_n_contiguous = false, const void* residual = nullptr);
+                         cudaStream_t st, bool b_n_contiguous = false, const void* residual = nullptr,
+                         bool static_b = false);
 // False when the tensor-core kernels are switched off (CATGRAD_B200_NO_TCGEN05) or the driver entry point is missing.
 bool tcgen05_available();
 // A batch of products laid out as outer x heads (attention): product (o, h) multiplies

@@ -100,6 +100,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ in, 
                                                       T* __restrict__ out, int H, float eps, long long row_mul,
                                                       long long row_off) {
   __shared__ float scratch[8];
+  pdl_launch_dependents();   // a GEMM that follows may start fetching its weight tiles
   const T* x = in + ((long long)blockIdx.x * row_mul + row_off) * H;
   T* y = out + (long long)blockIdx.x * H;
   float ss = 0.f;
@@ -1178,6 +1179,7 @@ template <class T>
 __global__ void __launch_bounds__(256) silu_mul_packed_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows,
                                                               int F) {
   constexpr int VEC = 16 / sizeof(T);
+  pdl_launch_dependents();   // the down projection that follows may start fetching its weight tiles
   const int per = F / VEC;
   const long long total = rows * per;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
