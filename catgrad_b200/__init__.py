@@ -8,4 +8,4 @@ from .backend import Backend, BackendError, Dtype, Status, Tensor, bf16_bits_to_
 from .ir import Interpreter, NodeType, OpKind, Parameters, ScalarOp, Term, TermBuilder  # noqa: F401
 from .llama import (LLAMA_1B, LLAMA_8B, TINY, LlamaConfig, LlamaRunner, empty_state_cache,  # noqa: F401
                     generate_with_interpreter, llama_term, random_weights, upload_weights)
-from . import tp  # noqa: F401,E402
+from . import safetensors, tp  # noqa: F401,E402
