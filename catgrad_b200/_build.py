@@ -21,6 +21,7 @@ SOURCES = [
     "kernels/reduce.cu",
     "kernels/matmul.cu",
     "kernels/gemm_tcgen05.cu",
+    "kernels/gemm_f32x3.cu",
     "kernels/argmax_noalloc.cu",
     "host/cuda_backend.cu",
     "host/llama_engine.cu",

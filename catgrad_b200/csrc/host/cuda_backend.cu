@@ -404,6 +404,26 @@ Tensor CudaBackend::matmul(const Tensor& a, const Tensor& b) {
     check_launch("matmul(tcgen05)");
     return t;
   }
+  // large f32 products with plain layouts: exact-f32 result from three-way bf16 splits on the tensor cores
+  if (a.dt == Dtype::F32 && cgk::matmul_f32x3_applicable(M, N, K, batch) && sak == 1 && sam == K &&
+      ((uintptr_t)a.raw() % 16 == 0) && ((uintptr_t)b.raw() % 16 == 0)) {
+    const bool b_row_major = sbn == 1 && sbk == N, b_k_major = sbk == 1 && sbn == K;
+    bool a_ok = batch == 1, b_ok = batch == 1, b_shared = false;
+    if (batch > 1 && bt.rank == 1) {
+      a_ok = bt.sa[0] == M * K;
+      b_shared = bt.sb[0] == 0;
+      b_ok = b_shared || bt.sb[0] == K * N;
+    }
+    if ((b_row_major || b_k_major) && a_ok && b_ok) {
+      Tensor a3 = empty({(int64_t)cgk::matmul_f32x3_scratch_elems(M * batch, K)}, Dtype::BF16);
+      Tensor b3 = empty({(int64_t)cgk::matmul_f32x3_scratch_elems(N * (b_shared ? 1 : batch), K)}, Dtype::BF16);
+      if (cgk::launch_matmul_f32x3((const float*)a.raw(), (const float*)b.raw(), (float*)t.raw(), a3.raw(), b3.raw(), M, N, K,
+                                   batch, b_row_major, b_shared, dev_words_, sm_count_, stream_)) {
+        check_launch("matmul(f32 via bf16x3)");
+        return t;
+      }
+    }
+  }
   cgk::launch_matmul((int)a.dt, bt, batch, a.raw(), b.raw(), t.raw(), M, N, K, sam, sak, sbk, sbn, sm_count_, stream_);
   check_launch("matmul");
   return t;

@@ -143,7 +143,8 @@ struct Plan {
   void gemv_launch(cgk::GemvArgs a) {
     size_t smem = (size_t)MT * a.K * sizeof(T);
     auto kern = cgk::gemv_fused_kernel<T, MT, PRO, EPI>;
-    static size_t smem_set = 0;  // per instantiation: raise the dynamic shared-memory limit once per size class
+    static size_t smem_set_dev[64] = {0};  // per instantiation and device: raise the dynamic shared-memory limit once per size class
+    size_t& smem_set = smem_set_dev[m.be->device() & 63];
     if (smem > 40 * 1024 && smem > smem_set) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       smem_set = smem;
@@ -222,7 +223,8 @@ struct Plan {
     per_warp = (per_warp + 15) / 16 * 16;
     size_t smem = 4 * per_warp;
     auto kern = cgk::attn_decode_group_kernel<__nv_bfloat16, HD, REP>;
-    static size_t smem_set = 0;
+    static size_t smem_set_dev[64] = {0};
+            size_t& smem_set = smem_set_dev[m.be->device() & 63];
     if (smem > 40 * 1024 && smem > smem_set) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       smem_set = smem;
@@ -468,7 +470,8 @@ struct Plan {
           dim3 grid((unsigned)nkv, (unsigned)B);
           if (hd == 64) {
             auto kern = cgk::attn_decode_warp_kernel<T, 64>;
-            static size_t smem_set = 0;
+            static size_t smem_set_dev[64] = {0};
+            size_t& smem_set = smem_set_dev[m.be->device() & 63];
             if (smem > 40 * 1024 && smem > smem_set) {
               cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
               smem_set = smem;
@@ -476,7 +479,8 @@ struct Plan {
             launch(kern, grid, dim3((unsigned)(32 * rep)), smem, a, err);
           } else {
             auto kern = cgk::attn_decode_warp_kernel<T, 128>;
-            static size_t smem_set = 0;
+            static size_t smem_set_dev[64] = {0};
+            size_t& smem_set = smem_set_dev[m.be->device() & 63];
             if (smem > 40 * 1024 && smem > smem_set) {
               cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
               smem_set = smem;
@@ -488,7 +492,8 @@ struct Plan {
         dim3 grid((unsigned)nh, (unsigned)B);
         if (hd == 64) {
           auto kern = cgk::attn_decode_kernel<T, 64>;
-          static size_t smem_set = 0;
+          static size_t smem_set_dev[64] = {0};
+            size_t& smem_set = smem_set_dev[m.be->device() & 63];
           if (smem > 40 * 1024 && smem > smem_set) {
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             smem_set = smem;
@@ -496,7 +501,8 @@ struct Plan {
           launch(kern, grid, dim3(256), smem, a, err);
         } else {
           auto kern = cgk::attn_decode_kernel<T, 128>;
-          static size_t smem_set = 0;
+          static size_t smem_set_dev[64] = {0};
+            size_t& smem_set = smem_set_dev[m.be->device() & 63];
           if (smem > 40 * 1024 && smem > smem_set) {
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             smem_set = smem;
@@ -635,8 +641,11 @@ struct Plan {
     }
     if (std::is_same<T, __nv_bfloat16>::value && Tp <= 1024 && Tp % 8 == 0) {
       const long long rows = B * nh * S;
-      cgk::softmax_mask_rows_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(scores, rows, (int)S, (int)Tt, (int)Tp,
-                                                                                  (int)T0, scale);
+      int lpr = 1;   // lanes per row: the smallest power of two whose 16-byte vectors cover a row (at most a warp)
+      while (lpr < 32 && lpr * 8 < Tp) lpr <<= 1;
+      const long long rows_per_cta = 8 * (32 / lpr);
+      cgk::softmax_mask_rows_kernel<T><<<(unsigned)((rows + rows_per_cta - 1) / rows_per_cta), 256, 0, st>>>(
+          scores, rows, (int)S, (int)Tt, (int)Tp, (int)T0, scale, lpr);
     } else {
       if ((size_t)Tt * 4 > 40 * 1024)
         cudaFuncSetAttribute(cgk::softmax_mask_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(Tt * 4));

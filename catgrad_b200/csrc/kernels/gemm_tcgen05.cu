@@ -207,7 +207,8 @@ __device__ __forceinline__ uint32_t add_res2(float a0, float a1, uint32_t r) {
 // a cluster barrier CTA z sums rows [z*128/Z, (z+1)*128/Z) over the cluster in rank order (distributed shared
 // memory reads), rounds once and stores.  A pass over a weight with few row tiles thus fills all SMs without
 // re-reading the activations per narrow column tile, and the result does not depend on timing.
-template <int BN, int STAGES, int BMODE, bool B_MN, bool SPLITK = false>
+// OUT_F32: C is a float matrix and the accumulator is stored unrounded (the exact-f32 product built from bf16 pieces).
+template <int BN, int STAGES, int BMODE, bool B_MN, bool SPLITK = false, bool OUT_F32 = false>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                                            const __grid_constant__ CUtensorMap tmB,
                                                            __nv_bfloat16* C, int M, int N, int K,
@@ -365,7 +366,23 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
-        if (row < M) {
+        if (OUT_F32) {
+          if (row < M) {
+            float* frow = reinterpret_cast<float*>(C) + c_off + (long long)row * g.ldc;
+            const int col = n0 + c0;
+            const int width = BN - c0 < 32 ? BN - c0 : 32;
+            if (width == 32 && (g.ldc % 4 == 0) && (((uintptr_t)C & 15) == 0) && (g.c_outer % 4 == 0) && col + 32 <= N) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                *reinterpret_cast<float4*>(frow + col + v * 4) =
+                    make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]), __uint_as_float(r[v * 4 + 2]),
+                                __uint_as_float(r[v * 4 + 3]));
+            } else {
+              for (int j = 0; j < width; ++j)
+                if (col + j < N) frow[col + j] = __uint_as_float(r[j]);
+            }
+          }
+        } else if (row < M) {
           const int col = n0 + c0;
           const int width = BN - c0 < 32 ? BN - c0 : 32;  // columns of this tile in the 32 just loaded
           if (width == 32 && vec_ok && col + 32 <= N) {
@@ -581,7 +598,10 @@ void launch_g(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M
   using L = SmemLayout<BN>;
   size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 /* alignment slack */ + (2 * STAGES + 1) * 8 + 16;
   auto kern = gemm_tcgen05_kernel<BN, STAGES, BMODE, B_MN>;
-  static bool attr_set = false;
+  static bool attr_set_dev[64] = {false};   // function attributes are per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& attr_set = attr_set_dev[dev & 63];
   if (!attr_set) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attr_set = true;
@@ -647,7 +667,10 @@ bool launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long l
   static_assert((size_t)STAGES * L::STAGE_BYTES >= (size_t)BM * (BN + 4) * 4, "partial tile must fit in the operand ring");
   size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
   auto kern = gemm_tcgen05_kernel<BN, STAGES, 0, false, true>;
-  static bool attr_set = false;
+  static bool attr_set_dev[64] = {false};   // function attributes are per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& attr_set = attr_set_dev[dev & 63];
   if (!attr_set) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attr_set = true;
@@ -693,6 +716,8 @@ void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M
   launch_g<BN, STAGES, BATCHED ? 1 : 0, B_MN>(ta, tb, C, M, N, K, batch, g, err, st);
 }
 }  // namespace
+
+bool tcgen05_available();
 
 bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, const void* B, long long M, long long N,
                              long long K, long long sam, long long sak, long long sbk, long long sbn) {
@@ -771,6 +796,58 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
     case 64: bt3 ? launch_t<64, 8, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual, static_b) : launch_t<64, 8, false>(ta, tb, C, p.M, N, K, 1, err, st, residual, static_b); break;
     case 32: bt3 ? launch_t<32, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual, static_b) : launch_t<32, 5, false>(ta, tb, C, p.M, N, K, 1, err, st, residual, static_b); break;
     default: bt3 ? launch_t<16, 5, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual, static_b) : launch_t<16, 5, false>(ta, tb, C, p.M, N, K, 1, err, st, residual, static_b); break;
+  }
+  return true;
+}
+
+// f32 result from bf16 operands (K-major both, optional batch): used by the split-operand exact-f32 product.
+template <int BN, int STAGES, bool BATCHED>
+void launch_f32out(const CUtensorMap& ta, const CUtensorMap& tb, float* C, long long M, long long N, long long K,
+                   long long batch, unsigned* err, cudaStream_t st) {
+  using L = SmemLayout<BN>;
+  size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, BATCHED ? 1 : 0, false, false, true>;
+  static bool attr_set_dev[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set_dev[dev & 63]) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set_dev[dev & 63] = true;
+  }
+  BatchGeom g;
+  g.heads = 1;
+  g.b_div = 1;
+  g.c_outer = M * N;
+  g.c_inner = 0;
+  g.ldc = (int)N;
+  g.res = nullptr;
+  g.early_b = 0;
+  dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)batch);
+  kern<<<grid, 192, smem, st>>>(ta, tb, reinterpret_cast<__nv_bfloat16*>(C), (int)M, (int)N, (int)K, g, err);
+}
+
+bool launch_tcgen05_gemm_f32out(const void* A, const void* B, float* C, long long M, long long N, long long K,
+                                long long batch, long long a_bs, long long b_bs, unsigned* err, int sm_count,
+                                cudaStream_t st) {
+  if (!tcgen05_available()) return false;
+  if (K % 8 != 0 || K < 16 || N < 16 || M < 1 || batch < 1 || batch > 65535) return false;
+  if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return false;
+  if (a_bs % 8 != 0 || b_bs % 8 != 0 || a_bs <= 0) return false;
+  CUtensorMap ta, tb;
+  const long long mtiles = ((M + BM - 1) / BM) * batch;
+  int bn = 256;
+  while (bn > 64 && mtiles * ((N + bn - 1) / bn) < (3ll * sm_count) / 4) bn >>= 1;
+  if (bn > N) bn = N >= 256 ? 256 : (N >= 128 ? 128 : 64);
+  if (N < 64) return false;
+  // a right operand shared by the whole batch (b_bs == 0) is addressed through a 2-D map by every batch entry
+  const bool b3 = batch > 1;
+  if (!make_map(&ta, A, K, M, K, batch, a_bs, BM)) return false;
+  if (b3 && b_bs == 0) return false;   // callers fold a shared right operand into M instead
+  if (!make_map(&tb, B, K, N, K, batch, b_bs, bn)) return false;
+  switch (bn) {
+    case 256: b3 ? launch_f32out<256, 4, true>(ta, tb, C, M, N, K, batch, err, st) : launch_f32out<256, 4, false>(ta, tb, C, M, N, K, 1, err, st); break;
+    case 128: b3 ? launch_f32out<128, 6, true>(ta, tb, C, M, N, K, batch, err, st) : launch_f32out<128, 6, false>(ta, tb, C, M, N, K, 1, err, st); break;
+    default: b3 ? launch_f32out<64, 8, true>(ta, tb, C, M, N, K, batch, err, st) : launch_f32out<64, 8, false>(ta, tb, C, M, N, K, 1, err, st); break;
   }
   return true;
 }

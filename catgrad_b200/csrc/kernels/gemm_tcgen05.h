@@ -18,6 +18,11 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
                          long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
                          cudaStream_t st, bool b_n_contiguous = false, const void* residual = nullptr,
                          bool static_b = false);
+// C[batch, M, N] (contiguous f32) = A[batch, M, K] x B[batch, N, K]^T with bf16 operands (both K-contiguous, rows K
+// apart, batch strides a_bs / b_bs in elements) and the f32 accumulator stored unrounded.
+bool launch_tcgen05_gemm_f32out(const void* A, const void* B, float* C, long long M, long long N, long long K,
+                                long long batch, long long a_bs, long long b_bs, unsigned* err, int sm_count,
+                                cudaStream_t st);
 // False when the tensor-core kernels are switched off (CATGRAD_B200_NO_TCGEN05) or the driver entry point is missing.
 bool tcgen05_available();
 // A batch of products laid out as outer x heads (attention): product (o, h) multiplies

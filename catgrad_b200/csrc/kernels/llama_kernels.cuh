@@ -407,24 +407,35 @@ __global__ void __launch_bounds__(256) rope_append_kernel(RopeArgs a, unsigned* 
   const T* v = (const T*)a.v + (long long)m * a.v_row_stride;
   const float* ct = a.cos_t + (long long)pos * half;
   const float* st = a.sin_t + (long long)pos * half;
-  const int q_pairs = a.nh * half, k_pairs = a.nkv * half;
-  for (int e = threadIdx.x; e < q_pairs + k_pairs; e += 256) {
-    bool is_q = e < q_pairs;
-    int ee = is_q ? e : e - q_pairs;
-    int h = ee / half, i = ee - h * half;
+  // 16-byte vectors: a thread rotates VEC pairs (x1 from the first half of a head, x2 from the second)
+  constexpr int VEC = 16 / sizeof(T);
+  const int gph = half / VEC;  // vector groups per head half
+  const int q_groups = a.nh * gph, k_groups = a.nkv * gph;
+  for (int e = threadIdx.x; e < q_groups + k_groups; e += 256) {
+    const bool is_q = e < q_groups;
+    const int ee = is_q ? e : e - q_groups;
+    const int h = ee / gph, i = (ee - h * gph) * VEC;
     const T* src = is_q ? q + h * a.HD : k + h * a.HD;
-    float x1 = Elem<T>::load(src[i]), x2 = Elem<T>::load(src[i + half]);
-    float c = ct[i], sn = st[i];
-    // cos*x + sin*rotate_half(x), rotate_half = cat(-x2, x1): two products and one sum, each rounded
-    float o1 = c * x1 + sn * (-x2);
-    float o2 = c * x2 + sn * x1;
+    const VecT<T, VEC> x1 = *reinterpret_cast<const VecT<T, VEC>*>(src + i);
+    const VecT<T, VEC> x2 = *reinterpret_cast<const VecT<T, VEC>*>(src + i + half);
+    VecT<T, VEC> o1, o2;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float a1 = Elem<T>::load(x1.v[j]), a2 = Elem<T>::load(x2.v[j]);
+      const float c = ct[i + j], sn = st[i + j];
+      // cos*x + sin*rotate_half(x), rotate_half = cat(-x2, x1): two products and one sum, each rounded
+      o1.v[j] = Elem<T>::store(c * a1 + sn * (-a2));
+      o2.v[j] = Elem<T>::store(c * a2 + sn * a1);
+    }
     T* dst = is_q ? q + h * a.HD : (T*)a.kc + (((long long)b * a.nkv + h) * a.P + pos) * a.HD;
-    dst[i] = Elem<T>::store(o1);
-    dst[i + half] = Elem<T>::store(o2);
+    *reinterpret_cast<VecT<T, VEC>*>(dst + i) = o1;
+    *reinterpret_cast<VecT<T, VEC>*>(dst + i + half) = o2;
   }
-  for (int e = threadIdx.x; e < a.nkv * a.HD; e += 256) {
-    int h = e / a.HD, i = e - h * a.HD;
-    ((T*)a.vc)[(((long long)b * a.nkv + h) * a.P + pos) * a.HD + i] = v[e];
+  const int vph = a.HD / VEC;
+  for (int e = threadIdx.x; e < a.nkv * vph; e += 256) {
+    const int h = e / vph, i = (e - h * vph) * VEC;
+    *reinterpret_cast<VecT<T, VEC>*>((T*)a.vc + (((long long)b * a.nkv + h) * a.P + pos) * a.HD + i) =
+        *reinterpret_cast<const VecT<T, VEC>*>(v + h * a.HD + i);
   }
 }
 
@@ -1078,22 +1089,24 @@ __global__ void __launch_bounds__(256) softmax_mask_kernel(T* __restrict__ score
 // follows; with the IEEE forms this kernel is bound by the special-function and divide sequences, not by HBM.
 template <class T>
 __global__ void __launch_bounds__(256) softmax_mask_rows_kernel(T* __restrict__ scores, long long rows, int S, int Tt,
-                                                                int pitch, int T0, float scale) {
+                                                                int pitch, int T0, float scale, int lpr) {
+  // lpr = lanes per row (a power of two, 32 / lpr rows per warp): short rows do not leave lanes idle
   constexpr int VEC = 16 / sizeof(T);
   constexpr int MAXV = 1024 / (32 * VEC);
   const int lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  T* x = scores + row * pitch;
-  const int s = (int)(row % S);
+  const int rpw = 32 / lpr, sub = lane / lpr, l = lane % lpr;
+  const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * rpw + sub;
+  const bool live = row < rows;
+  T* x = scores + (live ? row : 0) * pitch;
+  const int s = (int)((live ? row : 0) % S);
   const float masked = rt<T>(-FLT_MAX);
-  const int nv = (pitch + 32 * VEC - 1) / (32 * VEC);
+  const int nv = (pitch + lpr * VEC - 1) / (lpr * VEC);
   float v[MAXV][VEC];
   float mx = -FLT_MAX;
 #pragma unroll
   for (int j = 0; j < MAXV; ++j) {
-    const int t0 = (j * 32 + lane) * VEC;
-    if (j < nv && t0 < pitch) {
+    const int t0 = (j * lpr + l) * VEC;
+    if (j < nv && t0 < pitch && live) {
       VecT<T, VEC> in = *reinterpret_cast<const VecT<T, VEC>*>(x + t0);
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
@@ -1106,12 +1119,12 @@ __global__ void __launch_bounds__(256) softmax_mask_rows_kernel(T* __restrict__ 
       }
     }
   }
-  mx = warp_max(mx);
+  for (int o = lpr >> 1; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   float sum = 0.f;
 #pragma unroll
   for (int j = 0; j < MAXV; ++j) {
-    const int t0 = (j * 32 + lane) * VEC;
-    if (j < nv && t0 < pitch) {
+    const int t0 = (j * lpr + l) * VEC;
+    if (j < nv && t0 < pitch && live) {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
         float e = t0 + i < Tt ? __expf(v[j][i] - mx) : 0.f;
@@ -1120,12 +1133,12 @@ __global__ void __launch_bounds__(256) softmax_mask_rows_kernel(T* __restrict__ 
       }
     }
   }
-  sum = warp_sum(sum);
+  for (int o = lpr >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   const float inv = 1.0f / sum;
 #pragma unroll
   for (int j = 0; j < MAXV; ++j) {
-    const int t0 = (j * 32 + lane) * VEC;
-    if (j < nv && t0 < pitch) {
+    const int t0 = (j * lpr + l) * VEC;
+    if (j < nv && t0 < pitch && live) {
       VecT<T, VEC> o;
 #pragma unroll
       for (int i = 0; i < VEC; ++i) o.v[i] = Elem<T>::store(v[j][i] * inv);

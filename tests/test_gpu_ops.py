@@ -286,6 +286,36 @@ def test_matmul(oracle, gpu, dtype):
         gpu.matmul(gpu.from_numpy(x), gpu.from_numpy(w))
 
 
+@pytest.mark.parametrize("case", [((3, 256, 512), (3, 512, 320), "row-major right operand"),
+                                  ((1024, 256), (256, 640), "rank 2"),
+                                  ((4, 128, 264), (264, 200), "weight shared by the batch, stored [N, K]")], ids=lambda c: c[2])
+def test_f32_matmul_on_tensor_cores_from_split_operands(gpu, case):
+    """Large f32 products run on the bf16 tensor cores from three-way split operands (six partial products, f32
+    accumulate).  Against float64 numpy the error must stay near f32 level (the tensor core's truncating accumulation
+    costs a few 1e-6 of the largest entry), far below what a single bf16 or TF32 rounding of the operands would
+    give (~4e-3)."""
+    import os
+    sa, sb, kind = case
+    rng = np.random.default_rng(17)
+    a = rng.standard_normal(sa).astype(np.float32)
+    if kind.startswith("weight"):
+        w = rng.standard_normal((sb[1], sb[0])).astype(np.float32)           # [N, K]
+        bg = gpu.broadcast(gpu.transpose(gpu.from_numpy(w), 0, 1), (sa[0],) + sb)
+        ref = a.astype(np.float64) @ w.T.astype(np.float64)
+    else:
+        b = rng.standard_normal(sb).astype(np.float32)
+        bg = gpu.from_numpy(b)
+        ref = a.astype(np.float64) @ b.astype(np.float64)
+    got = gpu.to_numpy(gpu.matmul(gpu.from_numpy(a), bg))
+    scale = np.abs(ref).max()
+    assert np.abs(got - ref).max() / scale < 1e-5
+    # scaled inputs with a wide dynamic range: the split must not lose small operands next to large ones
+    a2 = (a * np.exp(rng.uniform(-8, 8, size=a.shape))).astype(np.float32)
+    got2 = gpu.to_numpy(gpu.matmul(gpu.from_numpy(a2), bg))
+    ref2 = a2.astype(np.float64) @ (w.T if kind.startswith("weight") else b).astype(np.float64)
+    assert np.abs(got2 - ref2).max() / np.abs(ref2).max() < 1e-5
+
+
 def test_matmul_sweep_shape_linearity(gpu):
     """Full op-sweep size [16,1024,1024]^2 (too slow for the scalar oracle): checked through linearity,
     (A1+A2) B = A1 B + A2 B, and against a float64 numpy product on a sampled block."""
