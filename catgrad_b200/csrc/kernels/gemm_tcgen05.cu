@@ -337,12 +337,13 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
     // all lanes of the warp must agree before the warp-collective tcgen05.ld
     ok = __all_sync(0xffffffffu, ok);
     if (ok && SPLITK) {
-      // park the f32 partial tile in the (now idle) operand ring: row r at r * (BN + 4) floats
+      // park the f32 partial tile in the (now idle) operand ring: row r at r * (BN + 4) floats; warps whose 32 rows
+      // lie beyond M have nothing to park (a decode batch of 32 rows uses one warp of the four)
       tc_fence_after();
       const int q = warp & 3;
       float* prow = reinterpret_cast<float*>(smem) + (size_t)(q * 32 + lane) * (BN + 4);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < BN && m0 + q * 32 < M; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
@@ -362,7 +363,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
       const bool vec_ok = (g.ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (((uintptr_t)g.res & 15) == 0) &&
                           (g.c_outer % 8 == 0) && (g.c_inner % 8 == 0);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < BN && m0 + q * 32 < M; c0 += 32) {   // a warp whose 32 rows lie beyond M stores nothing
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
@@ -423,12 +424,14 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
     // every thread of every CTA of the cluster passes both barriers, whatever happened before
     cluster_sync_all();
     const int Z = (int)gridDim.z;
-    const int rows_per = BM / Z;
+    const int rows_valid = M - m0 < BM ? M - m0 : BM;   // rows of this tile that exist
+    const int rows_per = (rows_valid + Z - 1) / Z;      // CTA z reduces rows [z * rows_per, (z + 1) * rows_per)
     if (warp >= 2 && !*abort_flag) {
       const int t = threadIdx.x - 64;  // 0..127
       const bool vec_ok = (g.ldc % 4 == 0) && (((uintptr_t)C & 7) == 0);
       for (int item = t; item < rows_per * (BN / 4); item += 128) {
         const int rr = bz * rows_per + item / (BN / 4), c4 = (item % (BN / 4)) * 4;
+        if (rr >= rows_valid) break;
         const float* src = reinterpret_cast<const float*>(smem) + (size_t)rr * (BN + 4) + c4;
         float4 part[8];
 #pragma unroll
