@@ -3,11 +3,11 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|c3|c4|c5|tiny|sweep]
 
 One "step" is one decode step of the whole batch (one new token per sequence).
-  N = 1  : Llama-3.2-1B shape, bf16, batch 1, 512-token prompt, then K timed decode steps (baseline config 3).
-           The batch-sharded workload (config 4: 256 sequences x 128 prompt tokens) is timed too and reported
-           under "c4" so that the N>1 runs have their single-GPU point.
-  N > 1  : config 4: the 256 sequences are split evenly over the ranks (one process per GPU, no collective on
-           the data path; the generated ids are gathered once at the end).  Total work is fixed: strong scaling.
+  Every N: baseline config 4, the configuration the metric is quoted on ("1/2/4/8 B200"): Llama-3.2-1B shape, bf16,
+           256 sequences x 128-token prompt, split evenly over the N ranks (one process per GPU, no collective on the
+           data path; the generated ids are gathered once at the end).  Total work is fixed: strong scaling.
+  N = 1  : additionally times baseline config 3 (batch 1, 512-token prompt: the configuration the 70 %-of-roofline
+           target is stated on) and reports it under "c3" with its own roofline; `--workload c3` makes it the line.
 `value` is decode tokens/s with everything resident on the device (CUDA-graph replay, ids fed back on the
 device); `e2e` is the same loop driven like the reference's runner, one host round trip per token: the token
 ids are copied host->device, the step runs, the new ids are read back (examples/llama/main.rs:1016-1037).
@@ -39,6 +39,9 @@ import catgrad_b200 as cb  # noqa: E402
 HBM_NOMINAL_GBS = 8000.0
 # (8.44 + 67.18 + 33.62 + 12.66) MB x 16 layers + 525.3 MB lm_head, DRAM bytes measured by ncu per launch
 TRAFFIC_PER_STEP_B1 = int((8.44e6 + 67.18e6 + 33.62e6 + 12.66e6) * 16 + 525.3e6)
+# batch 256 on one GPU: per layer [q;k;v] 12.73 + o_proj 8.67 + down_proj 34.23 MB (ncu, split-K summary), [gate;up]
+# 67.11 MB and lm_head 525.3 MB (not captured: their weight bytes), attention 70.1 MB (ncu, context ~135)
+TRAFFIC_PER_STEP_C4 = int((12.73e6 + 8.67e6 + 34.23e6 + 67.11e6 + 70.1e6) * 16 + 525.3e6)
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -168,7 +171,7 @@ def run_decode_workload(be, cfg, params, batch, prompt_len, steps, warmup, dev_i
     return res
 
 
-def cpu_baseline_sample(cfg, weights_f32, prompt_len=8, steps=2):
+def cpu_baseline_sample(cfg, weights_f32, prompt_len=8, steps=2, batch=1):
     """The oracle (CPU restatement of the reference's ndarray path, 1 thread) on a bounded sample of the workload:
     a short prefill, then `steps` decode steps through the op-by-op interpreter, f32 (the ndarray backend has no
     bf16).  Returns decode tokens/s."""
@@ -179,8 +182,8 @@ def cpu_baseline_sample(cfg, weights_f32, prompt_len=8, steps=2):
     params = cb.upload_weights(oracle, weights_f32, cb.Dtype.F32)
     term = cb.llama_term(oracle, cfg)
     interp = cb.Interpreter(oracle, params)
-    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(1, prompt_len), dtype=np.uint32)
-    in_k, in_v = cb.empty_state_cache(oracle, cfg, 1, cb.Dtype.F32)
+    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(batch, prompt_len), dtype=np.uint32)
+    in_k, in_v = cb.empty_state_cache(oracle, cfg, batch, cb.Dtype.F32)
     x = ids
     times = []
     for i in range(steps + 1):
@@ -189,12 +192,12 @@ def cpu_baseline_sample(cfg, weights_f32, prompt_len=8, steps=2):
         last = oracle.to_numpy(r[0])[:, -1, 0]
         times.append(time.perf_counter() - t0)
         in_k, in_v = r[1], r[2]
-        x = last.reshape(1, 1).astype(np.uint32)
+        x = last.reshape(batch, 1).astype(np.uint32)
     dec = times[1:]
-    return {"value": len(dec) / sum(dec), "unit": "tok/s", "cores": 1, "kind": "port",
-            "sample": f"oracle/ndarray_ref (1 thread, f32): prefill of {prompt_len} tokens ({times[0]:.1f} s) then "
-                      f"{steps} decode steps of the same model ({sum(dec):.1f} s)",
-            "prefill_tok_s": prompt_len / times[0]}
+    return {"value": batch * len(dec) / sum(dec), "unit": "tok/s", "cores": 1, "kind": "port",
+            "sample": f"oracle/ndarray_ref (1 thread, f32): {batch} sequence(s), prefill of {prompt_len} tokens "
+                      f"({times[0]:.1f} s) then {steps} decode steps of the same model ({sum(dec):.1f} s)",
+            "prefill_tok_s": batch * prompt_len / times[0]}
 
 
 def timed_op(be, fn, iters=10, flush_bytes=256 << 20):
@@ -278,7 +281,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="profiling aid: override the number of sequences (c3/c4)")
     ap.add_argument("--prompt", type=int, default=0, help="profiling aid: override the prompt length (c3/c4)")
-    ap.add_argument("--skip-c4", action="store_true", help="N=1 only: do not time the batch-sharded workload as well")
+    ap.add_argument("--skip-c4", action="store_true", help="with --workload c3: do not time config 4 as well")
+    ap.add_argument("--skip-c3", action="store_true", help="N=1 only: do not time config 3 (batch 1) as well")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -300,12 +304,14 @@ def main():
         if rank != 0:
             return
         w = cb.random_weights(cfg, seed=0)
-        base = cpu_baseline_sample(cfg, w, prompt_len=8, steps=max(1, min(args.steps, 2)))
+        ref_batch = 1   # one of the workload's sequences: the oracle is single-threaded and sequences are independent
+        base = cpu_baseline_sample(cfg, w, prompt_len=8, steps=max(1, min(args.steps, 2)), batch=ref_batch)
         line = {"impl": "reference", "metric": "decode tokens/s", "value": base["value"], "unit": "tok/s",
                 "n_gpus": args.gpus, "steps": max(1, min(args.steps, 2)), "warmup": 0,
-                "ms_per_step": 1e3 / base["value"], "higher_is_better": True, "scaling": "weak" if args.gpus == 1 else "strong",
+                "ms_per_step": 1e3 * ref_batch / base["value"], "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": f"{model_name}, batch 1, greedy decode on the host CPU (ndarray-path restatement)"},
+                "config": {"workload": f"{model_name}, {ref_batch} sequence(s) of the workload, greedy decode on the host CPU "
+                                       "(ndarray-path restatement)"},
                 "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
@@ -322,7 +328,7 @@ def main():
     be = cb.Backend(local_rank)
     hbm_peak, _, peak_src = measured_peaks()
     single = world == 1
-    workload = args.workload if args.workload != "auto" else ("c3" if single else "c4")
+    workload = args.workload if args.workload != "auto" else "c4"
     tensor_parallel = workload == "c5"
     comm = None
     if tensor_parallel:
@@ -384,7 +390,7 @@ def main():
     line = {
         "metric": "decode tokens/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-        "scaling": "weak" if single else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "strong" if workload in ("c4", "c5") else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{model_name} bf16, {batch_total} sequence(s) x {prompt_len}-token prompt, greedy decode, "
                                f"context {int(r['ctx_mid'] - args.steps / 2)}..{int(r['ctx_mid'] + args.steps / 2)}",
                    "global_batch": batch_total, "prompt_len": prompt_len,
@@ -407,11 +413,29 @@ def main():
                      "bytes_per_step": bytes_step,
                      "how": "algorithmic bytes of a step on one GPU (every weight it holds once + KV cache read + new KV "
                             "rows) / CUDA-event time of a step on the launching stream",
-                     # dram__bytes_read.sum + dram__bytes_write.sum of the gemv launches of one step, summed from the
-                     # ncu capture in profiles/gemv_fused_decode_llama1b_bf16.md (batch 1; weights only)
-                     "traffic": TRAFFIC_PER_STEP_B1 if (batch_total == 1 and workload == "c3") else None},
+                     # dram__bytes_read.sum + dram__bytes_write.sum of the launches of one step, summed from the ncu
+                     # captures under profiles/ (batch 1: the gemv launches; batch 256 on one GPU: GEMM + attention)
+                     "traffic": (TRAFFIC_PER_STEP_B1 if (batch_total == 1 and workload == "c3") else
+                                 TRAFFIC_PER_STEP_C4 if (workload == "c4" and batch == 256 and not args.prompt) else None)},
         "load_s": load_s,
     }
+    if workload == "c4" and not tensor_parallel:
+        line["roofline"]["kernel"] = ("one decode step = 64 gemm_tcgen05 launches (62 % of the device time, "
+                                      "profiles/decode_step_llama1b_bf16_batch256_launch_list.md) + attention + norms + greedy pick")
+    if single and workload == "c4" and args.workload == "auto" and not args.skip_c3:
+        # config 3: batch 1, 512-token prompt: the configuration the 70 %-of-HBM-roofline target is stated on
+        c3_steps = min(max(args.steps, 32), 128)
+        r3 = run_decode_workload(be, cfg, params, 1, 512, c3_steps, args.warmup, local_rank)
+        b3 = decode_bytes(cfg, 1, r3["ctx_mid"])
+        a3 = b3 / (r3["ms"] / c3_steps / 1e3) / 1e9
+        line["c3"] = {"workload": "1 sequence x 512-token prompt on one GPU", "decode_tok_s": c3_steps / (r3["ms"] / 1e3),
+                      "ms_per_step": r3["ms"] / c3_steps, "prefill_tok_s": r3["prefill_tok_s"], "prefill_ms": r3["prefill_ms"],
+                      "e2e_tok_s": r3["e2e_steps"] / (r3["e2e_ms"] / 1e3), "gpu_launches": r3["launches"],
+                      "roofline": {"bound": "hbm", "kernel": "65 gemv_fused_kernel launches per step (79 % of the device time, "
+                                   "profiles/decode_step_llama1b_bf16_launch_list.md)", "achieved": a3, "peak": hbm_peak,
+                                   "unit": "GB/s", "frac": a3 / hbm_peak, "peak_source": peak_src,
+                                   "frac_of_8TBs_nominal": a3 / HBM_NOMINAL_GBS, "bytes_per_step": b3,
+                                   "traffic": TRAFFIC_PER_STEP_B1}}
     if tensor_parallel:
         del comm
     if single and workload == "c3" and not args.skip_c4:
@@ -424,7 +448,7 @@ def main():
     if single and not args.no_cpu_baseline and not tensor_parallel:
         del params
         wf = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
-        line["cpu_baseline"] = cpu_baseline_sample(cfg, wf, prompt_len=8, steps=2)
+        line["cpu_baseline"] = cpu_baseline_sample(cfg, wf, prompt_len=8, steps=2, batch=1)
         line["cpu_baseline"]["host"] = {"nproc": os.cpu_count()}
     print(json.dumps(line))
     if dist is not None:

@@ -100,11 +100,16 @@ def test_many_sequences_use_the_warp_per_head_attention_and_match_solo_runs(gpu)
         assert helpers.rel_err(solo.last_logits()[0], logits[b]) <= REL_F32
 
 
-@pytest.mark.parametrize("B", [96, 304])
-def test_many_sequences_bf16_gqa(gpu, B):
-    """Same check in bf16 with grouped heads.  96 sequences: one warp per query head (the 4 heads of a kv head share a
-    CTA); 304 sequences x 2 kv heads: one warp per (kv head, sequence) computing its 4 query heads."""
+@pytest.mark.parametrize("B,kv_heads", [(96, 2), (304, 2), (80, 1)])
+def test_many_sequences_bf16_gqa(gpu, B, kv_heads):
+    """Same check in bf16 with grouped heads.  With 2 kv heads (96 and 304 sequences) there are at least as many
+    (kv head, sequence) pairs as SMs: one warp per pair computes its 4 query heads.  80 sequences x 1 kv head is below
+    that but has 640 (head, sequence) pairs: one warp per query head, the 8 heads of the kv head sharing a CTA."""
     cfg, wb, _ = small_bf16_model()
+    if kv_heads != cfg.num_key_value_heads:
+        cfg = cb.LlamaConfig(512, 1536, 2, 8, kv_heads, 4096, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=True)
+        w = cb.random_weights(cfg, seed=0)
+        wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
     ids = np.random.default_rng(6).integers(0, cfg.vocab_size, size=(B, 20), dtype=np.uint32)
     pg = cb.upload_weights(gpu, wb, Dtype.BF16)
     runner = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=B, max_positions=40)
