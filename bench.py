@@ -258,6 +258,7 @@ def run_op_sweep(be):
             s = be.sum(e)
             return be.cast(be.div(e, be.broadcast(s, xf.shape)), dt)
         add_row("softmax [8192,4096] (nn::softmax op graph)", timed_op(be, softmax_graph), 2 * r_np.size * es)
+        add_row("softmax [8192,4096] (fused kernel, cg_softmax)", timed_op(be, lambda: be.softmax(r)), 2 * r_np.size * es)
         a, b = be.from_numpy(a_np, dt), be.from_numpy(b_np, dt)
         add_row("matmul [16,1024,1024]x[16,1024,1024]", timed_op(be, lambda: be.matmul(a, b)), 3 * a_np.size * es,
                 flops=2 * 16 * 1024 ** 3)

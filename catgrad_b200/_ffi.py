@@ -113,6 +113,7 @@ CUDA_ONLY = {
                                   C.c_void_p, C.c_uint64, c_void_pp]),
     "random_normal": (C.c_int, [_CTX, C.c_uint64, C.c_float, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
                                 C.c_int, c_void_pp]),
+    "softmax": (C.c_int, [_CTX, C.c_void_p, c_void_pp]),
     "comm_create": (C.c_int, [_CTX, C.c_int, C.c_int, C.c_uint64, c_void_pp]),
     "comm_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
     "comm_attach": (C.c_int, [C.c_void_p, C.c_void_p]),

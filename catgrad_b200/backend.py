@@ -202,6 +202,12 @@ class Backend:
     def cast(self, x, target_dtype):
         return self._out(self._ns.cast, x.handle, int(target_dtype))
 
+    def softmax(self, x):
+        """Fused last-axis softmax (stdlib nn::softmax in one kernel; CUDA library only, not a trait method)."""
+        if not hasattr(self._ns, "softmax"):
+            raise BackendError(Status.CUDA, "the fused softmax exists only in the CUDA library")
+        return self._out(self._ns.softmax, x.handle)
+
     def matmul(self, lhs, rhs):
         return self._out(self._ns.matmul, lhs.handle, rhs.handle)
 

@@ -463,6 +463,19 @@ Tensor CudaBackend::reduce(int kind, const Tensor& x) {
   check_launch("reduce");
   return t;
 }
+Tensor CudaBackend::softmax(const Tensor& x) {
+  CG_CHECK(x.rank() >= 1, ERR_SHAPE_MISMATCH, "softmax needs rank >= 1");
+  CG_CHECK(x.dt == Dtype::F32 || x.dt == Dtype::BF16 || x.dt == Dtype::F16, ERR_UNSUPPORTED_DTYPE,
+           "softmax is defined for f32, f16 and bf16");
+  Tensor c = contiguous(x);
+  Tensor t = empty(x.shape, x.dt);
+  const int64_t n = x.shape.back();
+  if (t.size() == 0) return t;
+  CG_CHECK(t.size() / n <= 0x7fffffffll, ERR_INVALID_ARG, "softmax: too many rows");
+  cgk::launch_softmax((int)x.dt, c.raw(), t.raw(), t.size() / n, n, stream_);
+  check_launch("softmax");
+  return t;
+}
 Tensor CudaBackend::max(const Tensor& x) { return reduce(cgk::R_MAX, x); }        // mod.rs:83
 Tensor CudaBackend::sum(const Tensor& x) { return reduce(cgk::R_SUM, x); }        // mod.rs:84
 Tensor CudaBackend::argmax(const Tensor& x) { return reduce(cgk::R_ARGMAX, x); }  // mod.rs:85

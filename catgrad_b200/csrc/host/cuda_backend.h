@@ -78,6 +78,7 @@ class CudaBackend : public Backend {
   void guard() const;  // makes this context's device current
   Tensor empty(const Shape& shape, Dtype dt);
   Tensor contiguous(const Tensor& x);
+  Tensor softmax(const Tensor& x);   // not in the trait: stdlib nn::softmax (nn/mod.rs:168-179) fused, last axis
   void check_launch(const char* what);
   void check_device_errors();  // reads the sticky error word; call only at synchronising points
   cudaStream_t stream() const { return stream_; }

@@ -1209,6 +1209,18 @@ int cg_random_normal(cg_ctx* ctx, uint64_t seed, float std, uint64_t rows, uint6
   CG_API_END(ctx)
 }
 
+// Fused last-axis softmax (the graph of stdlib nn::softmax, nn/mod.rs:168-179, in one kernel).  Not part of the trait.
+int cg_softmax(cg_ctx* ctx, const cg_tensor* x, cg_tensor** out) {
+  CG_API_BEGIN
+  CG_CHECK(ctx && ctx->be && x && out, ERR_BAD_HANDLE, "null argument");
+  CudaBackend* be = static_cast<CudaBackend*>(ctx->be.get());
+  be->guard();
+  cg_tensor* h = new cg_tensor();
+  h->t = be->softmax(x->t);
+  *out = h;
+  CG_API_END(ctx)
+}
+
 int cg_flush_l2(cg_ctx* ctx, uint64_t bytes) {
   CG_API_BEGIN
   CG_CHECK(ctx && ctx->be, ERR_BAD_HANDLE, "null context");

@@ -28,6 +28,8 @@ enum { R_SUM = 0, R_MAX = 1, R_ARGMAX = 2 };
 // strides in vw.sa) and the inner stride is `inner_stride`.  Output is contiguous [rows].
 void launch_reduce(int kind, int dtype, const View4& outer, long long rows, long long n, long long inner_stride,
                    const void* a, void* o, int sm_count, cudaStream_t st);
+// out = softmax over the last axis of contiguous x [rows, n] (f32, bf16 or f16): the nn::softmax graph in one kernel.
+void launch_softmax(int dtype, const void* x, void* out, long long rows, long long n, cudaStream_t st);
 // out[o, j, i] = x[o, idx[j], i]; x is contiguous [outer, dim, inner]; idx has n_idx entries (stride idx_stride).
 void launch_gather(int elem_size, const void* x, const unsigned* idx, long long idx_stride, void* out, long long outer,
                    long long dim, long long n_idx, long long inner, unsigned* err, int sm_count, cudaStream_t st);

@@ -268,6 +268,120 @@ inline int grid_for(long long items, int sm) {
 }
 }  // namespace
 
+// ---- fused last-axis softmax: the graph of stdlib nn::softmax (nn/mod.rs:168-179) in one pass --------------
+// cast to f32, subtract the row maximum (folded from f32::MIN like `max`, ndarray.rs:656-661), exp, divide by the row
+// sum, cast back.  One CTA per row, the row kept in registers (up to 256 x ITEMS x VEC elements); rows longer than
+// that are re-read from global memory (L2) for the second and third pass.
+template <class T, int ITEMS>
+__global__ void __launch_bounds__(256) softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ out, long long n) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ float red[8];
+  const T* xr = x + (long long)blockIdx.x * n;
+  T* orow = out + (long long)blockIdx.x * n;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float v[ITEMS][VEC];
+  float mx = -FLT_MAX;
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    const long long t0 = ((long long)j * 256 + threadIdx.x) * VEC;
+    if (t0 < n) {
+      const Vec<T, VEC> in = *reinterpret_cast<const Vec<T, VEC>*>(xr + t0);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        v[j][i] = Elem<T>::load(in.v[i]);
+        mx = fmaxf(mx, v[j][i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
+  __syncthreads();
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    const long long t0 = ((long long)j * 256 + threadIdx.x) * VEC;
+    if (t0 < n) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        v[j][i] = expf(v[j][i] - mx);
+        sum += v[j][i];
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  sum = ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    const long long t0 = ((long long)j * 256 + threadIdx.x) * VEC;
+    if (t0 < n) {
+      Vec<T, VEC> o;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o.v[i] = Elem<T>::store(v[j][i] / sum);
+      *reinterpret_cast<Vec<T, VEC>*>(orow + t0) = o;
+    }
+  }
+}
+
+// any row length and alignment: three passes over global memory (the row stays in L2)
+template <class T>
+__global__ void __launch_bounds__(256) softmax_rows_generic_kernel(const T* __restrict__ x, T* __restrict__ out, long long n) {
+  __shared__ float red[8];
+  const T* xr = x + (long long)blockIdx.x * n;
+  T* orow = out + (long long)blockIdx.x * n;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float mx = -FLT_MAX;
+  for (long long t = threadIdx.x; t < n; t += 256) mx = fmaxf(mx, Elem<T>::load(xr[t]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
+  __syncthreads();
+  float sum = 0.f;
+  for (long long t = threadIdx.x; t < n; t += 256) sum += expf(Elem<T>::load(xr[t]) - mx);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  sum = ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
+  for (long long t = threadIdx.x; t < n; t += 256) orow[t] = Elem<T>::store(expf(Elem<T>::load(xr[t]) - mx) / sum);
+}
+
+template <class T>
+void launch_softmax_t(const void* x, void* out, long long rows, long long n, cudaStream_t st) {
+  constexpr int VEC = 16 / sizeof(T);
+  const bool vec = n % VEC == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  const long long per_item = 256ll * VEC;
+  if (vec && n <= per_item * 1)
+    softmax_rows_kernel<T, 1><<<(unsigned)rows, 256, 0, st>>>((const T*)x, (T*)out, n);
+  else if (vec && n <= per_item * 2)
+    softmax_rows_kernel<T, 2><<<(unsigned)rows, 256, 0, st>>>((const T*)x, (T*)out, n);
+  else if (vec && n <= per_item * 4)
+    softmax_rows_kernel<T, 4><<<(unsigned)rows, 256, 0, st>>>((const T*)x, (T*)out, n);
+  else if (vec && n <= per_item * 8)
+    softmax_rows_kernel<T, 8><<<(unsigned)rows, 256, 0, st>>>((const T*)x, (T*)out, n);
+  else
+    softmax_rows_generic_kernel<T><<<(unsigned)rows, 256, 0, st>>>((const T*)x, (T*)out, n);
+}
+
+void launch_softmax(int dtype, const void* x, void* out, long long rows, long long n, cudaStream_t st) {
+  switch (dtype) {
+    case DT_F32: launch_softmax_t<float>(x, out, rows, n, st); break;
+    case DT_BF16: launch_softmax_t<__nv_bfloat16>(x, out, rows, n, st); break;
+    default: launch_softmax_t<__half>(x, out, rows, n, st); break;
+  }
+}
+
 void launch_reduce(int kind, int dtype, const View4& outer, long long rows, long long n, long long inner_stride,
                    const void* a, void* o, int sm, cudaStream_t st) {
   if (rows <= 0) return;

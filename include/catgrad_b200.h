@@ -245,6 +245,10 @@ cg_status cg_ctx_stats(cg_ctx*, uint64_t stats[4] /* live bytes, cached bytes, c
 cg_status cg_random_normal(cg_ctx*, uint64_t seed, float std, uint64_t rows, uint64_t cols, uint64_t row0,
                            uint64_t col0, uint64_t full_cols, cg_dtype dtype, cg_tensor** out);
 
+/* Fused softmax over the last axis: what the graph of stdlib nn::softmax (nn/mod.rs:168-179: cast f32, x - max,
+ * exp, / sum, cast back) computes, in one kernel.  Not a trait method; a plan compiler would substitute it. */
+cg_status cg_softmax(cg_ctx*, const cg_tensor* x, cg_tensor** out);
+
 /* Writes `bytes` of device memory on the context's stream (used by benchmarks to evict L2). */
 cg_status cg_flush_l2(cg_ctx*, uint64_t bytes);
 

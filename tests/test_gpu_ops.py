@@ -316,6 +316,31 @@ def test_f32_matmul_on_tensor_cores_from_split_operands(gpu, case):
     assert np.abs(got2 - ref2).max() / np.abs(ref2).max() < 1e-5
 
 
+@pytest.mark.parametrize("dtype", [Dtype.F32, Dtype.BF16], ids=lambda d: d.name)
+@pytest.mark.parametrize("shape", [(7, 33), (64, 1024), (5, 3, 4096), (3, 10000), (4, 40000)], ids=str)
+def test_fused_softmax_equals_the_nn_softmax_graph(oracle, gpu, dtype, shape):
+    """cg_softmax against the nine-op graph of stdlib nn::softmax run on the oracle (cast f32, x - max, exp, / sum,
+    cast back): f32 to 1e-6, bf16 to one bf16 ulp of the largest probability; rows sum to 1."""
+    rng = np.random.default_rng(sum(shape))
+    x = rng.uniform(-6, 6, shape).astype(np.float32)
+    x[0, ..., 0] = 30.0     # a dominant entry: the others underflow towards 0 without overflow anywhere
+    xo, xg = both(oracle, gpu, x, dtype)
+
+    def graph(be, t):
+        xf = be.cast(t, Dtype.F32)
+        e = be.exp(be.sub(xf, be.broadcast(be.max(xf), xf.shape)))
+        return be.cast(be.div(e, be.broadcast(be.sum(e), xf.shape)), dtype)
+    want = oracle.to_f32(graph(oracle, xo))
+    got = gpu.to_f32(gpu.softmax(xg))
+    tol = 1e-6 if dtype == Dtype.F32 else 2 ** -8
+    assert np.abs(got - want).max() <= tol
+    assert np.abs(got.sum(-1) - 1.0).max() <= (1e-5 if dtype == Dtype.F32 else 2e-2)
+    # a strided view goes through a contiguous copy
+    if len(shape) == 2:
+        xt = gpu.transpose(gpu.from_numpy(np.ascontiguousarray(x.T), dtype), 0, 1)
+        np.testing.assert_array_equal(gpu.to_f32(gpu.softmax(xt)), got)
+
+
 def test_matmul_sweep_shape_linearity(gpu):
     """Full op-sweep size [16,1024,1024]^2 (too slow for the scalar oracle): checked through linearity,
     (A1+A2) B = A1 B + A2 B, and against a float64 numpy product on a sampled block."""
