@@ -1,7 +1,7 @@
 """Writes tests/golden/reference_vectors.json: the known-answer vectors of the reference's own tests for the
 backend/interpreter path, transcribed with their source locations (paths inside hellas-ai/catgrad).
 
-When the reference checkout is available (first argument, default /root/reference) every case is checked
+When a checkout of the reference is given (first argument, or the environment variable CATGRAD_REFERENCE) every case is checked
 against the cited lines: each number of the case must appear as a literal in that line range.  The JSON is what
 the test-suite reads; this script is only needed to regenerate or re-verify it.
 
@@ -187,8 +187,8 @@ def verify(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    if os.path.isdir(ref_root):
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CATGRAD_REFERENCE", "")
+    if ref_root and os.path.isdir(ref_root):
         bad = verify(ref_root)
         if bad:
             for b in bad:
