@@ -206,8 +206,8 @@ struct Plan {
   }
 
   void rmsnorm(const void* in, const void* gain, void* out, int64_t rows, int64_t H, int64_t row_mul, int64_t row_off) {
-    cgk::rmsnorm_kernel<T><<<(int)rows, 256, 0, st>>>((const T*)in, (const T*)gain, (T*)out, (int)H, m.cfg.rms_norm_eps,
-                                                      row_mul, row_off);
+    launch(cgk::rmsnorm_kernel<T>, dim3((unsigned)rows), dim3(256), 0, (const T*)in, (const T*)gain, (T*)out, (int)H,
+           m.cfg.rms_norm_eps, (long long)row_mul, (long long)row_off);
     launched("rmsnorm");
   }
   void add_inplace(void* xx, const void* y, int64_t n) {
@@ -558,7 +558,8 @@ struct Plan {
       } else {
         rmsnorm(x, w.post_norm, m.xn.raw(), M, H, 1, 0);
         gemm(m.xn.raw(), H, w.gate_up, m.g.raw(), M, 2 * F, H);   // one product over the stacked [gate; up]
-        cgk::silu_mul_packed_kernel<T><<<grid_for(M * F / (16 / sizeof(T))), 256, 0, st>>>((const T*)m.g.raw(), hbuf, M, (int)F);
+        launch(cgk::silu_mul_packed_kernel<T>, dim3((unsigned)grid_for(M * F / (16 / sizeof(T)))), dim3(256), 0,
+               (const T*)m.g.raw(), hbuf, (long long)M, (int)F);
         launched("silu_mul");
       }
       if (gemv_ok(M, F)) {

@@ -101,6 +101,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ in, 
                                                       long long row_off) {
   __shared__ float scratch[8];
   pdl_launch_dependents();   // a GEMM that follows may start fetching its weight tiles
+  pdl_wait();                // no-op unless launched with programmatic stream serialization
   const T* x = in + ((long long)blockIdx.x * row_mul + row_off) * H;
   T* y = out + (long long)blockIdx.x * H;
   float ss = 0.f;
@@ -1193,6 +1194,7 @@ __global__ void __launch_bounds__(256) silu_mul_packed_kernel(const T* __restric
                                                               int F) {
   constexpr int VEC = 16 / sizeof(T);
   pdl_launch_dependents();   // the down projection that follows may start fetching its weight tiles
+  pdl_wait();
   const int per = F / VEC;
   const long long total = rows * per;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
