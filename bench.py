@@ -64,7 +64,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -78,7 +78,7 @@ class ClockSampler:
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -141,11 +141,12 @@ def run_decode_workload(be, cfg, params, batch, prompt_len, steps, warmup, dev_i
     res["prefill_ms"] = min(pre_ms[1:])
     res["prefill_tok_s"] = batch * prompt_len / (res["prefill_ms"] / 1e3)
     # ---- device-resident decode ----
+    sampler = ClockSampler(dev_index)
+    sampler.start()          # nvidia-smi needs ~0.1 s to come up: start it before the warm-up steps
+    time.sleep(0.2)
     runner.decode(max(warmup, 3))
     l0 = runner.launch_count
     ctx0 = runner.context_len
-    sampler = ClockSampler(dev_index)
-    sampler.start()
     be.synchronize()
     be._ns.event_record(be._ctx, 2)
     ids = runner.decode(steps)
