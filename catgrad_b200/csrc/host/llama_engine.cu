@@ -217,8 +217,29 @@ struct Plan {
 
   // Decode attention with one warp per (kv head, sequence): taken when that alone gives every SM a warp or
   // more, for bf16, GQA groups of 1/2/4/8 and contexts up to 512 (a captured graph keeps the choice of its first step).
+  // two warps per (kv head, sequence), two pairs per CTA
+  template <int HD, int REP>
+  void pair_attention_launch(const cgk::AttnArgs& a, int64_t B, int64_t nkv, unsigned* err) {
+    const size_t per_pair = ((size_t)2 * HD * sizeof(T) + (size_t)(2 * REP * HD + 4 * REP + REP * (m.P + 1)) * 4 + 15) / 16 * 16;
+    const size_t smem = 2 * per_pair;
+    auto kern = cgk::attn_decode_pair_kernel<__nv_bfloat16, HD, REP>;
+    static size_t smem_set_dev[64] = {0};
+    size_t& smem_set = smem_set_dev[m.be->device() & 63];
+    if (smem > 40 * 1024 && smem > smem_set) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      smem_set = smem;
+    }
+    launch(kern, dim3((unsigned)((nkv + 1) / 2), (unsigned)B), dim3(128), smem, a, err);
+  }
   template <int HD, int REP>
   void group_attention_launch(const cgk::AttnArgs& a, int64_t B, int64_t nkv, unsigned* err) {
+    static const bool one_warp = std::getenv("CATGRAD_B200_ATTN_ONE_WARP") != nullptr;   // A/B aid
+    // measured (8 kv heads): two warps per pair +8 % tokens/s at batch 32, -4 % at batch 256, where one warp per
+    // pair already fills every SM
+    if (!one_warp && B * nkv <= 8 * (int64_t)sm) {
+      pair_attention_launch<HD, REP>(a, B, nkv, err);
+      return;
+    }
     size_t per_warp = (size_t)2 * HD * sizeof(T) + (size_t)REP * HD * 4 + (size_t)REP * (m.P + 1) * 4;
     per_warp = (per_warp + 15) / 16 * 16;
     size_t smem = 4 * per_warp;

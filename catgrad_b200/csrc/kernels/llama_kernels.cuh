@@ -868,6 +868,183 @@ __global__ void __launch_bounds__(128) attn_decode_group_kernel(AttnArgs a, unsi
   }
 }
 
+// ---- the same with TWO warps per (kv head, sequence): the keys of a pair are interleaved in blocks of 32 between
+// its warps (half the dependent load rounds per warp); maxima, sums and the partial P.v meet in shared memory behind
+// 64-thread named barriers.  CTA = 2 pairs.  Rounding points unchanged; summation order: warp 0's keys, then warp 1's.
+__device__ __forceinline__ void pair_barrier(int pair) { asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory"); }
+
+template <class T, int HD, int REP>
+__global__ void __launch_bounds__(128) attn_decode_pair_kernel(AttnArgs a, unsigned* err) {
+  static_assert(sizeof(T) == 2, "16-byte rows of 8 elements");
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int CH = HD / 8, KG = 32 / CH, half = HD / 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = warp >> 1, hw = warp & 1, pl = hw * 32 + lane;   // lane index within the pair: 0..63
+  const int kvh = blockIdx.x * 2 + pair, b = blockIdx.y;
+  // per pair: k_new[HD] T | v_new[HD] T | q[REP][HD] | acc_x[REP][HD] | red[2][2*REP] | p[REP][P + 1]   (f32 after the T rows)
+  const size_t per_pair = ((size_t)2 * HD * sizeof(T) + (size_t)(2 * REP * HD + 4 * REP + REP * (a.P + 1)) * 4 + 15) / 16 * 16;
+  unsigned char* base = smem_raw + (size_t)pair * per_pair;
+  T* k_new = reinterpret_cast<T*>(base);
+  T* v_new = k_new + HD;
+  float* q_s = reinterpret_cast<float*>(v_new + HD);
+  float* acc_x = q_s + REP * HD;
+  float* red = acc_x + REP * HD;        // [0..2*REP): maxima of warp 0 / 1, [2*REP..4*REP): sums
+  float* p_s = red + 4 * REP;
+  const int pp = a.P + 1;
+  pdl_launch_dependents();
+  pdl_wait();
+  const bool live = kvh < a.nkv;
+  const int pos = *a.ctx_len;
+  if (pos >= a.P) {
+    if (threadIdx.x == 0) atomicOr(err, DEV_ERR_INDEX_OOB);
+    return;
+  }
+  const int total = pos + 1;
+  const int kv_i = live ? kvh : 0;      // dead pairs (odd nkv) walk pair 0's data and store nothing: barriers stay matched
+  T* kc = (T*)a.kc + ((long long)b * a.nkv + kv_i) * a.P * HD;
+  T* vc = (T*)a.vc + ((long long)b * a.nkv + kv_i) * a.P * HD;
+  const float* ct = a.cos_t + (long long)pos * half;
+  const float* st = a.sin_t + (long long)pos * half;
+  for (int i = pl; i < REP * half; i += 64) {
+    const int h = i / half, j = i - h * half;
+    const T* qsrc = (const T*)a.q + (long long)b * a.q_row_stride + (kv_i * REP + h) * HD;
+    float x1 = Elem<T>::load(qsrc[j]), x2 = Elem<T>::load(qsrc[j + half]);
+    float c = ct[j], sn = st[j];
+    q_s[h * HD + j] = rt<T>(c * x1 + sn * (-x2));
+    q_s[h * HD + j + half] = rt<T>(c * x2 + sn * x1);
+  }
+  {
+    const T* ksrc = (const T*)a.k + (long long)b * a.k_row_stride + kv_i * HD;
+    const T* vsrc = (const T*)a.v + (long long)b * a.v_row_stride + kv_i * HD;
+    for (int i = pl; i < half; i += 64) {
+      float x1 = Elem<T>::load(ksrc[i]), x2 = Elem<T>::load(ksrc[i + half]);
+      float c = ct[i], sn = st[i];
+      T o1 = Elem<T>::store(c * x1 + sn * (-x2)), o2 = Elem<T>::store(c * x2 + sn * x1);
+      k_new[i] = o1;
+      k_new[i + half] = o2;
+      if (live) {
+        kc[(long long)pos * HD + i] = o1;
+        kc[(long long)pos * HD + i + half] = o2;
+      }
+    }
+    for (int i = pl; i < HD; i += 64) {
+      T vv = vsrc[i];
+      v_new[i] = vv;
+      if (live) vc[(long long)pos * HD + i] = vv;
+    }
+  }
+  pair_barrier(pair);
+  // scores: lane = key, keys pl, pl + 64, ...
+  float mx[REP];
+#pragma unroll
+  for (int h = 0; h < REP; ++h) mx[h] = -FLT_MAX;
+  for (int t = pl; t < total; t += 64) {
+    const uint4* krow = reinterpret_cast<const uint4*>(t == pos ? k_new : kc + (long long)t * HD);
+    uint4 kr[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) kr[c] = krow[c];
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      float d = 0.f;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const T* e = reinterpret_cast<const T*>(&kr[c]);
+        const float4 qa = *reinterpret_cast<const float4*>(q_s + h * HD + c * 8);
+        const float4 qb = *reinterpret_cast<const float4*>(q_s + h * HD + c * 8 + 4);
+        d = fmaf(qa.x, Elem<T>::load(e[0]), d);
+        d = fmaf(qa.y, Elem<T>::load(e[1]), d);
+        d = fmaf(qa.z, Elem<T>::load(e[2]), d);
+        d = fmaf(qa.w, Elem<T>::load(e[3]), d);
+        d = fmaf(qb.x, Elem<T>::load(e[4]), d);
+        d = fmaf(qb.y, Elem<T>::load(e[5]), d);
+        d = fmaf(qb.z, Elem<T>::load(e[6]), d);
+        d = fmaf(qb.w, Elem<T>::load(e[7]), d);
+      }
+      const float sres = rt<T>(rt<T>(d) / a.scale);
+      p_s[h * pp + t] = sres;
+      mx[h] = fmaxf(mx[h], sres);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < REP; ++h) {
+    const float m = warp_max(mx[h]);
+    if (lane == 0) red[hw * REP + h] = m;
+  }
+  pair_barrier(pair);
+  float sm_[REP];
+#pragma unroll
+  for (int h = 0; h < REP; ++h) {
+    const float m = fmaxf(red[h], red[REP + h]);
+    float sum = 0.f;
+    for (int t = pl; t < total; t += 64) {
+      const float e = expf(p_s[h * pp + t] - m);
+      p_s[h * pp + t] = e;
+      sum += e;
+    }
+    sm_[h] = warp_sum(sum);
+    if (lane == 0) red[2 * REP + hw * REP + h] = sm_[h];
+  }
+  pair_barrier(pair);
+#pragma unroll
+  for (int h = 0; h < REP; ++h) {
+    const float sum = red[2 * REP + h] + red[3 * REP + h];
+    for (int t = pl; t < total; t += 64) p_s[h * pp + t] = rt<T>(p_s[h * pp + t] / sum);
+  }
+  pair_barrier(pair);
+  // P.v: lane = (key group g, 16-byte chunk c); warp hw takes keys hw*KG + g, + 2*KG, ...
+  const int g = lane / CH, c = lane % CH;
+  float acc[REP][8];
+#pragma unroll
+  for (int h = 0; h < REP; ++h)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[h][i] = 0.f;
+#pragma unroll 4
+  for (int t = hw * KG + g; t < pos; t += 2 * KG) {
+    const uint4 vv = *reinterpret_cast<const uint4*>(vc + (long long)t * HD + c * 8);
+    const T* e = reinterpret_cast<const T*>(&vv);
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      const float ph = p_s[h * pp + t];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[h][i] = fmaf(ph, Elem<T>::load(e[i]), acc[h][i]);
+    }
+  }
+  if (g == 0 && hw == 1) {   // the new value row
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      const float ph = p_s[h * pp + pos];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[h][i] = fmaf(ph, Elem<T>::load(v_new[c * 8 + i]), acc[h][i]);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < REP; ++h)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float v = acc[h][i];
+#pragma unroll
+      for (int o = CH; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      acc[h][i] = v;
+    }
+  if (hw == 1 && g == 0) {
+#pragma unroll
+    for (int h = 0; h < REP; ++h)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc_x[h * HD + c * 8 + i] = acc[h][i];
+  }
+  pair_barrier(pair);
+  if (hw == 0 && g == 0 && live) {
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      uint4 ov;
+      T* o = reinterpret_cast<T*>(&ov);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = Elem<T>::store(acc[h][i] + acc_x[h * HD + c * 8 + i]);
+      *reinterpret_cast<uint4*>((T*)a.out + (long long)b * a.out_row_stride + (kvh * REP + h) * HD + c * 8) = ov;
+    }
+  }
+}
+
 // ---- decode attention for long contexts: keys split into chunks of 128 across CTAs ---------------------------
 // Two launches per layer, grid (chunk, kv head, sequence), 128 threads.  Same sub-graph and rounding points as
 // attn_decode_kernel (scores and probabilities are rounded to T exactly as there; only the f32 summation orders
