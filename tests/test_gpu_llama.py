@@ -100,11 +100,12 @@ def test_many_sequences_use_the_warp_per_head_attention_and_match_solo_runs(gpu)
         assert helpers.rel_err(solo.last_logits()[0], logits[b]) <= REL_F32
 
 
-@pytest.mark.parametrize("B,kv_heads", [(96, 2), (304, 2), (80, 1)])
+@pytest.mark.parametrize("B,kv_heads", [(96, 2), (600, 2), (80, 1)])
 def test_many_sequences_bf16_gqa(gpu, B, kv_heads):
-    """Same check in bf16 with grouped heads.  With 2 kv heads (96 and 304 sequences) there are at least as many
-    (kv head, sequence) pairs as SMs: one warp per pair computes its 4 query heads.  80 sequences x 1 kv head is below
-    that but has 640 (head, sequence) pairs: one warp per query head, the 8 heads of the kv head sharing a CTA."""
+    """Same check in bf16 with grouped heads.  With 2 kv heads there are at least as many (kv head, sequence) pairs as
+    SMs: 96 sequences take two warps per pair, 600 sequences (more than 8 pairs per SM) one warp per pair, each
+    computing the 4 query heads of the group.  80 sequences x 1 kv head is below that but has 640 (head, sequence)
+    pairs: one warp per query head, the 8 heads of the kv head sharing a CTA."""
     cfg, wb, _ = small_bf16_model()
     if kv_heads != cfg.num_key_value_heads:
         cfg = cb.LlamaConfig(512, 1536, 2, 8, kv_heads, 4096, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=True)
