@@ -122,11 +122,13 @@ def decode_bytes(cfg, batch, ctx_len):
 
 
 def run_decode_workload(be, cfg, params, batch, prompt_len, steps, warmup, dev_index, e2e_steps=None, name="",
-                        comm=None):
+                        comm=None, persistent=True):
     """Prefill, then W warm-up + K timed decode steps (device-resident), then the same through host round trips."""
     P = prompt_len + 2 * (warmup + steps) + 16
     runner = cb.LlamaRunner(be, cfg, params, cb.Dtype.BF16, max_batch=batch, max_positions=P, comm=comm,
                             max_tokens=batch * prompt_len)
+    if not persistent:
+        runner.set_persistent(False)
     prompts = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(batch, prompt_len), dtype=np.uint32)
     res = {}
     # ---- prefill (reported beside the headline) ----
@@ -168,6 +170,7 @@ def run_decode_workload(be, cfg, params, batch, prompt_len, steps, warmup, dev_i
     res["e2e_ms"] = (time.perf_counter() - t0) * 1e3
     res["e2e_steps"] = k
     res["batch"] = batch
+    res["persistent"] = runner.persistent_active
     del runner
     return res
 
@@ -283,6 +286,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="profiling aid: override the number of sequences (c3/c4)")
     ap.add_argument("--prompt", type=int, default=0, help="profiling aid: override the prompt length (c3/c4)")
+    ap.add_argument("--no-persistent", action="store_true",
+                    help="small batches: take the graph of per-sub-graph kernels instead of the persistent decode kernel")
     ap.add_argument("--skip-c4", action="store_true", help="with --workload c3: do not time config 4 as well")
     ap.add_argument("--skip-c3", action="store_true", help="N=1 only: do not time config 3 (batch 1) as well")
     args = ap.parse_args()
@@ -361,7 +366,8 @@ def main():
 
     if dist is not None:
         dist.barrier()
-    r = run_decode_workload(be, cfg, params, batch, prompt_len, args.steps, args.warmup, local_rank, comm=comm)
+    r = run_decode_workload(be, cfg, params, batch, prompt_len, args.steps, args.warmup, local_rank, comm=comm,
+                            persistent=not args.no_persistent)
     ms, e2e_ms, pre_ms = r["ms"], r["e2e_ms"], r["prefill_ms"]
     if dist is not None:
         import torch
@@ -427,7 +433,7 @@ def main():
     if single and workload == "c4" and args.workload == "auto" and not args.skip_c3:
         # config 3: batch 1, 512-token prompt: the configuration the 70 %-of-HBM-roofline target is stated on
         c3_steps = min(max(args.steps, 32), 128)
-        r3 = run_decode_workload(be, cfg, params, 1, 512, c3_steps, args.warmup, local_rank)
+        r3 = run_decode_workload(be, cfg, params, 1, 512, c3_steps, args.warmup, local_rank, persistent=not args.no_persistent)
         b3 = decode_bytes(cfg, 1, r3["ctx_mid"])
         a3 = b3 / (r3["ms"] / c3_steps / 1e3) / 1e9
         line["c3"] = {"workload": "1 sequence x 512-token prompt on one GPU", "decode_tok_s": c3_steps / (r3["ms"] / 1e3),

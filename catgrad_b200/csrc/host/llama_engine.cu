@@ -20,7 +20,7 @@
 #include "../kernels/elementwise.h"
 #include "../kernels/gemm_tcgen05.h"
 #include "../kernels/llama_kernels.cuh"
-#include "../kernels/llama_mega.cuh"
+#include "../kernels/llama_persist.cuh"
 #include "../kernels/matmul.h"
 #include "c_api_internal.h"
 #include "cuda_backend.h"
@@ -68,8 +68,10 @@ struct cg_llama {
   Tensor partials;            // u64 [Bmax, ceil(V/4096)]: stage-1 keys of the greedy pick (scratch)
   int argmax_chunks = 0;
   // persistent one-kernel decode step (batch <= 4)
-  Tensor mega_layers, mega_partials, mega_prof;
+  Tensor mega_layers, mega_partials, mega_prof, mega_att;
   bool mega_enabled = false;
+  bool mega_possible = false;   // cooperative launch available and no tensor parallelism
+  bool mega_last_step = false;  // the most recent decode step ran as the persistent kernel
   unsigned long long bar_base = 0;
   int mega_grid = 0;
   bool use_pdl = true;        // programmatic dependent launch between the kernels of a step
@@ -333,67 +335,55 @@ struct Plan {
     ++m.launches;
   }
 
-  // ---- the one-kernel decode step (llama_mega.cuh) ----
-  static int mega_mt(int64_t B) { return B <= 1 ? 1 : (B <= 2 ? 2 : 4); }
-  struct MegaGeom { bool ok = false; int nslots = 0; int xs_bytes = 0; size_t smem = 0; };
+  // ---- the one-kernel decode step (llama_persist.cuh) ----
+  struct MegaGeom { bool ok = false; int nslots = 0; int xs_bytes = 0; int xs_pitch = 0; size_t smem = 0; };
   MegaGeom mega_geom(int64_t B) const {
     MegaGeom g;
     const LlamaConfig& c = m.cfg;
-    if (!m.mega_enabled || B > 4) return g;
-    const int mt = mega_mt(B);
-    const int64_t kmax = std::max<int64_t>(std::max<int64_t>(c.hidden_size, c.intermediate_size), c.num_attention_heads * m.hd);
-    constexpr int VEC = 16 / sizeof(T);
-    const int64_t hd = m.hd;
-    int64_t attn_bytes = (m.P + 1 + (256 / (hd / VEC)) * hd) * 4;
-    int64_t xs = std::max<int64_t>(mt * kmax * (int64_t)sizeof(T), attn_bytes);
+    if (!m.mega_enabled || !std::is_same<T, __nv_bfloat16>::value || B > cgk::PK_MAX_B) return g;
+    const int64_t hd = m.hd, H = c.hidden_size, F = c.intermediate_size, NQ = c.num_attention_heads * hd,
+                  NKV = c.num_key_value_heads * hd, V = c.vocab_size, rep = c.num_attention_heads / c.num_key_value_heads;
+    if (!(rep == 1 || rep == 2 || rep == 4)) return g;
+    // whole 16-row tiles (8 + 8 for gate/up), whole 16-column K-steps, the norm loader holds 4 x 256 16-byte groups
+    if (NQ % 16 || NKV % 16 || H % 16 || V % 16 || F % 16 || H / 8 > 4 * cgk::PK_COMPUTE_THREADS) return g;
+    if (m.P > 16384) return g;   // attention chunk partials are combined by every CTA: keep that list short
+    const int64_t kmax = std::max<int64_t>(std::max<int64_t>(H, F), NQ);
+    const int64_t pitch = kmax * 2 + cgk::PK_XS_PAD;
+    int64_t xs = std::max<int64_t>(B * pitch, cgk::pk_att_smem_bytes((int)hd, (int)rep));
     xs = (xs + 127) / 128 * 128;
-    const int64_t tail = 8192;
     const int64_t budget = 227 * 1024;
-    int64_t nslots = (budget - xs - tail) / cgk::MEGA_SLOT_BYTES;
-    if (nslots > 8) nslots = 8;
-    if (nslots < 2) return g;
-    // every row of every matrix must fit one slot; the input loader holds at most 4 x 256 16-byte groups;
-    // the row split uses 32-bit arithmetic
-    if (kmax * (int64_t)sizeof(T) > cgk::MEGA_SLOT_BYTES) return g;
-    if (kmax / VEC > 1024) return g;
-    if (std::max<int64_t>(c.vocab_size, c.intermediate_size) * (m.mega_grid + 1) >= (1ll << 31)) return g;
+    int64_t nslots = (budget - xs - cgk::pk_tail_bytes()) / cgk::PK_SLOT_BYTES;
+    if (nslots > cgk::PK_MAX_SLOTS) nslots = cgk::PK_MAX_SLOTS;
+    if (nslots < 3) return g;
     g.ok = true;
     g.nslots = (int)nslots;
     g.xs_bytes = (int)xs;
-    g.smem = (size_t)(nslots * cgk::MEGA_SLOT_BYTES + xs + tail);
+    g.xs_pitch = (int)pitch;
+    g.smem = (size_t)(nslots * cgk::PK_SLOT_BYTES + xs + cgk::pk_tail_bytes());
     return g;
   }
-  template <int MT, int HD>
-  bool mega_launch_t(const cgk::MegaArgs& a, const MegaGeom& g) {
-    auto kern = m.mega_prof.defined() ? cgk::llama_decode_mega_kernel<T, MT, HD, true> : cgk::llama_decode_mega_kernel<T, MT, HD, false>;
-    static size_t smem_set[2] = {0, 0};
-    size_t& smem_set_ref = smem_set[m.mega_prof.defined() ? 1 : 0];
+  template <int HD, int REP>
+  bool mega_launch_t(const cgk::PkArgs& a, const MegaGeom& g) {
+    auto kern = m.mega_prof.defined() ? cgk::llama_decode_persistent_kernel<HD, REP, true> : cgk::llama_decode_persistent_kernel<HD, REP, false>;
+    static size_t smem_set_dev[64][2] = {};
+    size_t& smem_set_ref = smem_set_dev[m.be->device() & 63][m.mega_prof.defined() ? 1 : 0];
     if (g.smem > smem_set_ref) {
       cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
-      if (e0 != cudaSuccess) {
+      int per_sm = 0;
+      cudaError_t e1 = e0 == cudaSuccess ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, cgk::PK_THREADS, g.smem) : e0;
+      if (e1 != cudaSuccess || per_sm < 1) {
         cudaGetLastError();
-        std::fprintf(stderr, "[catgrad_b200] persistent decode kernel unavailable (shared memory %zu: %s); using the multi-kernel plan\n",
-                     g.smem, cudaGetErrorString(e0));
+        std::fprintf(stderr, "[catgrad_b200] persistent decode kernel unavailable (shared memory %zu, occupancy %d: %s); using the kernel-per-sub-graph plan\n",
+                     g.smem, per_sm, cudaGetErrorString(e1));
         m.mega_enabled = false;
         return false;
       }
       smem_set_ref = g.smem;
     }
-    int per_sm = 0;
-    cudaError_t e1 = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, cgk::MEGA_THREADS, g.smem);
-    if (e1 != cudaSuccess || per_sm < 1) {
-      cudaGetLastError();
-      cudaFuncAttributes fa;
-      cudaFuncGetAttributes(&fa, kern);
-      std::fprintf(stderr, "[catgrad_b200] persistent decode kernel unavailable (occupancy %d, %s, regs %d, smem %zu); using the multi-kernel plan\n",
-                   per_sm, cudaGetErrorString(e1), fa.numRegs, g.smem);
-      m.mega_enabled = false;
-      return false;
-    }
-    cgk::MegaArgs args = a;
+    cgk::PkArgs args = a;
     int xs_bytes = g.xs_bytes;
     void* params[] = {(void*)&args, (void*)&xs_bytes};
-    cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(a.G), dim3(cgk::MEGA_THREADS), params, g.smem, st);
+    cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(a.G), dim3(cgk::PK_THREADS), params, g.smem, st);
     if (e != cudaSuccess) throw Error(ERR_CUDA, std::string("cooperative launch of the decode kernel: ") + cudaGetErrorString(e));
     return true;
   }
@@ -402,17 +392,25 @@ struct Plan {
     MegaGeom g = mega_geom(B);
     if (!g.ok) return false;
     const LlamaConfig& c = m.cfg;
-    cgk::MegaArgs a{};
+    const int64_t rep = c.num_attention_heads / c.num_key_value_heads;
+    const int att_chunks = (int)((m.P + cgk::PK_ATT_CHUNK - 1) / cgk::PK_ATT_CHUNK);
+    if (!m.mega_att.defined())
+      m.mega_att = m.be->empty({(int64_t)std::min<int64_t>(m.max_batch, cgk::PK_MAX_B) * c.num_key_value_heads * att_chunks *
+                                cgk::pk_att_item_floats((int)m.hd, (int)rep)},
+                               Dtype::F32);
+    cgk::PkArgs a{};
     a.L = (int)c.num_hidden_layers; a.H = (int)c.hidden_size; a.F = (int)c.intermediate_size;
     a.NQ = (int)(c.num_attention_heads * m.hd); a.NKV = (int)(c.num_key_value_heads * m.hd);
     a.V = (int)c.vocab_size; a.nh = (int)c.num_attention_heads; a.nkv = (int)c.num_key_value_heads;
-    a.P = (int)m.P; a.B = (int)B; a.G = m.mega_grid; a.nslots = g.nslots;
+    a.P = (int)m.P; a.B = (int)B; a.G = m.mega_grid; a.nslots = g.nslots; a.xs_pitch = g.xs_pitch;
     a.eps = c.rms_norm_eps; a.scale = cgk_host_round((float)std::sqrt((float)m.hd));
     a.embed = m.embed; a.final_norm = m.final_norm; a.head = m.head;
-    a.layers = (const cgk::MegaLayer*)m.mega_layers.raw();
-    a.x = m.x.raw(); a.qkv = m.qkv.raw(); a.attn = m.attn.raw(); a.h = m.h.raw(); a.logits = m.logits.raw();
+    a.layers = (const cgk::PkLayer*)m.mega_layers.raw();
+    a.x = m.x.raw(); a.qkv = m.qkv.raw(); a.h = m.h.raw(); a.logits = m.logits.raw();
+    a.att = (float*)m.mega_att.raw(); a.att_chunks = att_chunks;
     a.kc = m.kc.raw(); a.vc = m.vc.raw();
     a.kv_layer_stride = m.max_batch * c.num_key_value_heads * m.P * m.hd;
+    a.kv_seq_stride = m.P * m.hd;
     a.cos_t = (const float*)m.cos_t.raw(); a.sin_t = (const float*)m.sin_t.raw();
     a.ids_cur = (unsigned*)m.ids_cur.raw(); a.out_ids = (unsigned*)m.ids_out.raw();
     a.ctx_len = (int*)m.words.raw(); a.step_no = (int*)m.words.raw() + 1; a.out_cap_steps = (int)m.out_cap_steps;
@@ -421,14 +419,11 @@ struct Plan {
     a.bar_base = m.bar_base;
     a.err = m.be->dev_err(); a.abort_word = (unsigned*)m.words.raw() + 2;
     a.prof = m.mega_prof.defined() ? (unsigned long long*)m.mega_prof.raw() : nullptr;
-    const int mt = mega_mt(B);
-    const bool hd64 = m.hd == 64;
-    bool ok;
-    if (mt == 1) ok = hd64 ? mega_launch_t<1, 64>(a, g) : mega_launch_t<1, 128>(a, g);
-    else if (mt == 2) ok = hd64 ? mega_launch_t<2, 64>(a, g) : mega_launch_t<2, 128>(a, g);
-    else ok = hd64 ? mega_launch_t<4, 64>(a, g) : mega_launch_t<4, 128>(a, g);
+    bool ok = false;
+    if (m.hd == 64) ok = rep == 1 ? mega_launch_t<64, 1>(a, g) : rep == 2 ? mega_launch_t<64, 2>(a, g) : mega_launch_t<64, 4>(a, g);
+    else ok = rep == 1 ? mega_launch_t<128, 1>(a, g) : rep == 2 ? mega_launch_t<128, 2>(a, g) : mega_launch_t<128, 4>(a, g);
     if (!ok) return false;
-    m.bar_base += (unsigned long long)(5 * c.num_hidden_layers + 1) * (unsigned long long)a.G;
+    m.bar_base += (unsigned long long)cgk::pk_barriers_per_step((int)c.num_hidden_layers) * (unsigned long long)a.G;
     ++m.launches;
     return true;
   }
@@ -826,9 +821,11 @@ void run_step(cg_llama& m, const unsigned* ids, int64_t B, int64_t S, bool allow
     bool done = m.dt == Dtype::BF16 ? Plan<__nv_bfloat16>(m).mega_step(B) : Plan<float>(m).mega_step(B);
     if (done) {
       m.host_ctx_len += 1;
+      m.mega_last_step = true;
       return;
     }
   }
+  if (S == 1) m.mega_last_step = false;
   if (m.dt == Dtype::BF16) Plan<__nv_bfloat16>(m).step(ids, B, S);
   else Plan<float>(m).step(ids, B, S);
   m.host_ctx_len += S;
@@ -954,20 +951,21 @@ int create_runner(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const cg_
   m->out_cap_steps = 0;
   {
     // table of per-layer weight pointers for the persistent decode kernel
-    std::vector<cgk::MegaLayer> tab;
-    for (auto& w : m->layers) tab.push_back(cgk::MegaLayer{w.in_norm, w.q, w.k, w.v, w.o, w.post_norm, w.gate, w.up, w.down});
-    m->mega_layers = be.empty({(int64_t)(tab.size() * sizeof(cgk::MegaLayer) / 4)}, Dtype::U32);
-    CG_CUDA(cudaMemcpyAsync(m->mega_layers.raw(), tab.data(), tab.size() * sizeof(cgk::MegaLayer), cudaMemcpyHostToDevice,
+    std::vector<cgk::PkLayer> tab;
+    for (auto& w : m->layers) tab.push_back(cgk::PkLayer{w.in_norm, w.q, w.k, w.v, w.o, w.post_norm, w.gate, w.up, w.down});
+    m->mega_layers = be.empty({(int64_t)(tab.size() * sizeof(cgk::PkLayer) / 4)}, Dtype::U32);
+    CG_CUDA(cudaMemcpyAsync(m->mega_layers.raw(), tab.data(), tab.size() * sizeof(cgk::PkLayer), cudaMemcpyHostToDevice,
                             be.stream()));
     CG_CUDA(cudaStreamSynchronize(be.stream()));
     m->mega_grid = be.sm_count();
-    m->mega_partials = be.zeros({(int64_t)m->mega_grid * 4 * 2}, Dtype::U32);
+    m->mega_partials = be.zeros({(int64_t)m->mega_grid * cgk::PK_MAX_B * 2}, Dtype::U32);
     int coop = 0;
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, be.device());
-    // opt-in: at the current tuning the graph of per-sub-graph kernels is faster
-    m->mega_enabled = coop != 0 && comm == nullptr && std::getenv("CATGRAD_B200_MEGA") != nullptr;
-    // CATGRAD_B200_MEGA_PROF: per-CTA cycle counters of the persistent kernel, printed by cg_llama_free
-    if (std::getenv("CATGRAD_B200_MEGA_PROF")) m->mega_prof = be.zeros({(int64_t)m->mega_grid * 8 * 2}, Dtype::U32);
+    // on by default where the shape allows it (bf16, small batch); cg_llama_set_persistent turns it off
+    m->mega_possible = coop != 0 && comm == nullptr && m->dt == Dtype::BF16;
+    m->mega_enabled = m->mega_possible;
+    // CATGRAD_B200_PERSIST_PROF: per-CTA cycle counters of the persistent kernel, printed by cg_llama_free
+    if (std::getenv("CATGRAD_B200_PERSIST_PROF")) m->mega_prof = be.zeros({(int64_t)m->mega_grid * cgk::PK_PROF_SLOTS * 2}, Dtype::U32);
   }
   *out = m.release();
   CG_API_END(ctx)
@@ -993,15 +991,16 @@ void cg_llama_free(cg_llama* m) {
     m->be->guard();
     cudaStreamSynchronize(m->be->stream());
     if (m->mega_prof.defined()) {
-      std::vector<unsigned long long> h((size_t)m->mega_grid * 8);
+      const int NS = cgk::PK_PROF_SLOTS;
+      std::vector<unsigned long long> h((size_t)m->mega_grid * NS);
       if (cudaMemcpy(h.data(), m->mega_prof.raw(), h.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
-        static const char* names[] = {"barrier", "prologue", "wait_data", "multiply", "epilogue", "attention", "total"};
+        static const char* names[] = {"barrier", "input", "wait_chunk", "products", "epilogue", "attention", "total"};
         for (int c : {0, 1, 31, 32, 100, m->mega_grid - 1}) {
-          if (c < 0 || c >= m->mega_grid || h[(size_t)c * 8 + 7] == 0) continue;
-          double steps = (double)h[(size_t)c * 8 + 7];
-          std::fprintf(stderr, "[mega prof] cta %3d steps %.0f cycles/step:", c, steps);
-          for (int i = 0; i < 7; ++i) std::fprintf(stderr, " %s=%.0f", names[i], (double)h[(size_t)c * 8 + i] / steps);
-          std::fprintf(stderr, "\n");
+          if (c < 0 || c >= m->mega_grid || h[(size_t)c * NS + 7] == 0) continue;
+          double steps = (double)h[(size_t)c * NS + 7];
+          std::fprintf(stderr, "[persist prof] cta %3d steps %.0f cycles/step:", c, steps);
+          for (int i = 0; i < 7; ++i) std::fprintf(stderr, " %s=%.0f", names[i], (double)h[(size_t)c * NS + i] / steps);
+          std::fprintf(stderr, " copy_warp_waits_for_slot=%.0f\n", (double)h[(size_t)c * NS + 8] / steps);
         }
       }
     }
@@ -1139,6 +1138,15 @@ int cg_llama_last_logits(cg_llama* mm, float* dst, uint64_t cap_elems) {
   m.be->to_vec(f, dst, (size_t)n * 4);
   CG_API_END(ctx)
 }
+
+int cg_llama_set_persistent(cg_llama* mm, int on) {
+  cg_ctx* ctx = mm ? mm->ctx : nullptr;
+  CG_API_BEGIN
+  cg_llama& m = *L(mm);
+  m.mega_enabled = on != 0 && m.mega_possible;
+  CG_API_END(ctx)
+}
+int cg_llama_persistent_active(const cg_llama* m) { return m && m->mega_last_step ? 1 : 0; }
 
 uint64_t cg_llama_context_len(const cg_llama* m) { return m ? (uint64_t)m->host_ctx_len : 0; }
 uint64_t cg_llama_launch_count(const cg_llama* m) { return m ? m->launches : 0; }

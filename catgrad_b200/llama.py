@@ -191,6 +191,14 @@ class LlamaRunner:
         self._be._check(self._be._ns.llama_last_logits(self._h, out.ctypes.data_as(C.c_void_p), out.size))
         return out
 
+    def set_persistent(self, on):
+        """Allow (or forbid) the one-kernel persistent decode step for small batches (`cg_llama_set_persistent`)."""
+        self._be._check(self._be._ns.llama_set_persistent(self._h, int(bool(on))))
+
+    @property
+    def persistent_active(self):
+        return bool(self._be._ns.llama_persistent_active(self._h))
+
     @property
     def context_len(self):
         return int(self._be._ns.llama_context_len(self._h))

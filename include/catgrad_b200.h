@@ -228,6 +228,13 @@ cg_status cg_llama_forward(cg_llama* m, const uint32_t* ids, uint64_t batch, uin
 cg_status cg_llama_decode(cg_llama* m, uint64_t steps, uint32_t* out_ids);
 /* Copies the logits of the last forward/decode step ([batch, vocab], last position only) to host as f32. */
 cg_status cg_llama_last_logits(cg_llama* m, float* dst, uint64_t cap_elems);
+/* Decode steps of small batches can run as ONE persistent kernel (weights streamed through shared memory by an
+ * asynchronous-copy warp, grid barriers between the sub-graphs) instead of a captured graph of one kernel per
+ * sub-graph.  on != 0 allows it where the shape permits (bf16, no tensor parallelism); on == 0 forces the
+ * kernel-per-sub-graph plan.  Both keep the term's results within the bf16 tolerance of each other. */
+cg_status cg_llama_set_persistent(cg_llama* m, int on);
+/* 1 if the most recent decode step ran as the persistent kernel. */
+int cg_llama_persistent_active(const cg_llama* m);
 /* Current context length T. */
 uint64_t cg_llama_context_len(const cg_llama* m);
 /* Number of kernel launches issued by this runner since creation (graph replays count their nodes). */

@@ -1,0 +1,73 @@
+"""Writes tests/golden/llama1b_bf16_semantics.json: how far the reference's own bf16 semantics (every op output
+rounded to bf16, candle.rs:1165-1192, as restated by the CPU oracle in bf16 mode) lands from the f32 evaluation of
+the same Llama-3.2-1B-shaped model (weights rounded to bf16 first), on the inputs tests/test_gpu_full_dims.py uses:
+seed-0 weights, a 16-token prompt from seed 1, two decode steps fed with the f32 run's ids.
+
+The bf16 kernels are held to the f32 oracle with a bar derived from these figures, because at this size the 2e-2
+max-abs bar that holds for small models is out of reach for the reference semantics themselves.
+
+Run from the repository root (about 10 minutes of CPU, ~12 GB of RAM):  python tests/golden/make_llama1b_bf16_semantics.py
+"""
+import ctypes
+import gc
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+import catgrad_b200 as cb  # noqa: E402
+from catgrad_b200 import Dtype  # noqa: E402
+
+PROMPT, DECODE = 16, 2
+
+
+def run(oracle, cfg, wb, dtype, ids, forced):
+    """Last-position logits of the prefill call and of DECODE single-token calls; `forced` = ids to feed (or None:
+    feed the run's own greedy ids and return them)."""
+    term = cb.llama_term(oracle, cfg, tap_logits=True)
+    params = cb.upload_weights(oracle, wb, dtype)
+    interp = cb.Interpreter(oracle, params)
+    in_k, in_v = cb.empty_state_cache(oracle, cfg, 1, dtype)
+    x, out, logits = ids, [], []
+    for i in range(1 + DECODE):
+        res = interp.run(term, [oracle.ndarray_from_vec_u32(x, x.shape), in_k, in_v, PROMPT + DECODE + 1])
+        in_k, in_v = res[1], res[2]
+        logits.append(oracle.to_f32(res[3])[0, -1].astype(np.float32))
+        tok = int(oracle.to_numpy(res[0])[0, -1, 0])
+        out.append(tok)
+        nxt = tok if forced is None else forced[i]
+        x = np.array([[nxt]], dtype=np.uint32)
+    del params, interp, term
+    gc.collect()
+    return out, np.stack(logits)
+
+
+def main():
+    so = os.path.join(ROOT, "oracle", "_build", "libndarray_ref.so")
+    oracle = cb.Backend(_cdll=ctypes.CDLL(so), _prefix="ref_")
+    cfg = cb.LLAMA_1B
+    w = cb.random_weights(cfg, seed=0)
+    wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+    del w
+    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(1, PROMPT), dtype=np.uint32)
+    ids32, l32 = run(oracle, cfg, wb, Dtype.F32, ids, None)
+    ids16, l16 = run(oracle, cfg, wb, Dtype.BF16, ids, ids32)
+    d = np.abs(l16 - l32)
+    out = {
+        "model": "Llama-3.2-1B shape, seed-0 N(0, 0.02) weights rounded to bf16, norm gains 1",
+        "prompt_seed": 1, "prompt_len": PROMPT, "decode_steps": DECODE,
+        "f32_ids": ids32, "bf16_ids": ids16,
+        "logit_absmax": [float(np.abs(r).max()) for r in l32], "logit_std": [float(r.std()) for r in l32],
+        "bf16_vs_f32_max_abs": [float(r.max()) for r in d], "bf16_vs_f32_mean_abs": [float(r.mean()) for r in d],
+        "top2_gap_f32": [float(np.sort(r)[-1] - np.sort(r)[-2]) for r in l32],
+    }
+    with open(os.path.join(ROOT, "tests", "golden", "llama1b_bf16_semantics.json"), "w") as f:
+        json.dump(out, f, indent=1)
+    print(json.dumps(out, indent=1))
+
+
+if __name__ == "__main__":
+    main()

@@ -272,19 +272,15 @@ def test_runner_refuses_bad_use(gpu):
 
 
 def test_persistent_decode_kernel_matches_the_multi_kernel_plan(gpu):
-    """With CATGRAD_B200_MEGA set at creation, batch <= 4 decode steps run as one persistent kernel instead of the
-    graph of per-sub-graph kernels.  Same rounding points, different summation order: logits agree to
-    bf16 resolution (teacher-forced so that one flipped argmax cannot compound), and the KV caches they build are
-    interchangeable."""
-    import os
+    """Decode steps of a few bf16 sequences run as one persistent kernel unless cg_llama_set_persistent(0) asks for
+    the graph of per-sub-graph kernels.  Same rounding points except inside attention (chunked softmax, see
+    llama_persist.cuh), different summation order: logits agree to bf16 resolution (teacher-forced so that one
+    flipped argmax cannot compound), and the KV caches they build are interchangeable."""
     cfg, wb, ids = small_bf16_model()
     pg = cb.upload_weights(gpu, wb, Dtype.BF16)
-    os.environ["CATGRAD_B200_MEGA"] = "1"
-    try:
-        mega = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=2, max_positions=64)
-    finally:
-        del os.environ["CATGRAD_B200_MEGA"]
+    mega = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=2, max_positions=64)
     plain = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=2, max_positions=64)
+    plain.set_persistent(False)
     mega.reset(2)
     plain.reset(2)
     ta = mega.forward(ids)
@@ -294,6 +290,7 @@ def test_persistent_decode_kernel_matches_the_multi_kernel_plan(gpu):
     for _ in range(8):
         ta = mega.forward(tok.reshape(2, 1))
         tb = plain.forward(tok.reshape(2, 1))
+        assert mega.persistent_active and not plain.persistent_active
         la, lb = mega.last_logits(), plain.last_logits()
         assert np.abs(la - lb).max() <= ABS_BF16
         tok = tb
@@ -309,3 +306,48 @@ def test_persistent_decode_kernel_matches_the_multi_kernel_plan(gpu):
         cols.append(t)
     np.testing.assert_array_equal(out, np.stack(cols, 1))
     assert mega.launch_count < plain.launch_count   # one launch per decode step
+    # a cache built by one plan serves the other: switch plans in the middle of a sequence
+    mega.set_persistent(False)
+    plain.set_persistent(True)
+    ta = mega.forward(t.reshape(2, 1))
+    plain.reset(2)
+    plain.forward(ids)
+    for c in [first] + cols:                       # the same history: prompt, its greedy token, the six decoded ones
+        plain.forward(c.reshape(2, 1))
+    assert np.abs(mega.last_logits() - plain.last_logits()).max() <= ABS_BF16
+
+
+@pytest.mark.parametrize("heads,kv_heads,batch,ctx", [(8, 2, 1, 300), (4, 2, 3, 140), (8, 8, 4, 20)])
+def test_persistent_decode_kernel_long_contexts_and_head_shapes(gpu, heads, kv_heads, batch, ctx):
+    """The persistent kernel's attention splits the keys into 128-key chunks over the CTAs and combines the chunk
+    partials when it loads the o_proj input: contexts spanning several chunks, head_dim 64 and 128, GQA groups of
+    4, 2 and 1, against the f32 runner on the same weights (same history on both sides)."""
+    cfg = cb.LlamaConfig(512, 1536, 2, heads, kv_heads, 4096, rope_theta=500000.0, rms_norm_eps=1e-5,
+                         tie_word_embeddings=True)
+    w = cb.random_weights(cfg, seed=0)
+    wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+    ids = np.random.default_rng(12).integers(0, cfg.vocab_size, size=(batch, ctx), dtype=np.uint32)
+    r16 = cb.LlamaRunner(gpu, cfg, cb.upload_weights(gpu, wb, Dtype.BF16), Dtype.BF16, max_batch=batch, max_positions=ctx + 140)
+    r32 = cb.LlamaRunner(gpu, cfg, cb.upload_weights(gpu, wb, Dtype.F32), Dtype.F32, max_batch=batch, max_positions=ctx + 140)
+    r16.reset(batch)
+    r32.reset(batch)
+    tok = r16.forward(ids)
+    r32.forward(ids)
+    for _ in range(4):
+        nxt = r16.forward(tok.reshape(batch, 1))
+        assert r16.persistent_active
+        r32.forward(tok.reshape(batch, 1))
+        assert np.abs(r16.last_logits() - r32.last_logits()).max() <= ABS_BF16
+        tok = nxt
+    # the on-device loop crosses a chunk boundary (a multiple of 128) and must equal stepping from the host
+    more = r16.decode(130)
+    again = cb.LlamaRunner(gpu, cfg, r16._params, Dtype.BF16, max_batch=batch, max_positions=ctx + 140)
+    again.reset(batch)
+    t2 = again.forward(ids)
+    for _ in range(4):
+        t2 = again.forward(t2.reshape(batch, 1))
+    cols = []
+    for _ in range(130):
+        t2 = again.forward(t2.reshape(batch, 1))
+        cols.append(t2)
+    np.testing.assert_array_equal(more, np.stack(cols, 1))

@@ -30,6 +30,7 @@ def test_single_rank_communicator_reproduces_the_plain_runner(gpu, dtype, batch)
     params = cb.upload_weights(gpu, w, dtype)
     ids = np.random.default_rng(2).integers(0, cfg.vocab_size, size=(batch, 17), dtype=np.uint32)
     plain = cb.LlamaRunner(gpu, cfg, params, dtype, max_batch=batch, max_positions=32)
+    plain.set_persistent(False)          # the tensor-parallel runner always takes the kernel-per-sub-graph plan
     want = plain.generate(ids, 8)
     want_logits = plain.last_logits()
     es = 4 if dtype == Dtype.F32 else 2
