@@ -345,7 +345,7 @@ struct Plan {
                   NKV = c.num_key_value_heads * hd, V = c.vocab_size, rep = c.num_attention_heads / c.num_key_value_heads;
     if (!(rep == 1 || rep == 2 || rep == 4)) return g;
     // whole 16-row tiles (8 + 8 for gate/up), whole 16-column K-steps, the norm loader holds 4 x 256 16-byte groups
-    if (NQ % 16 || NKV % 16 || H % 16 || V % 16 || F % 16 || H / 8 > 4 * cgk::PK_COMPUTE_THREADS) return g;
+    if (NQ % 16 || NKV % 16 || H % 16 || V % 16 || F % 16 || H / 4 > 8 * cgk::PK_COMPUTE_THREADS) return g;
     if (m.P > 16384) return g;   // attention chunk partials are combined by every CTA: keep that list short
     const int64_t kmax = std::max<int64_t>(std::max<int64_t>(H, F), NQ);
     const int64_t pitch = kmax * 2 + cgk::PK_XS_PAD;
@@ -354,7 +354,8 @@ struct Plan {
     const int64_t budget = 227 * 1024;
     int64_t nslots = (budget - xs - cgk::pk_tail_bytes()) / cgk::PK_SLOT_BYTES;
     if (nslots > cgk::PK_MAX_SLOTS) nslots = cgk::PK_MAX_SLOTS;
-    if (nslots < 3) return g;
+    if (const char* e = std::getenv("CATGRAD_B200_PERSIST_SLOTS")) nslots = std::min<int64_t>(nslots, std::atoi(e));   // tuning aid
+    if (nslots < 2) return g;
     g.ok = true;
     g.nslots = (int)nslots;
     g.xs_bytes = (int)xs;
@@ -387,22 +388,25 @@ struct Plan {
     if (e != cudaSuccess) throw Error(ERR_CUDA, std::string("cooperative launch of the decode kernel: ") + cudaGetErrorString(e));
     return true;
   }
-  // Runs one decode step (S = 1) as one persistent kernel.  Returns false if this shape cannot use it.
-  bool mega_step(int64_t B) {
+  // Runs `nsteps` (<= PK_MAX_STEPS) decode steps as one launch of the persistent kernel, starting from the ids in
+  // ids_cur.  Returns false if this shape cannot use it.
+  bool mega_steps(int64_t B, int nsteps) {
     MegaGeom g = mega_geom(B);
     if (!g.ok) return false;
     const LlamaConfig& c = m.cfg;
     const int64_t rep = c.num_attention_heads / c.num_key_value_heads;
+    const int64_t NQ = c.num_attention_heads * m.hd, NKV = c.num_key_value_heads * m.hd;
     const int att_chunks = (int)((m.P + cgk::PK_ATT_CHUNK - 1) / cgk::PK_ATT_CHUNK);
     if (!m.mega_att.defined())
-      m.mega_att = m.be->empty({(int64_t)std::min<int64_t>(m.max_batch, cgk::PK_MAX_B) * c.num_key_value_heads * att_chunks *
+      m.mega_att = m.be->empty({std::min<int64_t>(m.max_batch, cgk::PK_MAX_B) * c.num_key_value_heads * att_chunks *
                                 cgk::pk_att_item_floats((int)m.hd, (int)rep)},
                                Dtype::F32);
     cgk::PkArgs a{};
     a.L = (int)c.num_hidden_layers; a.H = (int)c.hidden_size; a.F = (int)c.intermediate_size;
-    a.NQ = (int)(c.num_attention_heads * m.hd); a.NKV = (int)(c.num_key_value_heads * m.hd);
+    a.NQ = (int)NQ; a.NKV = (int)NKV;
     a.V = (int)c.vocab_size; a.nh = (int)c.num_attention_heads; a.nkv = (int)c.num_key_value_heads;
     a.P = (int)m.P; a.B = (int)B; a.G = m.mega_grid; a.nslots = g.nslots; a.xs_pitch = g.xs_pitch;
+    a.nsteps = nsteps;
     a.eps = c.rms_norm_eps; a.scale = cgk_host_round((float)std::sqrt((float)m.hd));
     a.embed = m.embed; a.final_norm = m.final_norm; a.head = m.head;
     a.layers = (const cgk::PkLayer*)m.mega_layers.raw();
@@ -423,7 +427,7 @@ struct Plan {
     if (m.hd == 64) ok = rep == 1 ? mega_launch_t<64, 1>(a, g) : rep == 2 ? mega_launch_t<64, 2>(a, g) : mega_launch_t<64, 4>(a, g);
     else ok = rep == 1 ? mega_launch_t<128, 1>(a, g) : rep == 2 ? mega_launch_t<128, 2>(a, g) : mega_launch_t<128, 4>(a, g);
     if (!ok) return false;
-    m.bar_base += (unsigned long long)cgk::pk_barriers_per_step((int)c.num_hidden_layers) * (unsigned long long)a.G;
+    m.bar_base += (unsigned long long)nsteps * (unsigned long long)cgk::pk_barriers_per_step((int)c.num_hidden_layers) * (unsigned long long)a.G;
     ++m.launches;
     return true;
   }
@@ -810,15 +814,13 @@ void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
   }
 }
 
-bool mega_available(cg_llama& m, int64_t B) {
-  return m.dt == Dtype::BF16 ? Plan<__nv_bfloat16>(m).mega_geom(B).ok : Plan<float>(m).mega_geom(B).ok;
-}
+bool mega_available(cg_llama& m, int64_t B) { return m.dt == Dtype::BF16 && Plan<__nv_bfloat16>(m).mega_geom(B).ok; }
 
 // allow_mega: decode steps that take their ids from the device id buffer may run as the single persistent
 // kernel; a step being captured into a CUDA graph may not (cooperative launch, per-launch barrier base).
 void run_step(cg_llama& m, const unsigned* ids, int64_t B, int64_t S, bool allow_mega = false) {
   if (allow_mega && S == 1 && ids == (const unsigned*)m.ids_cur.raw()) {
-    bool done = m.dt == Dtype::BF16 ? Plan<__nv_bfloat16>(m).mega_step(B) : Plan<float>(m).mega_step(B);
+    bool done = m.dt == Dtype::BF16 && Plan<__nv_bfloat16>(m).mega_steps(B, 1);
     if (done) {
       m.host_ctx_len += 1;
       m.mega_last_step = true;
@@ -1104,13 +1106,23 @@ int cg_llama_decode(cg_llama* mm, uint64_t steps, uint32_t* out_ids) {
     if (e != cudaSuccess) throw Error(ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
     m.graph_batch = B;
   }
-  for (uint64_t i = first; i < steps; ++i) {
+  for (uint64_t i = first; i < steps;) {
     if (use_graph) {
       CG_CUDA(cudaGraphLaunch(m.graph, st));
       m.launches += m.graph_nodes;
       m.host_ctx_len += 1;
+      ++i;
+    } else if (mega && m.mega_enabled) {
+      // the persistent kernel runs up to PK_MAX_STEPS steps per launch (ids fed back inside the kernel)
+      const int n = (int)std::min<uint64_t>(steps - i, cgk::PK_MAX_STEPS);
+      if (Plan<__nv_bfloat16>(m).mega_steps(B, n)) {
+        m.host_ctx_len += n;
+        m.mega_last_step = true;
+        i += (uint64_t)n;
+      }   // else: mega_enabled was switched off, the next turn takes the plain step
     } else {
-      run_step(m, (const unsigned*)m.ids_cur.raw(), B, 1, /*allow_mega=*/true);
+      run_step(m, (const unsigned*)m.ids_cur.raw(), B, 1, /*allow_mega=*/false);
+      ++i;
     }
   }
   if (out_ids) {

@@ -16,8 +16,11 @@
 //    different threads) race on it.  Serialise them.
 //  * the array keeps whatever the last call left.  Nothing has to start at zero here: stage 1 writes every
 //    entry [0, rows * chunks) that stage 2 of the same call reads.
-//  * the first call on each device looks the array's device address up (cudaGetSymbolAddress).  Make that first
-//    call outside any stream capture.
+//  * the first call on each device looks the array's device address up (cudaGetSymbolAddress).
+//  * every call waits for its kernels (it synchronises `stream`), so no call may be made while `stream` is being
+//    captured: such a call is refused with CG_ERR_INVALID_ARG and the capture is left intact.
+//  * x and out must be device memory of the CURRENT device (checked with cudaPointerGetAttributes, which allocates
+//    nothing): the kernels and the scratch follow the current device, and a foreign pointer would fault there.
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -120,8 +123,35 @@ extern "C" int cg_argmax_rows_noalloc(const void* x, int dtype, uint64_t rows, u
            "cg_argmax_rows_noalloc: rows * ceil(n / 4096) = " + std::to_string(rows * chunks) +
                " exceeds the fixed scratch of " + std::to_string(CG_NOALLOC_MAX_PARTIALS) +
                " entries; use cg_argmax or split the rows");
-  unsigned long long* scratch = scratch_for_current_device();
   cudaStream_t st = (cudaStream_t)stream;
+  {
+    // refuse inside a stream capture: the synchronisation below would invalidate the caller's capture
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaError_t ce = cudaStreamIsCapturing(st, &cap);
+    if (ce != cudaSuccess) {
+      cudaGetLastError();
+      throw cg::Error(cg::ERR_INVALID_ARG, std::string("cg_argmax_rows_noalloc: bad stream: ") + cudaGetErrorString(ce));
+    }
+    CG_CHECK(cap == cudaStreamCaptureStatusNone, cg::ERR_INVALID_ARG,
+             "cg_argmax_rows_noalloc: the stream is being captured; this call synchronises and cannot be captured");
+    // both buffers must be device memory of the current device
+    int dev = -1;
+    ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) throw cg::Error(cg::ERR_CUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(ce));
+    const void* ptrs[2] = {x, (const void*)out};
+    const char* names[2] = {"x", "out"};
+    for (int i = 0; i < 2; ++i) {
+      cudaPointerAttributes pa;
+      ce = cudaPointerGetAttributes(&pa, ptrs[i]);
+      if (ce != cudaSuccess) {
+        cudaGetLastError();
+        throw cg::Error(cg::ERR_INVALID_ARG, std::string("cg_argmax_rows_noalloc: ") + names[i] + " is not a CUDA pointer");
+      }
+      CG_CHECK((pa.type == cudaMemoryTypeDevice || pa.type == cudaMemoryTypeManaged) && pa.device == dev, cg::ERR_INVALID_ARG,
+               std::string("cg_argmax_rows_noalloc: ") + names[i] + " must be device memory of the current device");
+    }
+  }
+  unsigned long long* scratch = scratch_for_current_device();
   dim3 grid((unsigned)chunks, (unsigned)rows);
   switch (dtype) {
     case cgk::DT_F32:

@@ -1,8 +1,8 @@
-// One decode step of the Llama term (llama.rs:144-385, S = 1) as ONE persistent kernel, bf16, batch <= 8.
+// Greedy decode steps of the Llama term (llama.rs:144-385, S = 1) as ONE persistent kernel, bf16, batch <= 8.
 //
 // A decode step of a 1B-parameter model reads ~2.5 GB of weights (0.38 ms at HBM speed) through ~85 dependent
 // sub-graphs (per layer: qkv, attention, o_proj, gate/up, down).  As separate launches every sub-graph pays a
-// launch, a cold pipeline and a drain.  Here one CTA per SM stays resident for the whole step and is split in two:
+// launch, a cold pipeline and a drain.  Here one CTA per SM stays resident for a run of steps and is split in two:
 //
 //   * the COPY WARP streams this CTA's share of every weight matrix, in the order the step consumes it, into a ring
 //     of shared-memory slots with 1-D bulk asynchronous copies (one per weight row, completion counted on the slot's
@@ -29,7 +29,12 @@
 // round-off of the attention output and is closer to the f32 evaluation of the term.  Every other rounding point is
 // the graph's (bf16 at each op output the graph types as bf16).
 //
-// Grid barriers (5 per layer) are taken by the compute warps only.  Every wait is bounded: on a timeout the CTA
+// Grid barriers (5 per layer, one more for the greedy pick) are taken by the compute warps only.  A launch runs up to
+// 64 steps: after a step's last barrier every CTA reduces the per-CTA greedy keys itself, so the next step starts
+// without a launch gap and with the weight ring already streaming.  Measured alternatives that were slower on B200
+// and are not kept: handing activations over as words tagged with the producing sub-graph's number and re-read until
+// current (faster on an idle GPU, slower under the weight stream); an extra L2 prefetch cursor ahead of the ring; a
+// polling instead of a blocking copy warp.  Every wait is bounded: on a timeout the CTA
 // records DEV_ERR_WAIT_TIMEOUT and raises a device-wide abort word that all other waits poll; the copy warp then
 // waits (bounded) for its copies in flight before the CTA returns.  Must be launched cooperatively (all CTAs
 // co-resident), 288 threads, one CTA per SM.
@@ -53,13 +58,14 @@ constexpr int PK_ATT_CHUNK = 128;                     // keys per attention work
 constexpr int PK_XS_PAD = 32;                         // bytes added to an input row so that sequences land on distinct banks
 constexpr long long PK_WAIT_CYCLES = 4000000000ll;    // ~2 s
 constexpr int PK_PROF_SLOTS = 16;
+constexpr int PK_MAX_STEPS = 64;                      // decode steps per launch
 
 struct PkLayer {
   const void *in_norm, *q, *k, *v, *o, *post_norm, *gate, *up, *down;
 };
 
 struct PkArgs {
-  int L, H, F, NQ, NKV, V, nh, nkv, P, B, G, nslots, xs_pitch;
+  int L, H, F, NQ, NKV, V, nh, nkv, P, B, G, nslots, xs_pitch, nsteps;
   float eps, scale;
   const void* embed;
   const void* final_norm;
@@ -76,7 +82,7 @@ struct PkArgs {
   long long kv_layer_stride, kv_seq_stride;
   const float* cos_t;
   const float* sin_t;
-  unsigned* ids_cur;            // [B] in: this step's token ids; out: the next ones
+  unsigned* ids_cur;            // [B] in: the first step's token ids; out: the ids after the last step
   unsigned* out_ids;            // [steps, B] record
   int* ctx_len;
   int* step_no;
@@ -92,7 +98,7 @@ struct PkArgs {
 // Floats of one attention chunk partial: rep x HD accumulators, rep maxima, rep sums; padded to 16 bytes.
 __host__ __device__ constexpr int pk_att_item_floats(int HD, int REP) { return (REP * (HD + 2) + 3) & ~3; }
 
-// Number of grid barriers one launch takes (the host advances bar_base by this x G).
+// Number of grid barriers of one step (the host advances bar_base by steps x this x CTAs per launch).
 __host__ __device__ inline int pk_barriers_per_step(int L) { return 5 * L + 1; }
 
 __device__ __forceinline__ uint32_t pk_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -497,7 +503,7 @@ __device__ __forceinline__ void pk_attention_item(const PkArgs& a, int layer, in
 
 // Shared memory: [nslots x slot ring][input rows / attention scratch: xs_bytes][partial sums 2 x 8 x 16 x 8 f32]
 //                [mbarriers: full[6], empty[6]][scratch f32[8]][ok flag][best keys u64[128]]
-__host__ __device__ constexpr int pk_tail_bytes() { return 2 * PK_COMPUTE_WARPS * PK_TILE_ROWS * PK_MAX_B * 4 + 2 * PK_MAX_SLOTS * 8 + 64 + 16 + 128 * 8; }
+__host__ __device__ constexpr int pk_tail_bytes() { return 2 * PK_COMPUTE_WARPS * PK_TILE_ROWS * PK_MAX_B * 4 + 2 * PK_MAX_SLOTS * 8 + 64 + 16 + 128 * 8 + 32; }
 
 template <int HD, int REP, bool PROF>
 __global__ void __launch_bounds__(PK_THREADS, 1) llama_decode_persistent_kernel(PkArgs a, int xs_bytes) {
@@ -511,6 +517,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1) llama_decode_persistent_kernel(
   float* scratch = reinterpret_cast<float*>(empty + PK_MAX_SLOTS);               // [16]
   int* ok_flag = reinterpret_cast<int*>(scratch + 16);
   unsigned long long* best_s = reinterpret_cast<unsigned long long*>(ok_flag + 4);  // [128]
+  unsigned* ids_s = reinterpret_cast<unsigned*>(best_s + 128);                   // [8] token ids of the current step
 
   const int cta = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -526,14 +533,15 @@ __global__ void __launch_bounds__(PK_THREADS, 1) llama_decode_persistent_kernel(
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  if (threadIdx.x < PK_MAX_B) ids_s[threadIdx.x] = threadIdx.x < B ? a.ids_cur[threadIdx.x] : 0u;
   __syncthreads();
 
-  const int pos = *a.ctx_len;  // position of the new token
-  if (pos >= a.P) {            // cache full: every CTA sees the same value and leaves before anything is issued
+  const int pos0 = *a.ctx_len;  // position of the first new token
+  if (pos0 + a.nsteps > a.P) {  // cache would overflow: every CTA sees the same value and leaves before anything is issued
     if (threadIdx.x == 0) {
       if (cta == 0) atomicOr(a.err, DEV_ERR_INDEX_OOB);
-      // keep the barrier counter in step with the host's bookkeeping (it advances by barriers x CTAs per launch)
-      atomicAdd(a.bar_counter, (unsigned long long)pk_barriers_per_step(a.L));
+      // keep the barrier counter in step with the host's bookkeeping (it advances by steps x barriers x CTAs per launch)
+      atomicAdd(a.bar_counter, (unsigned long long)a.nsteps * (unsigned long long)pk_barriers_per_step(a.L));
     }
     return;
   }
@@ -543,6 +551,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1) llama_decode_persistent_kernel(
     long long stall = 0;
     int n = 0;
     bool alive = true;
+    for (int step = 0; step < a.nsteps && alive; ++step)
     for (int l = 0; l <= a.L && alive; ++l) {
       const int n_ph = l < a.L ? 4 : 1;
       for (int pi = 0; pi < n_ph && alive; ++pi) {
@@ -588,22 +597,6 @@ __global__ void __launch_bounds__(PK_THREADS, 1) llama_decode_persistent_kernel(
   // ====================================== the compute warps ========================================
   const long long NQKV = a.NQ + 2 * a.NKV;
   unsigned long long bar_target = a.bar_base;
-  const int nch = pos / PK_ATT_CHUNK + 1;   // attention chunks in use
-
-  // per-sequence embedding rows: the residual stream of layer 0 (helpers/tensors.rs:255-272)
-  PkRows emb;
-  bool bad_id = false;
-#pragma unroll
-  for (int m = 0; m < PK_MAX_B; ++m) {
-    unsigned id = m < B ? a.ids_cur[m] : 0u;
-    if (id >= (unsigned)a.V) {
-      bad_id = true;
-      id = 0;
-    }
-    emb.p[m] = (const T*)a.embed + (long long)id * a.H;
-  }
-  if (bad_id && cta == 0 && threadIdx.x == 0) atomicOr(a.err, DEV_ERR_INDEX_OOB);
-
   // cycle counters of thread 0 (PROF builds): 0 barrier, 1 input, 2 wait for a chunk, 3 products, 4 reduce + epilogue,
   // 5 attention, 6 total, 7 launches; slot 8 is the copy warp's wait for free slots
   long long pc[6] = {0, 0, 0, 0, 0, 0}, pt = 0, pt_start = 0;
@@ -612,7 +605,6 @@ __global__ void __launch_bounds__(PK_THREADS, 1) llama_decode_persistent_kernel(
 
   int n = 0;
   int red_buf = 0;
-  unsigned long long my_best = 0ull;   // greedy pick: thread (row, sequence) keeps the best key of its rows
   bool alive = true;
   const int g = lane >> 2, tq = lane & 3;
   // ldmatrix source of this lane within a slot: rows 0-7 / 8-15 of K-columns 0-7 / 8-15 of a K-step
@@ -620,6 +612,23 @@ __global__ void __launch_bounds__(PK_THREADS, 1) llama_decode_persistent_kernel(
   const uint32_t ring_u32 = pk_smem(ring);
   const uint32_t xfrag_u32 = pk_smem(xs) + (uint32_t)(g * a.xs_pitch + tq * 8);
 
+  for (int step = 0; step < a.nsteps && alive; ++step) {
+  const int pos = pos0 + step;              // position of this step's new token
+  const int nch = pos / PK_ATT_CHUNK + 1;   // attention chunks in use
+  unsigned long long my_best = 0ull;        // greedy pick: thread (row, sequence) keeps the best key of its rows
+  // per-sequence embedding rows: the residual stream of layer 0 (helpers/tensors.rs:255-272)
+  PkRows emb;
+  bool bad_id = false;
+#pragma unroll
+  for (int m = 0; m < PK_MAX_B; ++m) {
+    unsigned id = m < B ? ids_s[m] : 0u;
+    if (id >= (unsigned)a.V) {
+      bad_id = true;
+      id = 0;
+    }
+    emb.p[m] = (const T*)a.embed + (long long)id * a.H;
+  }
+  if (bad_id && cta == 0 && threadIdx.x == 0) atomicOr(a.err, DEV_ERR_INDEX_OOB);
   for (int l = 0; l <= a.L && alive; ++l) {
     const int n_ph = l < a.L ? 4 : 1;
     for (int pi = 0; pi < n_ph && alive; ++pi) {
@@ -758,53 +767,56 @@ __global__ void __launch_bounds__(PK_THREADS, 1) llama_decode_persistent_kernel(
     }
   }
 
-  // ---- greedy pick (llama.rs:225): per-CTA keys, grid barrier, CTA 0 finishes and advances the step ----
-  if (alive) {
-    if (threadIdx.x < PK_TILE_ROWS * PK_MAX_B) best_s[threadIdx.x] = my_best;
-    pk_compute_sync();
-    if (threadIdx.x < B) {
-      unsigned long long b = 0ull;
-      for (int r = 0; r < PK_TILE_ROWS; ++r) {
-        const unsigned long long k = best_s[r * PK_MAX_B + threadIdx.x];
-        b = k > b ? k : b;
-      }
-      a.partials[(long long)cta * PK_MAX_B + threadIdx.x] = b;
+  // ---- greedy pick (llama.rs:225): per-CTA keys, grid barrier, then every CTA reduces the keys to the next ids ----
+  if (!alive) break;
+  if (threadIdx.x < PK_TILE_ROWS * PK_MAX_B) best_s[threadIdx.x] = my_best;
+  pk_compute_sync();
+  if (threadIdx.x < B) {
+    unsigned long long b = 0ull;
+    for (int r = 0; r < PK_TILE_ROWS; ++r) {
+      const unsigned long long k = best_s[r * PK_MAX_B + threadIdx.x];
+      b = k > b ? k : b;
     }
-    alive = pk_grid_barrier(a, bar_target, ok_flag);
+    a.partials[(long long)cta * PK_MAX_B + threadIdx.x] = b;
   }
+  alive = pk_grid_barrier(a, bar_target, ok_flag);
+  if (!alive) break;
+  if (warp < B) {
+    unsigned long long b = 0ull;
+    for (int c = lane; c < a.G; c += 32) {
+      const unsigned long long k = __ldcg(a.partials + (long long)c * PK_MAX_B + warp);
+      b = k > b ? k : b;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, b, o);
+      b = other > b ? other : b;
+    }
+    if (lane == 0) {
+      const unsigned id = (unsigned)(b & 0xffffffffull);
+      ids_s[warp] = id;
+      if (cta == 0) {
+        const int rec = *a.step_no + step;
+        a.ids_cur[warp] = id;
+        if (rec < a.out_cap_steps) a.out_ids[(long long)rec * B + warp] = id;
+      }
+    }
+  }
+  // the partial keys are rewritten only at the end of the next step, many barriers later
+  pk_compute_sync();
+  PK_PROF(0);
+  if (cta == 0 && threadIdx.x == 0 && step + 1 == a.nsteps) {
+    *a.ctx_len = pos + 1;
+    *a.step_no = *a.step_no + a.nsteps;
+  }
+  }   // steps
   if (PROF && a.prof && threadIdx.x == 0) {
-    PK_PROF(0);
     unsigned long long* pr = a.prof + (long long)cta * PK_PROF_SLOTS;
     for (int i = 0; i < 6; ++i) pr[i] += (unsigned long long)pc[i];
     pr[6] += (unsigned long long)(clock64() - pt_start);
-    pr[7] += 1ull;
+    pr[7] += (unsigned long long)a.nsteps;
   }
 #undef PK_PROF
-  if (alive && cta == 0) {
-    const int step = *a.step_no;
-    if (warp < B) {
-      unsigned long long b = 0ull;
-      for (int c = lane; c < a.G; c += 32) {
-        const unsigned long long k = __ldcg(a.partials + (long long)c * PK_MAX_B + warp);
-        b = k > b ? k : b;
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const unsigned long long other = __shfl_xor_sync(0xffffffffu, b, o);
-        b = other > b ? other : b;
-      }
-      if (lane == 0) {
-        const unsigned id = (unsigned)(b & 0xffffffffull);
-        a.ids_cur[warp] = id;
-        if (step < a.out_cap_steps) a.out_ids[(long long)step * B + warp] = id;
-      }
-    }
-    pk_compute_sync();
-    if (threadIdx.x == 0) {
-      *a.ctx_len = pos + 1;
-      *a.step_no = step + 1;
-    }
-  }
   asm volatile("bar.sync 2, %0;" ::"n"(PK_THREADS) : "memory");   // shared memory stays alive until the copy warp is done
 }
 

@@ -268,7 +268,9 @@ cg_status cg_flush_l2(cg_ctx*, uint64_t bytes);
  * array inside the library.  Limits: rows <= 65535 and rows * ceil(n / 4096) <= 16384, otherwise
  * CG_ERR_INVALID_ARG.  The call returns after the kernels have finished (it synchronises `stream`) and calls no
  * cudaMalloc/cudaFree.  All calls on one GPU share the scratch: do not let two of them overlap on the device.
- * The first call on each device looks up the scratch address; make it outside any stream capture. */
+ * The first call on each device looks up the scratch address.  Because every call synchronises `stream`, a call on
+ * a stream that is being captured is refused (CG_ERR_INVALID_ARG, the capture stays valid); so is a buffer that is
+ * not device memory of the current device. */
 cg_status cg_argmax_rows_noalloc(const void* x, cg_dtype dtype, uint64_t rows, uint64_t n, uint64_t row_stride,
                                  uint32_t* out, void* stream);
 
