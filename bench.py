@@ -8,9 +8,15 @@ One "step" is one decode step of the whole batch (one new token per sequence).
            data path; the generated ids are gathered once at the end).  Total work is fixed: strong scaling.
   N = 1  : additionally times baseline config 3 (batch 1, 512-token prompt: the configuration the 70 %-of-roofline
            target is stated on) and reports it under "c3" with its own roofline; `--workload c3` makes it the line.
-`value` is decode tokens/s with everything resident on the device (CUDA-graph replay, ids fed back on the
-device); `e2e` is the same loop driven like the reference's runner, one host round trip per token: the token
+`value` is decode tokens/s with everything resident on the device (CUDA-graph replay, or the persistent decode
+kernel for a few sequences; ids fed back on the device): the median of `--repeats` timed blocks of exactly
+`--steps` steps, each after a fresh prefill and the warm-up steps so that every block sees the same context
+range.  `e2e` is the same loop driven like the reference's runner, one host round trip per token: the token
 ids are copied host->device, the step runs, the new ids are read back (examples/llama/main.rs:1016-1037).
+`ids_match`: the generated ids are checked, not just summed: every timed block must reproduce the first one's ids,
+with more than one rank rank 0 re-runs rank 1's shard and compares it with what rank 1 sent (batch sharding), or all
+ranks must hold the same ids (tensor parallelism); `ids_sha1` hashes each sequence's ids so that runs at different
+N can be compared row by row.
 Weights are synthetic (N(0,0.02), seed 0), prompts are uniform random ids (seed 1); the 2.47 GB of weights read
 per step exceed the 126 MB L2, so no flush is needed between steps.
 
@@ -37,7 +43,8 @@ sys.path.insert(0, ROOT)
 import catgrad_b200 as cb  # noqa: E402
 
 HBM_NOMINAL_GBS = 8000.0
-# (8.44 + 67.18 + 33.62 + 12.66) MB x 16 layers + 525.3 MB lm_head, DRAM bytes measured by ncu per launch
+# DRAM bytes per step from ncu captures (constants, not measured in this run).  Batch 1, kernel-per-sub-graph plan:
+# (8.44 + 67.18 + 33.62 + 12.66) MB x 16 layers + 525.3 MB lm_head, measured per launch.
 TRAFFIC_PER_STEP_B1 = int((8.44e6 + 67.18e6 + 33.62e6 + 12.66e6) * 16 + 525.3e6)
 # batch 256 on one GPU: per layer [q;k;v] 12.73 + o_proj 8.67 + down_proj 34.23 MB (ncu, split-K summary), [gate;up]
 # 67.11 MB and lm_head 525.3 MB (not captured: their weight bytes), attention 70.1 MB (ncu, context ~135)
@@ -122,43 +129,53 @@ def decode_bytes(cfg, batch, ctx_len):
 
 
 def run_decode_workload(be, cfg, params, batch, prompt_len, steps, warmup, dev_index, e2e_steps=None, name="",
-                        comm=None, persistent=True):
-    """Prefill, then W warm-up + K timed decode steps (device-resident), then the same through host round trips."""
-    P = prompt_len + 2 * (warmup + steps) + 16
+                        comm=None, persistent=True, repeats=3, prompts=None):
+    """`repeats` times: prefill, W warm-up steps, K timed decode steps (device-resident); then the same loop through
+    host round trips.  Returns timings and the ids [batch, steps] of the first timed block."""
+    warmup = max(warmup, 3)
+    P = prompt_len + warmup + steps + 2 * (3 + (e2e_steps or steps)) + 16
     runner = cb.LlamaRunner(be, cfg, params, cb.Dtype.BF16, max_batch=batch, max_positions=P, comm=comm,
                             max_tokens=batch * prompt_len)
     if not persistent:
         runner.set_persistent(False)
-    prompts = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(batch, prompt_len), dtype=np.uint32)
+    if prompts is None:
+        prompts = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(batch, prompt_len), dtype=np.uint32)
     res = {}
-    # ---- prefill (reported beside the headline) ----
-    pre_ms = []
-    for i in range(3):
+    sampler = ClockSampler(dev_index)
+    sampler.start()          # nvidia-smi needs ~0.1 s to come up: start it before the first block
+    time.sleep(0.2)
+    pre_ms, dec_ms, ids0, same = [], [], None, True
+    for rep in range(repeats + 1):                      # block 0 is a dry run (kernel loading, graph capture)
         runner.reset(batch)
         be._ns.event_record(be._ctx, 0)
         runner.forward(prompts, read=False)
         be._ns.event_record(be._ctx, 1)
+        runner.decode(warmup)
+        l0 = runner.launch_count
+        ctx0 = runner.context_len
         be.synchronize()
+        be._ns.event_record(be._ctx, 2)
+        ids = runner.decode(steps)
+        be._ns.event_record(be._ctx, 3)
+        be.synchronize()
+        if rep == 0:
+            continue
         pre_ms.append(event_ms(be, 0, 1))
-    res["prefill_ms"] = min(pre_ms[1:])
-    res["prefill_tok_s"] = batch * prompt_len / (res["prefill_ms"] / 1e3)
-    # ---- device-resident decode ----
-    sampler = ClockSampler(dev_index)
-    sampler.start()          # nvidia-smi needs ~0.1 s to come up: start it before the warm-up steps
-    time.sleep(0.2)
-    runner.decode(max(warmup, 3))
-    l0 = runner.launch_count
-    ctx0 = runner.context_len
-    be.synchronize()
-    be._ns.event_record(be._ctx, 2)
-    ids = runner.decode(steps)
-    be._ns.event_record(be._ctx, 3)
-    be.synchronize()
+        dec_ms.append(event_ms(be, 2, 3))
+        res["launches"] = runner.launch_count - l0
+        res["ctx_mid"] = ctx0 + steps / 2
+        if ids0 is None:
+            ids0 = ids
+        else:
+            same = same and bool((ids == ids0).all())
     res["clocks"] = sampler.stop()
-    res["ms"] = event_ms(be, 2, 3)
-    res["launches"] = runner.launch_count - l0
-    res["ctx_mid"] = ctx0 + steps / 2
-    res["ids_checksum"] = int(ids.astype(np.uint64).sum())
+    res["prefill_ms"] = float(np.median(pre_ms))
+    res["prefill_tok_s"] = batch * prompt_len / (res["prefill_ms"] / 1e3)
+    res["ms"] = float(np.median(dec_ms))
+    res["ms_all"] = [round(v, 4) for v in dec_ms]
+    res["ids"] = ids0
+    res["repeat_ids_equal"] = same
+    res["persistent"] = runner.persistent_active
     # ---- end to end: one host round trip per token, like the reference runner ----
     k = e2e_steps or steps
     tok = ids[:, -1].copy().reshape(batch, 1)
@@ -170,9 +187,40 @@ def run_decode_workload(be, cfg, params, batch, prompt_len, steps, warmup, dev_i
     res["e2e_ms"] = (time.perf_counter() - t0) * 1e3
     res["e2e_steps"] = k
     res["batch"] = batch
-    res["persistent"] = runner.persistent_active
     del runner
     return res
+
+
+def ids_digest(ids):
+    """sha1 over each sequence's generated ids (first 12 hex digits), and one over all of them."""
+    import hashlib
+    rows = [hashlib.sha1(np.ascontiguousarray(r, dtype=np.uint32).tobytes()).hexdigest()[:12] for r in ids]
+    return rows, hashlib.sha1("".join(rows).encode()).hexdigest()[:16]
+
+
+def interpreter_path_tok_s(be, cfg, params, prompt_len=64, steps=4):
+    """The same model through the op-by-op interpreter (cg_interp_run on the Llama term, the route catgrad's own
+    `interpreter.run(term)` takes): one kernel per IR edge, the KV cache threaded as a value and re-stacked every
+    step (helpers/cache.rs:13-75).  Returns decode tokens/s and launches per step."""
+    term = cb.llama_term(be, cfg)
+    interp = cb.Interpreter(be, params)
+    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(1, prompt_len), dtype=np.uint32)
+    in_k, in_v = cb.empty_state_cache(be, cfg, 1, cb.Dtype.BF16)
+    x = ids
+    times, launches = [], []
+    for i in range(steps + 2):
+        stats0 = be.stats()[3]
+        t0 = time.perf_counter()
+        r = interp.run(term, [be.ndarray_from_vec_u32(x, x.shape), in_k, in_v, prompt_len + steps + 3])
+        last = be.to_numpy(r[0])[:, -1, 0]
+        times.append(time.perf_counter() - t0)
+        launches.append(be.stats()[3] - stats0)
+        in_k, in_v = r[1], r[2]
+        x = last.reshape(1, 1).astype(np.uint32)
+    dec = times[2:]                                      # skip the prefill call and the first decode call
+    return {"decode_tok_s": len(dec) / sum(dec), "ms_per_step": 1e3 * sum(dec) / len(dec), "launches_per_step": int(launches[-1]),
+            "prompt_len": prompt_len, "steps": steps,
+            "how": "cg_llama_term through cg_interp_run, one kernel per IR edge, KV cache re-stacked per step"}
 
 
 def cpu_baseline_sample(cfg, weights_f32, prompt_len=8, steps=2, batch=1):
@@ -281,6 +329,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--repeats", type=int, default=3, help="timed blocks of --steps steps; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto", choices=["auto", "c3", "c4", "c5", "tiny", "sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -290,8 +339,10 @@ def main():
                     help="small batches: take the graph of per-sub-graph kernels instead of the persistent decode kernel")
     ap.add_argument("--skip-c4", action="store_true", help="with --workload c3: do not time config 4 as well")
     ap.add_argument("--skip-c3", action="store_true", help="N=1 only: do not time config 3 (batch 1) as well")
+    ap.add_argument("--no-interpreter-path", action="store_true", help="N=1 only: skip the op-by-op interpreter timing")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.repeats = max(args.repeats, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -299,7 +350,7 @@ def main():
     model_name = {"tiny": "tiny-llama", "c5": "Llama-3-8B shape"}.get(args.workload, "Llama-3.2-1B shape")
 
     if args.workload == "sweep":
-        # baseline config 2 (op-level sweep); not the headline metric, printed as its own JSON line
+        # the op-level sweep on random tensors; not the headline metric, printed as its own JSON line
         if rank == 0:
             be = cb.Backend(local_rank)
             hbm, tfl, src = measured_peaks()
@@ -310,15 +361,19 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
+        # The reference's tensor ops are single-threaded and its runner is batch 1: the bounded sample is ONE sequence of
+        # the workload (sequences are independent), a short prompt and two decode steps; tokens/s of that sequence.
         w = cb.random_weights(cfg, seed=0)
-        ref_batch = 1   # one of the workload's sequences: the oracle is single-threaded and sequences are independent
-        base = cpu_baseline_sample(cfg, w, prompt_len=8, steps=max(1, min(args.steps, 2)), batch=ref_batch)
+        nsteps = max(1, min(args.steps, 2))
+        base = cpu_baseline_sample(cfg, w, prompt_len=8, steps=nsteps, batch=1)
         line = {"impl": "reference", "metric": "decode tokens/s", "value": base["value"], "unit": "tok/s",
-                "n_gpus": args.gpus, "steps": max(1, min(args.steps, 2)), "warmup": 0,
-                "ms_per_step": 1e3 * ref_batch / base["value"], "higher_is_better": True, "scaling": "strong",
+                "n_gpus": args.gpus, "steps": nsteps, "warmup": 0,
+                "ms_per_step": 1e3 / base["value"], "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": f"{model_name}, {ref_batch} sequence(s) of the workload, greedy decode on the host CPU "
-                                       "(ndarray-path restatement)"},
+                "config": {"workload": f"{model_name}: ONE sequence of the workload (the reference runner is batch 1 and single-threaded), "
+                                       f"8-token prompt then {nsteps} greedy decode steps on the host CPU, f32 (ndarray-path restatement)",
+                           "like_for_like_with": "the `c3` block of the GPU arm's line (one sequence); the GPU arm's headline runs 256 "
+                                                 "sequences at once, so a ratio against it compares 256 sequences with one"},
                 "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
@@ -326,7 +381,6 @@ def main():
 
     dist = None
     if world > 1:
-        os.environ["NCCL_DEBUG"] = os.environ.get("NCCL_DEBUG_FOR_BENCH", "WARN")   # keep stdout to the one JSON line
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
@@ -364,18 +418,44 @@ def main():
         assert batch_total % world == 0
         batch = batch_total // world
 
+    # every rank draws the whole batch of prompts and takes its contiguous share (catgrad_b200.runner.shard_range)
+    from catgrad_b200 import runner as sharding
+    all_prompts = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(batch_total, prompt_len), dtype=np.uint32)
+    lo, hi = (0, batch_total) if tensor_parallel else sharding.shard_range(batch_total, world, rank)
     if dist is not None:
         dist.barrier()
     r = run_decode_workload(be, cfg, params, batch, prompt_len, args.steps, args.warmup, local_rank, comm=comm,
-                            persistent=not args.no_persistent)
+                            persistent=not args.no_persistent, repeats=args.repeats, prompts=all_prompts[lo:hi])
     ms, e2e_ms, pre_ms = r["ms"], r["e2e_ms"], r["prefill_ms"]
+    ids_match = r["repeat_ids_equal"]
+    all_ids = r["ids"]
     if dist is not None:
         import torch
         t = torch.tensor([ms, e2e_ms, pre_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)      # max over ranks
         ms, e2e_ms, pre_ms = [float(v) for v in t.tolist()]
-        gathered = [torch.zeros(1, dtype=torch.int64, device="cuda") for _ in range(world)]
-        dist.all_gather(gathered, torch.tensor([r["ids_checksum"] % (1 << 62)], device="cuda"))  # the final gather
+        if tensor_parallel:
+            # every rank ran the whole batch: all must hold the same ids
+            pieces = [None] * world
+            dist.all_gather_object(pieces, r["ids"].tobytes())
+            ids_match = ids_match and all(p == pieces[0] for p in pieces)
+        else:
+            # the one collective of this workload: the final gather of the generated ids [256, steps]
+            all_ids = sharding.gather_rows(r["ids"], batch_total, dist, device="cuda")
+            flags = [None] * world
+            dist.all_gather_object(flags, bool(r["repeat_ids_equal"]))
+            ids_match = all(flags)
+            if rank == 0:
+                # rank 0 re-runs rank 1's shard (same batch size, hence the same kernels) and compares with what rank 1 sent
+                lo1, hi1 = sharding.shard_range(batch_total, world, 1)
+                chk = cb.LlamaRunner(be, cfg, params, cb.Dtype.BF16, max_batch=hi1 - lo1, max_positions=prompt_len + args.warmup + args.steps + 8)
+                if args.no_persistent:
+                    chk.set_persistent(False)
+                chk.reset(hi1 - lo1)
+                chk.forward(all_prompts[lo1:hi1], read=False)
+                chk.decode(args.warmup)
+                ids_match = ids_match and bool((chk.decode(args.steps) == all_ids[lo1:hi1]).all())
+                del chk
         dist.barrier()
 
     if rank != 0:
@@ -395,6 +475,17 @@ def main():
     else:
         bytes_step = decode_bytes(cfg, batch, r["ctx_mid"])
     achieved = bytes_step / (ms / args.steps / 1e3) / 1e9
+    rows_sha, all_sha = ids_digest(all_ids)
+    if tensor_parallel:
+        kernel = "one decode step of one rank: tcgen05 GEMMs over its weight shard, attention, 64 all-reduces"
+    elif r["persistent"]:
+        kernel = "llama_decode_persistent_kernel: one launch runs up to 64 decode steps (weights streamed through shared memory)"
+    elif batch <= 16:
+        kernel = "one decode step = 65 gemv_fused_kernel launches (79 % of the device time) + attention + greedy pick"
+    else:
+        kernel = "one decode step = 64 gemm_tcgen05 launches (62 % of the device time) + attention + norms + greedy pick"
+    traffic = (TRAFFIC_PER_STEP_B1 if (batch_total == 1 and workload == "c3" and not r["persistent"]) else
+               TRAFFIC_PER_STEP_C4 if (workload == "c4" and batch == 256 and not args.prompt) else None)
     line = {
         "metric": "decode tokens/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -404,6 +495,11 @@ def main():
                    "global_batch": batch_total, "prompt_len": prompt_len,
                    "parallelism": f"tensor-parallel x{world}" if tensor_parallel else f"batch-sharded x{world}",
                    "l2": "inputs larger than L2 (weights read per step exceed 126 MB many times over)"},
+        "timing": {"blocks": args.repeats, "ms_per_step_each_block_rank0": [v / args.steps for v in r["ms_all"]],
+                   "how": "median over the blocks, each exactly `steps` steps after a fresh prefill and the warm-up steps; CUDA events "
+                          "on the launching stream, max over ranks"},
+        "per_sequence_tok_s": value / batch_total,
+        "ids_match": bool(ids_match), "ids_sha1": all_sha, "ids_sha1_per_sequence": rows_sha,
         "prefill": {"tok_s": batch_total * prompt_len / (pre_ms / 1e3), "ms": pre_ms,
                     "note": "lm_head on the last position of each sequence only"},
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4 * batch * (world if tensor_parallel else 1),
@@ -411,48 +507,49 @@ def main():
                 "steps": r["e2e_steps"], "how": "cg_llama_forward per token with host id buffers (copy in, step, copy out)"},
         "gpu_launches": r["launches"],
         "clocks": r["clocks"],
-        "roofline": {"bound": "hbm",
-                     "kernel": ("one decode step of one rank: tcgen05 GEMMs over its weight shard, attention, 64 all-reduces"
-                                if tensor_parallel else
-                                "one decode step = its 65 gemv_fused_kernel launches (79 % of the device time, "
-                                "profiles/decode_step_llama1b_bf16_launch_list.md) + attention + greedy pick"),
+        "roofline": {"bound": "hbm", "kernel": kernel,
                      "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "peak_source": peak_src, "frac_of_8TBs_nominal": achieved / HBM_NOMINAL_GBS,
                      "bytes_per_step": bytes_step,
                      "how": "algorithmic bytes of a step on one GPU (every weight it holds once + KV cache read + new KV "
                             "rows) / CUDA-event time of a step on the launching stream",
-                     # dram__bytes_read.sum + dram__bytes_write.sum of the launches of one step, summed from the ncu
-                     # captures under profiles/ (batch 1: the gemv launches; batch 256 on one GPU: GEMM + attention)
-                     "traffic": (TRAFFIC_PER_STEP_B1 if (batch_total == 1 and workload == "c3") else
-                                 TRAFFIC_PER_STEP_C4 if (workload == "c4" and batch == 256 and not args.prompt) else None)},
+                     "traffic": traffic,
+                     "traffic_how": "constant from ncu captures of the launches of one step (dram__bytes_read.sum + "
+                                    "dram__bytes_write.sum), part of it assumed equal to the weight bytes; not measured in this run"},
         "load_s": load_s,
     }
-    if workload == "c4" and not tensor_parallel:
-        line["roofline"]["kernel"] = ("one decode step = 64 gemm_tcgen05 launches (62 % of the device time, "
-                                      "profiles/decode_step_llama1b_bf16_batch256_launch_list.md) + attention + norms + greedy pick")
     if single and workload == "c4" and args.workload == "auto" and not args.skip_c3:
-        # config 3: batch 1, 512-token prompt: the configuration the 70 %-of-HBM-roofline target is stated on
+        # one sequence, 512-token prompt: the configuration the 70 %-of-HBM-roofline target is stated on
         c3_steps = min(max(args.steps, 32), 128)
-        r3 = run_decode_workload(be, cfg, params, 1, 512, c3_steps, args.warmup, local_rank, persistent=not args.no_persistent)
+        r3 = run_decode_workload(be, cfg, params, 1, 512, c3_steps, args.warmup, local_rank, persistent=not args.no_persistent,
+                                 repeats=args.repeats)
         b3 = decode_bytes(cfg, 1, r3["ctx_mid"])
         a3 = b3 / (r3["ms"] / c3_steps / 1e3) / 1e9
         line["c3"] = {"workload": "1 sequence x 512-token prompt on one GPU", "decode_tok_s": c3_steps / (r3["ms"] / 1e3),
-                      "ms_per_step": r3["ms"] / c3_steps, "prefill_tok_s": r3["prefill_tok_s"], "prefill_ms": r3["prefill_ms"],
+                      "ms_per_step": r3["ms"] / c3_steps, "ms_per_step_each_block": [v / c3_steps for v in r3["ms_all"]],
+                      "prefill_tok_s": r3["prefill_tok_s"], "prefill_ms": r3["prefill_ms"],
                       "e2e_tok_s": r3["e2e_steps"] / (r3["e2e_ms"] / 1e3), "gpu_launches": r3["launches"],
-                      "roofline": {"bound": "hbm", "kernel": "65 gemv_fused_kernel launches per step (79 % of the device time, "
-                                   "profiles/decode_step_llama1b_bf16_launch_list.md)", "achieved": a3, "peak": hbm_peak,
+                      "ids_match": bool(r3["repeat_ids_equal"]), "ids_sha1": ids_digest(r3["ids"])[1],
+                      "roofline": {"bound": "hbm",
+                                   "kernel": "llama_decode_persistent_kernel (one launch runs up to 64 steps)" if r3["persistent"]
+                                   else "65 gemv_fused_kernel launches per step (79 % of the device time)",
+                                   "achieved": a3, "peak": hbm_peak,
                                    "unit": "GB/s", "frac": a3 / hbm_peak, "peak_source": peak_src,
                                    "frac_of_8TBs_nominal": a3 / HBM_NOMINAL_GBS, "bytes_per_step": b3,
-                                   "traffic": TRAFFIC_PER_STEP_B1}}
+                                   "traffic": None if r3["persistent"] else TRAFFIC_PER_STEP_B1}}
+        if not args.no_interpreter_path:
+            line["c3"]["interpreter_path"] = interpreter_path_tok_s(be, cfg, params)
     if tensor_parallel:
         del comm
     if single and workload == "c3" and not args.skip_c4:
         # the batch-sharded workload on one GPU: the N=1 point of the scaling runs
         c4_steps = min(args.steps, 64)
-        r4 = run_decode_workload(be, cfg, params, 256, 128, c4_steps, args.warmup, local_rank, e2e_steps=8)
+        r4 = run_decode_workload(be, cfg, params, 256, 128, c4_steps, args.warmup, local_rank, e2e_steps=8, repeats=args.repeats)
         line["c4"] = {"decode_tok_s": 256 * c4_steps / (r4["ms"] / 1e3), "ms_per_step": r4["ms"] / c4_steps,
                       "prefill_tok_s": r4["prefill_tok_s"], "e2e_tok_s": 256 * r4["e2e_steps"] / (r4["e2e_ms"] / 1e3),
                       "workload": "256 sequences x 128-token prompt on one GPU"}
+    if single and workload == "c3" and not args.no_interpreter_path:
+        line["interpreter_path"] = interpreter_path_tok_s(be, cfg, params)
     if single and not args.no_cpu_baseline and not tensor_parallel:
         del params
         wf = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}

@@ -26,6 +26,7 @@ SOURCES = [
     "host/cuda_backend.cu",
     "host/llama_engine.cu",
     "host/tp_comm.cu",
+    "host/device_runner.cu",
     "host/c_api.cc",
     "host/interp.cc",
     "host/llama_term.cc",

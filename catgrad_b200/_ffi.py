@@ -132,6 +132,14 @@ CUDA_ONLY = {
     "llama_persistent_active": (C.c_int, [C.c_void_p]),
     "llama_context_len": (C.c_uint64, [C.c_void_p]),
     "llama_launch_count": (C.c_uint64, [C.c_void_p]),
+    "runner_create": (C.c_int, [C.POINTER(C.c_int), C.c_int, C.POINTER(LlamaConfigStruct), C.c_int, C.c_uint64, C.c_uint64,
+                                c_void_pp]),
+    "runner_size": (C.c_int, [C.c_void_p]),
+    "runner_ctx": (C.c_void_p, [C.c_void_p, C.c_int]),
+    "runner_set_params": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "runner_generate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]),
+    "runner_last_error": (C.c_char_p, [C.c_void_p]),
+    "runner_free": (None, [C.c_void_p]),
     "event_record": (C.c_int, [_CTX, C.c_int]),
     "event_elapsed_ms": (C.c_int, [_CTX, C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "ctx_stats": (C.c_int, [_CTX, u64p]),

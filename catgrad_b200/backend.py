@@ -120,9 +120,14 @@ def _dims(shape):
 class Backend:
     """The B200 backend.  `Backend()` opens CUDA device 0 through the in-tree library."""
 
-    def __init__(self, device=0, *, _cdll=None, _prefix="cg_"):
+    def __init__(self, device=0, *, _cdll=None, _prefix="cg_", _borrowed_ctx=None):
         self._ns = None
         self._ctx = None
+        if _borrowed_ctx is not None:
+            # a view of a context that something else owns (a replica of catgrad_b200.runner.DeviceRunner)
+            self._ns = _ffi.bind(C.CDLL(_ffi.library_path()), _prefix)
+            self._ctx = _borrowed_ctx
+            return
         if _cdll is None:
             path = _ffi.library_path()
             try:
@@ -164,6 +169,12 @@ class Backend:
         out = C.c_void_p()
         self._check(fn(self._ctx, *args, C.byref(out)))
         return Tensor(self, out)
+
+    def stats(self):
+        """(live bytes, cached bytes, cudaMalloc calls, kernel launches) of the context (`cg_ctx_stats`)."""
+        out = (C.c_uint64 * 4)()
+        self._check(self._ns.ctx_stats(self._ctx, out))
+        return tuple(int(v) for v in out)
 
     def synchronize(self):
         self._check(self._ns.synchronize(self._ctx))

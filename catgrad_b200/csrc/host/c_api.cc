@@ -28,31 +28,34 @@ int record_error(cg_ctx* ctx, int status, const std::string& msg) {
 // Default Backend::format_tensor: dtype, shape and the first elements (the reference prints ndarray's
 // Debug form, mod.rs:117-125; the exact text is not part of any contract).
 std::string Backend::format_tensor(const Tensor& x) {
-  std::ostringstream os;
-  os << dtype_name(x.dt) << shape_str(x.shape) << " [";
+  // plain snprintf: iostream number formatting goes through locale facets, which crashed when the process had
+  // loaded another C++ runtime's copy of them first (numpy does)
+  std::string s = std::string(dtype_name(x.dt)) + shape_str(x.shape) + " [";
   int64_t n = x.size();
   std::vector<char> buf((size_t)n * dtype_size(x.dt) + 1);
   to_vec(x, buf.data(), buf.size());
   int64_t shown = n < 16 ? n : 16;
+  char num[64];
   for (int64_t i = 0; i < shown; ++i) {
-    if (i) os << ", ";
+    if (i) s += ", ";
     switch (x.dt) {
-      case Dtype::F32: os << ((float*)buf.data())[i]; break;
-      case Dtype::U32: os << ((uint32_t*)buf.data())[i]; break;
+      case Dtype::F32: std::snprintf(num, sizeof(num), "%g", (double)((float*)buf.data())[i]); break;
+      case Dtype::U32: std::snprintf(num, sizeof(num), "%u", ((uint32_t*)buf.data())[i]); break;
       case Dtype::BF16: {
         uint32_t u = (uint32_t)((uint16_t*)buf.data())[i] << 16;
         float f;
         std::memcpy(&f, &u, 4);
-        os << f;
+        std::snprintf(num, sizeof(num), "%g", (double)f);
         break;
       }
-      case Dtype::F16: os << "0x" << std::hex << ((uint16_t*)buf.data())[i] << std::dec; break;
-      case Dtype::F8: os << "0x" << std::hex << (int)((uint8_t*)buf.data())[i] << std::dec; break;
+      case Dtype::F16: std::snprintf(num, sizeof(num), "0x%04x", (unsigned)((uint16_t*)buf.data())[i]); break;
+      default: std::snprintf(num, sizeof(num), "0x%02x", (unsigned)((uint8_t*)buf.data())[i]); break;
     }
+    s += num;
   }
-  if (shown < n) os << ", ...";
-  os << "]";
-  return os.str();
+  if (shown < n) s += ", ...";
+  s += "]";
+  return s;
 }
 }  // namespace cg
 

@@ -261,6 +261,7 @@ std::vector<Value> Interpreter::apply(const Edge& e, int id, std::vector<Value>&
       if (std::getenv("CATGRAD_PROBE")) {
         arity(a, 1, id);
         std::printf("[probe:%s] %s\n", op.str.c_str(), be_->format_tensor(as_tensor(a[0], id)).c_str());
+        std::fflush(stdout);
       }
       return {};
     }

@@ -235,10 +235,9 @@ struct Plan {
   }
   template <int HD, int REP>
   void group_attention_launch(const cgk::AttnArgs& a, int64_t B, int64_t nkv, unsigned* err) {
-    static const bool one_warp = std::getenv("CATGRAD_B200_ATTN_ONE_WARP") != nullptr;   // A/B aid
     // measured (8 kv heads): two warps per pair +8 % tokens/s at batch 32, -4 % at batch 256, where one warp per
     // pair already fills every SM
-    if (!one_warp && B * nkv <= 8 * (int64_t)sm) {
+    if (B * nkv <= 8 * (int64_t)sm) {
       pair_attention_launch<HD, REP>(a, B, nkv, err);
       return;
     }
@@ -256,12 +255,8 @@ struct Plan {
   }
   bool launch_group_attention(const cgk::AttnArgs& a, int64_t B, int64_t nkv, int64_t rep, int64_t hd, unsigned* err) {
     if (!std::is_same<T, __nv_bfloat16>::value) return false;
-    static const long long min_pairs = [] {
-      const char* e = std::getenv("CATGRAD_B200_GROUP_ATTN_MIN");   // tuning aid: smallest batch x kv heads taken here
-      return e ? std::atoll(e) : -1ll;
-    }();
     // measured at batch 32 and 64 (8 kv heads): 10 % and 21 % more tokens/s than one warp per query head
-    if (B * nkv < (min_pairs >= 0 ? min_pairs : (int64_t)sm) || m.host_ctx_len > 512) return false;
+    if (B * nkv < (int64_t)sm || m.host_ctx_len > 512) return false;
     const size_t per_warp = (size_t)2 * hd * 2 + (size_t)rep * hd * 4 + (size_t)rep * (m.P + 1) * 4 + 16;
     if (4 * per_warp > 200 * 1024) return false;
     if (hd == 64) {
@@ -296,8 +291,6 @@ struct Plan {
     if (!std::is_same<T, __nv_bfloat16>::value) return false;
     // a single sequence is faster through the one-launch kernel (measured: 1.00 vs 1.12 ms per step at batch 1)
     if (m.host_ctx_len <= 512 || B > 65535 || B * nkv < 32) return false;
-    static const bool off = std::getenv("CATGRAD_B200_NO_SPLIT_ATTN") != nullptr;
-    if (off) return false;
     const int64_t nh = nkv * rep;
     const int chunks_max = (int)((m.P + cgk::ATTN_CHUNK - 1) / cgk::ATTN_CHUNK);
     // the scratch is made by ensure_capacity: nothing may allocate here, this runs inside graph captures
@@ -354,8 +347,7 @@ struct Plan {
     const int64_t budget = 227 * 1024;
     int64_t nslots = (budget - xs - cgk::pk_tail_bytes()) / cgk::PK_SLOT_BYTES;
     if (nslots > cgk::PK_MAX_SLOTS) nslots = cgk::PK_MAX_SLOTS;
-    if (const char* e = std::getenv("CATGRAD_B200_PERSIST_SLOTS")) nslots = std::min<int64_t>(nslots, std::atoi(e));   // tuning aid
-    if (nslots < 2) return g;
+    if (nslots < 3) return g;
     g.ok = true;
     g.nslots = (int)nslots;
     g.xs_bytes = (int)xs;
@@ -947,9 +939,10 @@ int create_runner(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const cg_
   m->argmax_chunks = (int)((V + cgk::ARGMAX_CHUNK - 1) / cgk::ARGMAX_CHUNK);
   m->partials = be.zeros({m->max_batch * m->argmax_chunks * 2}, Dtype::U32);
   // programmatic dependent launch: the next kernel starts streaming its first weight rows while this one drains
-  m->use_pdl = std::getenv("CATGRAD_B200_NO_PDL") == nullptr;
-  // measured neutral-to-slower on B200 for this chain (the launches are latency-bound, not HBM-bound): opt-in
-  m->l2_prefetch = std::getenv("CATGRAD_B200_L2_PREFETCH") != nullptr;
+  m->use_pdl = true;
+  // cross-launch L2 prefetch of later weights: measured neutral-to-slower on B200 for this chain (the launches are
+  // latency-bound, not HBM-bound), so it stays off
+  m->l2_prefetch = false;
   m->out_cap_steps = 0;
   {
     // table of per-layer weight pointers for the persistent decode kernel

@@ -89,8 +89,7 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(const float* __res
 }  // namespace
 
 bool matmul_f32x3_applicable(long long M, long long N, long long K, long long batch) {
-  static const bool off = std::getenv("CATGRAD_B200_F32_SIMT") != nullptr;
-  if (off || !tcgen05_available()) return false;
+  if (!tcgen05_available()) return false;
   if (K % 8 != 0 || K < 64 || N < 64 || M * batch < 128 || batch > 65535) return false;
   return 2.0 * (double)M * (double)N * (double)K * (double)batch >= 2.68e8;   // ~2^28 flop: below that the split passes dominate
 }

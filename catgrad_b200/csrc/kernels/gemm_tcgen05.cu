@@ -16,7 +16,9 @@
 //   warps 2..5       : epilogue.  tcgen05.ld pulls the f32 accumulator (each warp its 32 TMEM lanes = 32 rows),
 //                      rounds once to bf16 and stores 64-byte row segments.
 // Rows/columns beyond M, N, K are zero-filled by TMA on the way in and masked on the way out, so any M, N and any
-// K that keeps rows 16-byte aligned work.  No multicast, no clusters: the kernel may run in multi-GPU jobs.
+// K that keeps rows 16-byte aligned work.  Every TMA load is a plain cp.async.bulk.tensor (no cluster multicast) over
+// this GPU's own memory, so the kernel may run in multi-GPU jobs; the split-K variant launches thread-block clusters
+// and uses them only for a cluster barrier and distributed-shared-memory reads of the partial tiles.
 //
 // Every wait on an mbarrier is bounded: after ~1 s a role records DEV_ERR_WAIT_TIMEOUT, raises a CTA-wide abort
 // flag, all roles fall through, TMEM is freed and the kernel returns.
@@ -759,8 +761,7 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
   }
   // One or two row tiles and too few 128-wide column tiles to fill the GPU: split K over a cluster instead of
   // cutting the columns finer (narrow tiles re-read the activations once per tile).
-  static const bool no_splitk = std::getenv("CATGRAD_B200_NO_SPLITK") != nullptr;
-  if (streaming && !no_splitk && p.batch == 1 && N >= 64) {
+  if (streaming && p.batch == 1 && N >= 64) {
     const long long num_k = (K + BK - 1) / BK;
     // candidates: column tiles of 128 or 64, 2/4/8-way split; keep the one that occupies the most SMs in ONE wave
     // of clusters (ties: wider tiles, then fewer splits)

@@ -66,7 +66,7 @@ class LlamaConfig:
         return sum(int(np.prod(s)) for _, s in self.param_shapes())
 
 
-# The model shapes BASELINE.json names.
+# The model shapes of the benchmark configurations: the tiny f32 model, Llama-3.2-1B and Llama-3-8B.
 TINY = LlamaConfig(256, 688, 2, 4, 4, 1024, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
 LLAMA_1B = LlamaConfig(2048, 8192, 16, 32, 8, 128256, rope_theta=500000.0, rms_norm_eps=1e-5,
                        tie_word_embeddings=True)

@@ -5,6 +5,8 @@ batch-polymorphic (llama.rs:159,271), which is what makes this split legal: ever
 of which rank ran it and of the other sequences in its batch.  There is no collective on the data path; the
 generated ids are gathered once at the end.
 """
+import ctypes as C
+
 import numpy as np
 
 
@@ -52,3 +54,65 @@ def generate_sharded(make_runner, prompts, steps, dist=None, device=None):
     else:
         local = np.zeros((0, steps), dtype=np.uint32)
     return gather_rows(local, prompts.shape[0], dist, device)
+
+
+class DeviceRunner:
+    """`cg_runner_*`: one process driving several GPUs, one context + weight replica + fused Llama runner per device
+    on its own host thread, sequences split by `shard_range`, ids gathered on the host.
+
+        r = DeviceRunner([0, 1, 2, 3], cfg, Dtype.BF16, max_batch_per_device=64, max_positions=256)
+        for i in range(r.size):
+            r.set_params(i, upload_weights(r.backend(i), weights, Dtype.BF16))
+        ids = r.generate(prompts, steps)                 # [n_seq, steps]
+    """
+
+    def __init__(self, devices, cfg, dtype, max_batch_per_device, max_positions):
+        from . import _ffi
+        from .backend import BackendError
+        self._ns = _ffi.bind(C.CDLL(_ffi.library_path()))
+        self._err = BackendError
+        devs = (C.c_int * len(devices))(*[int(d) for d in devices])
+        st = cfg.to_struct()
+        h = C.c_void_p()
+        code = self._ns.runner_create(devs, len(devices), C.byref(st), int(dtype), int(max_batch_per_device), int(max_positions),
+                                      C.byref(h))
+        if code != 0:
+            raise BackendError(code, self._ns.last_error(None).decode())
+        self._h = h
+        self._keep = {}
+
+    @property
+    def size(self):
+        return int(self._ns.runner_size(self._h))
+
+    def backend(self, i):
+        """A `Backend` over replica i's context (owned by the runner): upload that replica's parameters through it."""
+        from .backend import Backend
+        ctx = self._ns.runner_ctx(self._h, int(i))
+        if not ctx:
+            raise IndexError(i)
+        return Backend(_borrowed_ctx=C.c_void_p(ctx))
+
+    def set_params(self, i, params):
+        code = self._ns.runner_set_params(self._h, int(i), params.handle)
+        if code != 0:
+            raise self._err(code, self._ns.last_error(None).decode())
+        self._keep[i] = params
+
+    def generate(self, prompts, steps):
+        prompts = np.ascontiguousarray(prompts, dtype=np.uint32)
+        n, s = prompts.shape
+        out = np.zeros((n, steps), dtype=np.uint32)
+        code = self._ns.runner_generate(self._h, prompts.ctypes.data_as(C.c_void_p), n, s, int(steps), out.ctypes.data_as(C.c_void_p))
+        if code != 0:
+            raise self._err(code, self._ns.runner_last_error(self._h).decode() or self._ns.last_error(None).decode())
+        return out
+
+    def close(self):
+        h, self._h = getattr(self, "_h", None), None
+        self._keep = {}
+        if h:
+            self._ns.runner_free(h)
+
+    def __del__(self):
+        self.close()

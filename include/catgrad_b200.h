@@ -240,6 +240,25 @@ uint64_t cg_llama_context_len(const cg_llama* m);
 /* Number of kernel launches issued by this runner since creation (graph replays count their nodes). */
 uint64_t cg_llama_launch_count(const cg_llama* m);
 
+/* ---- batch-sharded multi-GPU runner (B200 only; the reference runs one device, batch 1: main.rs:947-951) -----
+ * One process drives several GPUs: a context, a weight replica and a fused Llama runner per device, each on its own
+ * host thread; independent sequences are split into contiguous shares (the first n % devices shares hold one more),
+ * there is no exchange while generating, and the ids are gathered on the host at the end.  Legal because the Llama
+ * term is batch-polymorphic (llama.rs:159,271).  Usage: create, upload each replica's parameters through
+ * cg_runner_ctx(r, i) (cg_from_vec_* / cg_params_set), cg_runner_set_params(r, i, params), then generate. */
+typedef struct cg_runner cg_runner;
+cg_status cg_runner_create(const int* devices, int n_devices, const cg_llama_config* cfg, cg_dtype dtype,
+                           uint64_t max_batch_per_device, uint64_t max_positions, cg_runner** out);
+int cg_runner_size(const cg_runner* r);
+cg_ctx* cg_runner_ctx(cg_runner* r, int i);
+cg_status cg_runner_set_params(cg_runner* r, int i, const cg_params* params);
+/* prompts [n_seq, prompt_len] u32 (host) -> out_ids [n_seq, steps] u32 (host): the greedy ids generate_stream
+ * (main.rs:876-1043) would produce for each sequence on its own, EOS ignored. */
+cg_status cg_runner_generate(cg_runner* r, const uint32_t* prompts, uint64_t n_seq, uint64_t prompt_len, uint64_t steps,
+                             uint32_t* out_ids);
+const char* cg_runner_last_error(const cg_runner* r);
+void cg_runner_free(cg_runner* r);
+
 /* ---- timing and allocator introspection ---------------------------------------------------- */
 /* CUDA events on the context's stream (the stream every kernel of this library is launched on). */
 cg_status cg_event_record(cg_ctx*, int slot /* 0..63 */);

@@ -1,12 +1,15 @@
-"""Writes tests/golden/llama1b_bf16_semantics.json: how far the reference's own bf16 semantics (every op output
-rounded to bf16, candle.rs:1165-1192, as restated by the CPU oracle in bf16 mode) lands from the f32 evaluation of
-the same Llama-3.2-1B-shaped model (weights rounded to bf16 first), on the inputs tests/test_gpu_full_dims.py uses:
-seed-0 weights, a 16-token prompt from seed 1, two decode steps fed with the f32 run's ids.
+"""Writes tests/golden/llama1b_bf16_semantics.json (default) or llama8b2l_bf16_semantics.json (argument "8b2l"):
+how far the reference's own bf16 semantics (every op output rounded to bf16, candle.rs:1165-1192, as restated by the
+CPU oracle in bf16 mode) lands from the f32 evaluation of the same model (weights rounded to bf16 first), on the
+inputs tests/test_gpu_full_dims.py uses:
+  1b   : Llama-3.2-1B shape, seed-0 weights, a 16-token prompt from seed 1, two decode steps fed with the f32 run's ids;
+  8b2l : Llama-3-8B dimensions at two layers, seed-3 weights, an 8-token prompt from seed 5, one decode step.
 
-The bf16 kernels are held to the f32 oracle with a bar derived from these figures, because at this size the 2e-2
+The bf16 kernels are held to the f32 oracle with a bar derived from these figures, because at these sizes the 2e-2
 max-abs bar that holds for small models is out of reach for the reference semantics themselves.
 
-Run from the repository root (about 10 minutes of CPU, ~12 GB of RAM):  python tests/golden/make_llama1b_bf16_semantics.py
+Run from the repository root (about 10 minutes of CPU, ~12 GB of RAM):
+    python tests/golden/make_llama1b_bf16_semantics.py [8b2l]
 """
 import ctypes
 import gc
@@ -46,25 +49,34 @@ def run(oracle, cfg, wb, dtype, ids, forced):
 
 
 def main():
+    global PROMPT, DECODE
     so = os.path.join(ROOT, "oracle", "_build", "libndarray_ref.so")
     oracle = cb.Backend(_cdll=ctypes.CDLL(so), _prefix="ref_")
-    cfg = cb.LLAMA_1B
-    w = cb.random_weights(cfg, seed=0)
+    which = sys.argv[1] if len(sys.argv) > 1 else "1b"
+    if which == "8b2l":
+        cfg = cb.LlamaConfig(4096, 14336, 2, 32, 8, 128256, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
+        wseed, pseed, PROMPT, DECODE = 3, 5, 8, 1
+        name, out_name = "Llama-3-8B dimensions, 2 layers", "llama8b2l_bf16_semantics.json"
+    else:
+        cfg = cb.LLAMA_1B
+        wseed, pseed = 0, 1
+        name, out_name = "Llama-3.2-1B shape", "llama1b_bf16_semantics.json"
+    w = cb.random_weights(cfg, seed=wseed)
     wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
     del w
-    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(1, PROMPT), dtype=np.uint32)
+    ids = np.random.default_rng(pseed).integers(0, cfg.vocab_size, size=(1, PROMPT), dtype=np.uint32)
     ids32, l32 = run(oracle, cfg, wb, Dtype.F32, ids, None)
     ids16, l16 = run(oracle, cfg, wb, Dtype.BF16, ids, ids32)
     d = np.abs(l16 - l32)
     out = {
-        "model": "Llama-3.2-1B shape, seed-0 N(0, 0.02) weights rounded to bf16, norm gains 1",
-        "prompt_seed": 1, "prompt_len": PROMPT, "decode_steps": DECODE,
+        "model": f"{name}, seed-{wseed} N(0, 0.02) weights rounded to bf16, norm gains 1",
+        "prompt_seed": pseed, "prompt_len": PROMPT, "decode_steps": DECODE,
         "f32_ids": ids32, "bf16_ids": ids16,
         "logit_absmax": [float(np.abs(r).max()) for r in l32], "logit_std": [float(r.std()) for r in l32],
         "bf16_vs_f32_max_abs": [float(r.max()) for r in d], "bf16_vs_f32_mean_abs": [float(r.mean()) for r in d],
         "top2_gap_f32": [float(np.sort(r)[-1] - np.sort(r)[-2]) for r in l32],
     }
-    with open(os.path.join(ROOT, "tests", "golden", "llama1b_bf16_semantics.json"), "w") as f:
+    with open(os.path.join(ROOT, "tests", "golden", out_name), "w") as f:
         json.dump(out, f, indent=1)
     print(json.dumps(out, indent=1))
 

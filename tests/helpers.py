@@ -194,3 +194,25 @@ def rel_err(a, b):
     a = np.asarray(a, dtype=np.float64)
     b = np.asarray(b, dtype=np.float64)
     return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+# ---- the bf16 bar at full model dimensions ---------------------------------------------------------------
+def bf16_semantics(name):
+    """tests/golden/<name>_bf16_semantics.json: how far the reference's own bf16 semantics (the CPU oracle rounding every
+    op output to bf16) land from its f32 run on a fixed model and prompt; written by make_llama1b_bf16_semantics.py."""
+    with open(os.path.join(GOLDEN, name + "_bf16_semantics.json")) as f:
+        return json.load(f)
+
+
+def check_bf16_against_f32(sem, step, got, want, small_bar=2e-2, max_factor=1.25, mean_factor=1.25):
+    """bf16 logits `got` of call `step` (0 = prefill; None = the worst call of the fixture) against f32 logits `want`: no
+    worse than the reference semantics themselves by more than the given factors, never tighter than the small-model
+    bar; and the same greedy id wherever the f32 top-2 gap clearly exceeds the error."""
+    pick = (lambda v: max(v)) if step is None else (lambda v: v[step])
+    d = np.abs(np.asarray(got, np.float64) - np.asarray(want, np.float64))
+    max_bar = max(small_bar, max_factor * pick(sem["bf16_vs_f32_max_abs"]))
+    mean_bar = mean_factor * pick(sem["bf16_vs_f32_mean_abs"])
+    assert d.max() <= max_bar, ("max-abs", step, float(d.max()), max_bar)
+    assert d.mean() <= mean_bar, ("mean-abs", step, float(d.mean()), mean_bar)
+    if step is not None and got.ndim == 1 and sem["top2_gap_f32"][step] > 2 * d.max():
+        assert int(np.argmax(got)) == int(np.argmax(want))

@@ -2,7 +2,8 @@
 
 * Llama-3.2-1B shape, all 16 layers (hidden 2048, 32 query / 8 kv heads x 64, FFN 8192, vocabulary 128256, tied
   head): the CPU oracle (f32, weights rounded to bf16 first) runs a 16-token prompt and two decode steps; the fused
-  f32 runner must give the same ids and logits within rel 1e-4, the fused bf16 runner logits within 2e-2 max-abs.
+  f32 runner must give the same ids and logits within rel 1e-4, the fused bf16 runner (both decode plans) logits
+  within the bf16 bar described below.
   This is the only place where the 128256-row head, the K = 8192 down projection and the stacked [q;k;v] /
   [gate;up] weights meet the oracle.
 * The per-GPU batches of the batch-sharded workload (32 and 256 sequences: tensor-core GEMM path, split-K
@@ -10,8 +11,13 @@
 * Llama-3-8B dimensions (hidden 4096, 32 / 8 heads x 128, FFN 14336, untied head) at two layers against the oracle.
 * The op-sweep shapes at full size where the oracle finishes in seconds (gather, argmax, pointwise in bf16).
 
-Bars: ids exact (f32), f32 logits rel <= 1e-4, bf16 logits <= 2e-2 max-abs against f32 on the same weights,
-integer/index results and correctly rounded pointwise results bit-exact."""
+Bars: ids exact (f32), f32 logits rel <= 1e-4, integer/index results and correctly rounded pointwise results
+bit-exact.  bf16 logits: <= 2e-2 max-abs against f32 on the same weights wherever the reference's own bf16 semantics
+meet that bar.  At the full 1B depth they do not: the CPU oracle in bf16 mode (every op output rounded to bf16,
+candle.rs:1165-1192) is 0.09-0.10 max-abs and 0.016-0.017 mean-abs away from its own f32 run on these inputs
+(tests/golden/llama1b_bf16_semantics.json, written by make_llama1b_bf16_semantics.py).  There the kernels are held
+to "no worse than the reference semantics": max-abs and mean-abs error against the f32 oracle within 1.25x of the
+bf16 oracle's, and the same greedy id wherever the f32 run's top-2 gap exceeds twice the error."""
 import gc
 
 import numpy as np
@@ -28,6 +34,13 @@ REL_F32 = 1e-4
 ABS_BF16 = 2e-2
 PROMPT = 16
 DECODE = 2
+SEM_1B = helpers.bf16_semantics("llama1b")
+SEM_8B2L = helpers.bf16_semantics("llama8b2l")
+assert SEM_1B["prompt_len"] == PROMPT and SEM_1B["decode_steps"] == DECODE
+
+
+def bf16_bar_1b(step, got, want):
+    helpers.check_bf16_against_f32(SEM_1B, step, got, want, small_bar=ABS_BF16)
 
 
 def bf16_round(w):
@@ -90,13 +103,13 @@ def test_1b_shape_bf16_runner_against_the_f32_oracle(gpu, model_1b, oracle_1b, g
     ids, ref_ids, ref_logits = oracle_1b
     r = cb.LlamaRunner(gpu, cfg, gpu_params_1b["bf16"], Dtype.BF16, max_batch=1, max_positions=PROMPT + DECODE + 1)
     r.set_persistent(persistent)
+    assert ref_ids[0].tolist() == SEM_1B["f32_ids"]          # the fixture was made from the same oracle run
     r.reset(1)
     r.forward(ids)
-    worst = float(np.abs(r.last_logits()[0] - ref_logits[0][0]).max())
+    bf16_bar_1b(0, r.last_logits()[0], ref_logits[0][0])
     for i in range(1, DECODE + 1):
         r.forward(ref_ids[:, i - 1].reshape(1, 1))
-        worst = max(worst, float(np.abs(r.last_logits()[0] - ref_logits[i][0]).max()))
-    assert worst <= ABS_BF16, worst
+        bf16_bar_1b(i, r.last_logits()[0], ref_logits[i][0])
     if persistent:
         assert r.persistent_active, "the persistent decode kernel was not used for this shape"
 
@@ -112,15 +125,20 @@ def test_1b_shape_batched_bf16_decode_against_the_pinned_f32_runner(gpu, model_1
     r32 = cb.LlamaRunner(gpu, cfg, gpu_params_1b["f32"], Dtype.F32, max_batch=batch, max_positions=P)
     r16.reset(batch)
     r32.reset(batch)
+    # see the module docstring; the maximum here is taken over up to 256 x 128256 logits instead of 128256, so the
+    # max-abs bar gets twice the single-sequence figure while the mean-abs bar stays at 1.25x
+    def close(a, b):
+        helpers.check_bf16_against_f32(SEM_1B, None, a, b, small_bar=ABS_BF16, max_factor=2.0)
+
     first = r16.forward(ids)
     r32.forward(ids)
-    assert np.abs(r16.last_logits() - r32.last_logits()).max() <= ABS_BF16
+    close(r16.last_logits(), r32.last_logits())
     rest = r16.decode(DECODE)                       # the path the benchmark times
     tok = first
     for s in range(DECODE):                         # f32 runner fed the bf16 run's ids: same history on both sides
         r32.forward(tok.reshape(batch, 1))
         tok = rest[:, s]
-    assert np.abs(r16.last_logits() - r32.last_logits()).max() <= ABS_BF16
+    close(r16.last_logits(), r32.last_logits())
     # sequences are independent: row b of the batch equals running it alone (what batch sharding relies on)
     solo = cb.LlamaRunner(gpu, cfg, gpu_params_1b["bf16"], Dtype.BF16, max_batch=1, max_positions=P)
     solo.set_persistent(False)
@@ -129,15 +147,17 @@ def test_1b_shape_batched_bf16_decode_against_the_pinned_f32_runner(gpu, model_1
         solo.forward(ids[b:b + 1])
         for s in range(DECODE):
             solo.forward(np.array([[first[b] if s == 0 else rest[b, s - 1]]], dtype=np.uint32))
-        assert np.abs(solo.last_logits()[0] - r16.last_logits()[b]).max() <= ABS_BF16
+        close(solo.last_logits()[0], r16.last_logits()[b])
 
 
 def test_8b_dimensions_two_layers_against_the_oracle(oracle, gpu):
-    """hidden 4096, 32 query / 8 kv heads x 128, FFN 14336, untied 128256-row head; two of the 32 layers."""
+    """hidden 4096, 32 query / 8 kv heads x 128, FFN 14336, untied 128256-row head; two of the 32 layers.  The bf16 bar
+    comes from tests/golden/llama8b2l_bf16_semantics.json (same model, prompt and steps)."""
     cfg = cb.LlamaConfig(4096, 14336, 2, 32, 8, 128256, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
     wb = bf16_round(cb.random_weights(cfg, seed=3))
     ids = np.random.default_rng(5).integers(0, cfg.vocab_size, size=(1, 8), dtype=np.uint32)
     ref_ids, ref_logits = oracle_run(oracle, cfg, wb, ids, 1)
+    assert ref_ids[0].tolist() == SEM_8B2L["f32_ids"]
     p32 = cb.upload_weights(gpu, wb, Dtype.F32)
     r32 = cb.LlamaRunner(gpu, cfg, p32, Dtype.F32, max_batch=1, max_positions=12)
     np.testing.assert_array_equal(r32.generate(ids, 2), ref_ids)
@@ -150,9 +170,11 @@ def test_8b_dimensions_two_layers_against_the_oracle(oracle, gpu):
         r16 = cb.LlamaRunner(gpu, cfg, p16, Dtype.BF16, max_batch=batch, max_positions=12)
         r16.reset(batch)
         r16.forward(np.repeat(ids, batch, 0))
-        assert np.abs(r16.last_logits() - ref_logits[0]).max() <= ABS_BF16
+        for b in range(batch):
+            helpers.check_bf16_against_f32(SEM_8B2L, 0, r16.last_logits()[b], ref_logits[0][0], small_bar=ABS_BF16)
         r16.forward(np.repeat(ref_ids[:, :1], batch, 0))
-        assert np.abs(r16.last_logits() - ref_logits[1]).max() <= ABS_BF16
+        for b in range(batch):
+            helpers.check_bf16_against_f32(SEM_8B2L, 1, r16.last_logits()[b], ref_logits[1][0], small_bar=ABS_BF16)
         del r16
 
 

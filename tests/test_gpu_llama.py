@@ -1,4 +1,4 @@
-"""Llama through the C ABI on the GPU against the CPU oracle (BASELINE config 1 and reduced bf16 shapes).
+"""Llama through the C ABI on the GPU against the CPU oracle (the tiny f32 configuration and reduced bf16 shapes).
 
 Bars: greedy ids exact and f32 logits within rel 1e-4 on the tiny model; bf16 logits within 2e-2 max-abs of the
 f32 oracle run on the same (bf16-rounded) weights."""
@@ -351,3 +351,27 @@ def test_persistent_decode_kernel_long_contexts_and_head_shapes(gpu, heads, kv_h
         t2 = again.forward(t2.reshape(batch, 1))
         cols.append(t2)
     np.testing.assert_array_equal(more, np.stack(cols, 1))
+
+
+def test_device_runner_shards_sequences_over_replicas(gpu):
+    """cg_runner_*: sequences split over replicas (two contexts here; on a box with several GPUs one per GPU), ids
+    gathered on the host: every row must equal what a single runner produces for it, in the right place."""
+    import torch
+    from catgrad_b200.runner import DeviceRunner, shard_range
+    cfg, w, _ = tiny_inputs()
+    n_dev = torch.cuda.device_count()
+    devices = [0, 1 % n_dev, 0]                      # three replicas; 7 sequences split 3 + 2 + 2
+    ids = np.random.default_rng(17).integers(0, cfg.vocab_size, size=(7, 10), dtype=np.uint32)
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    want = cb.LlamaRunner(gpu, cfg, params, Dtype.F32, max_batch=7, max_positions=32).generate(ids, 6)
+    r = DeviceRunner(devices, cfg, Dtype.F32, max_batch_per_device=3, max_positions=32)
+    assert r.size == 3 and shard_range(7, 3, 0) == (0, 3) and shard_range(7, 3, 2) == (5, 7)
+    with pytest.raises(cb.BackendError):
+        r.generate(ids, 6)                           # no parameters yet
+    for i in range(r.size):
+        r.set_params(i, cb.upload_weights(r.backend(i), w, Dtype.F32))
+    np.testing.assert_array_equal(r.generate(ids, 6), want)
+    np.testing.assert_array_equal(r.generate(ids[:2], 6), want[:2])          # fewer sequences than replicas: one idles
+    with pytest.raises(cb.BackendError):
+        r.generate(np.zeros((10, 10), np.uint32), 2)     # 4 sequences on a replica sized for 3
+    r.close()

@@ -437,3 +437,23 @@ def test_tensor_core_gemm_row_major_batched(gpu):
     got = gpu.to_f32(gpu.matmul(gpu.from_numpy(a, Dtype.BF16), gpu.from_numpy(b, Dtype.BF16)))
     ref64 = np.einsum("bmk,bkn->bmn", a.astype(np.float64), b.astype(np.float64))
     np.testing.assert_allclose(got, ref64, rtol=2e-2, atol=3e-2)
+
+
+def test_probe_and_format_on_the_gpu(gpu, capfd, monkeypatch):
+    """Probe through cg_interp_run on the CUDA backend (a synchronising read-back) and cg_format."""
+    tb = cb.TermBuilder(gpu)
+    x = tb.source(cb.NodeType.Tensor)
+    y = x * x
+    tb.probe("squared", y)
+    term = tb.finish([y])
+    a = np.array([[3.0, -1.5], [0.25, 8.0]], np.float32)
+    monkeypatch.setenv("CATGRAD_PROBE", "1")
+    out = cb.Interpreter(gpu).run(term, [gpu.from_numpy(a)])
+    np.testing.assert_array_equal(gpu.to_numpy(out[0]), a * a)
+    text = capfd.readouterr().out
+    assert "[probe:squared]" in text and "f32" in text and "[2,2]" in text and "2.25" in text and "64" in text
+    monkeypatch.delenv("CATGRAD_PROBE")
+    cb.Interpreter(gpu).run(term, [gpu.from_numpy(a)])
+    assert "[probe:" not in capfd.readouterr().out
+    s = gpu.format_tensor(gpu.transpose(gpu.from_numpy(a, Dtype.BF16), 0, 1))      # a strided view prints in logical order
+    assert "bf16" in s and s.index("0.25") < s.index("-1.5")

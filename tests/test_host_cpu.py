@@ -190,3 +190,29 @@ def test_reduced_precision_conversions(oracle):
     np.testing.assert_array_equal(b[~np.isnan(x)], wantb[~np.isnan(x)])
     back = oracle.to_numpy(oracle.cast(oracle.cast(t, Dtype.F16), Dtype.F32))
     np.testing.assert_array_equal(back[~np.isnan(x)], want.astype(np.float32)[~np.isnan(x)])
+
+
+def _probe_term(be):
+    tb = cb.TermBuilder(be)
+    x = tb.source(cb.NodeType.Tensor)
+    y = x + x
+    tb.probe("doubled", y)
+    return tb.finish([y])
+
+
+def test_probe_prints_only_when_asked_and_format_names_dtype_shape_values(oracle, capfd, monkeypatch):
+    """Probe (tensor_op.rs:121-136): a debug print of format_tensor, only with CATGRAD_PROBE set, no outputs."""
+    x = np.array([[1.5, -2.0, 3.25]], np.float32)
+    term = _probe_term(oracle)
+    monkeypatch.delenv("CATGRAD_PROBE", raising=False)
+    out = cb.Interpreter(oracle).run(term, [oracle.from_numpy(x)])
+    assert len(out) == 1 and "[probe:" not in capfd.readouterr().out
+    monkeypatch.setenv("CATGRAD_PROBE", "1")
+    out = cb.Interpreter(oracle).run(term, [oracle.from_numpy(x)])
+    np.testing.assert_array_equal(oracle.to_numpy(out[0]), 2 * x)
+    text = capfd.readouterr().out
+    assert "[probe:doubled]" in text and "f32" in text and "[1,3]" in text and "-4" in text and "6.5" in text
+    # format_tensor on its own: dtype, shape, leading values; u32 and bf16 too
+    assert "u32" in oracle.format_tensor(oracle.from_numpy(np.arange(5, dtype=np.uint32)))
+    s = oracle.format_tensor(oracle.from_numpy(np.array([0.5, 2.0], np.float32), cb.Dtype.BF16))
+    assert "bf16" in s and "0.5" in s and "2" in s
