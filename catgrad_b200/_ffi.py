@@ -27,6 +27,11 @@ class LlamaConfigStruct(C.Structure):
         ("rope_theta", C.c_float),
         ("rms_norm_eps", C.c_float),
         ("tie_word_embeddings", C.c_int),
+        ("rope_scaling_type", C.c_int),
+        ("rope_factor", C.c_float),
+        ("rope_low_freq_factor", C.c_float),
+        ("rope_high_freq_factor", C.c_float),
+        ("rope_original_max_position", C.c_uint64),
     ]
 
 

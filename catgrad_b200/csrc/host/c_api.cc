@@ -359,6 +359,9 @@ typedef struct {
   uint64_t hidden_size, intermediate_size, num_hidden_layers, num_attention_heads, num_key_value_heads, vocab_size;
   float rope_theta, rms_norm_eps;
   int tie_word_embeddings;
+  int rope_scaling_type;
+  float rope_factor, rope_low_freq_factor, rope_high_freq_factor;
+  uint64_t rope_original_max_position;
 } api_llama_config;
 
 int API(llama_term)(const api_llama_config* cfg, int tap_logits, cg_term** out) {
@@ -378,6 +381,15 @@ int API(llama_term)(const api_llama_config* cfg, int tap_logits, cg_term** out) 
   c.rope_theta = cfg->rope_theta;
   c.rms_norm_eps = cfg->rms_norm_eps;
   c.tie_word_embeddings = cfg->tie_word_embeddings;
+  c.rope_scaling_type = cfg->rope_scaling_type;
+  c.rope_factor = cfg->rope_factor;
+  c.rope_low_freq_factor = cfg->rope_low_freq_factor;
+  c.rope_high_freq_factor = cfg->rope_high_freq_factor;
+  c.rope_original_max_position = (int64_t)cfg->rope_original_max_position;
+  CG_CHECK(c.rope_scaling_type == 0 || (c.rope_scaling_type == 1 && c.rope_factor > 0.f && c.rope_original_max_position > 0 &&
+                                        c.rope_high_freq_factor != c.rope_low_freq_factor && c.rope_low_freq_factor > 0.f &&
+                                        c.rope_high_freq_factor > 0.f),
+           ERR_INVALID_ARG, "rope_scaling: type must be 0 (none) or 1 (llama3) with positive factors");
   std::unique_ptr<cg_term> term(new cg_term());
   term->t = build_llama_term(c, tap_logits != 0);
   schedule(term->t);

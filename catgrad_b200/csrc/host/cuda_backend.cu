@@ -379,6 +379,9 @@ Tensor CudaBackend::matmul(const Tensor& a, const Tensor& b) {
   CG_CHECK(a.dt != Dtype::F8, ERR_UNSUPPORTED_DTYPE, "fp8 matmul is not supported");
   int r = a.rank();
   int64_t M = a.shape[r - 2], K = a.shape[r - 1], N = b.shape[r - 1];
+  // the kernels index rows, columns and output tiles with 32-bit integers
+  CG_CHECK(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) && ((M + 63) / 64) * ((N + 63) / 64) < (1ll << 31), ERR_INVALID_ARG,
+           "matmul: a dimension (or the number of 64 x 64 output tiles) reaches 2^31");
   Tensor t = empty(out, a.dt);
   if (t.size() == 0) return t;
   if (K == 0) {
@@ -394,6 +397,7 @@ Tensor CudaBackend::matmul(const Tensor& a, const Tensor& b) {
     bt.total = 1;
   }
   CG_CHECK(batch <= 65535, ERR_INVALID_ARG, "matmul: more than 65535 batch entries");
+
   int64_t sam = a.strides[r - 2], sak = a.strides[r - 1], sbk = b.strides[r - 2], sbn = b.strides[r - 1];
   // bf16 products with K-contiguous A go to the tensor cores; the right operand may be K-contiguous (x @ W^T) or
   // N-contiguous (the trait's row-major [.., K, N])

@@ -19,6 +19,9 @@ typedef struct {
   uint64_t hidden_size, intermediate_size, num_hidden_layers, num_attention_heads, num_key_value_heads, vocab_size;
   float rope_theta, rms_norm_eps;
   int tie_word_embeddings;
+  int rope_scaling_type;
+  float rope_factor, rope_low_freq_factor, rope_high_freq_factor;
+  uint64_t rope_original_max_position;
 } runner_llama_config;
 int cg_init(int device, cg_ctx** out);
 void cg_destroy(cg_ctx* c);

@@ -174,6 +174,10 @@ struct LlamaConfig {
   float rope_theta = 10000.f;
   float rms_norm_eps = 1e-5f;
   int tie_word_embeddings = 0;
+  // rope_scaling (config.rs:10-18; helpers/rope.rs:14-60): 0 = absent (default tables), 1 = "llama3"
+  int rope_scaling_type = 0;
+  float rope_factor = 1.f, rope_low_freq_factor = 1.f, rope_high_freq_factor = 1.f;
+  int64_t rope_original_max_position = 0;
   int64_t head_dim() const { return hidden_size / num_attention_heads; }  // llama.rs:54-56
 };
 

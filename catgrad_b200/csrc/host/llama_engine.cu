@@ -87,6 +87,7 @@ struct cg_llama {
 
   cudaGraphExec_t graph = nullptr;
   int64_t graph_batch = -1;
+  int graph_ctx_bucket = -1;   // 0: captured at a context <= 512, 1: above (the attention variant is chosen by that)
   uint64_t graph_nodes = 0;
 
   ~cg_llama() {
@@ -837,6 +838,9 @@ typedef struct {
   uint64_t hidden_size, intermediate_size, num_hidden_layers, num_attention_heads, num_key_value_heads, vocab_size;
   float rope_theta, rms_norm_eps;
   int tie_word_embeddings;
+  int rope_scaling_type;
+  float rope_factor, rope_low_freq_factor, rope_high_freq_factor;
+  uint64_t rope_original_max_position;
 } api_llama_config;
 
 }  // extern "C"
@@ -866,6 +870,15 @@ int create_runner(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const cg_
   c.rope_theta = cfg->rope_theta;
   c.rms_norm_eps = cfg->rms_norm_eps;
   c.tie_word_embeddings = cfg->tie_word_embeddings;
+  c.rope_scaling_type = cfg->rope_scaling_type;
+  c.rope_factor = cfg->rope_factor;
+  c.rope_low_freq_factor = cfg->rope_low_freq_factor;
+  c.rope_high_freq_factor = cfg->rope_high_freq_factor;
+  c.rope_original_max_position = (int64_t)cfg->rope_original_max_position;
+  CG_CHECK(c.rope_scaling_type == 0 || (c.rope_scaling_type == 1 && c.rope_factor > 0.f && c.rope_original_max_position > 0 &&
+                                        c.rope_high_freq_factor != c.rope_low_freq_factor && c.rope_low_freq_factor > 0.f &&
+                                        c.rope_high_freq_factor > 0.f),
+           ERR_INVALID_ARG, "rope_scaling: type must be 0 (none) or 1 (llama3) with positive factors");
   CG_CHECK(c.num_attention_heads > 0 && c.num_key_value_heads > 0 && c.hidden_size % c.num_attention_heads == 0 &&
                c.num_attention_heads % c.num_key_value_heads == 0 && c.num_hidden_layers > 0,
            ERR_INVALID_ARG, "inconsistent Llama config");
@@ -930,7 +943,9 @@ int create_runner(cg_ctx* ctx, const api_llama_config* cfg, int dtype, const cg_
   m->sin_t = be.empty({m->P, hd / 2}, Dtype::F32);
   cgk::rope_table_kernel<<<std::max<int>(1, (int)std::min<int64_t>((m->P * (hd / 2) + 255) / 256, 1024)), 256, 0,
                            be.stream()>>>((float*)m->cos_t.raw(), (float*)m->sin_t.raw(), (int)m->P, (int)(hd / 2),
-                                          c.rope_theta, 2.0f / (float)hd);
+                                          c.rope_theta, 2.0f / (float)hd,
+                                          cgk::RopeScalingArgs{c.rope_scaling_type, c.rope_factor, c.rope_low_freq_factor,
+                                                               c.rope_high_freq_factor, (float)c.rope_original_max_position});
   be.check_launch("rope_table");
   m->words = be.zeros({16}, Dtype::U32);
   m->ids_cur = be.zeros({m->max_batch}, Dtype::U32);
@@ -1068,7 +1083,11 @@ int cg_llama_decode(cg_llama* mm, uint64_t steps, uint32_t* out_ids) {
   const bool mega = mega_available(m, B);
   const bool use_graph = !mega && std::getenv("CATGRAD_B200_NO_GRAPH") == nullptr;
   uint64_t first = 0;
-  if (use_graph && (m.graph == nullptr || m.graph_batch != B)) {
+  // The capture bakes in the attention variant picked from the context length at capture time (one launch up to 512
+  // cached positions, keys split over CTAs above): a graph captured on the other side of 512 is captured again.  Within
+  // one call the variant stays what it was at the call's first step (results are the same, only the speed differs).
+  const int ctx_bucket = m.host_ctx_len + 1 > 512 ? 1 : 0;
+  if (use_graph && (m.graph == nullptr || m.graph_batch != B || m.graph_ctx_bucket != ctx_bucket)) {
     // The first step of a new shape runs eagerly (it also loads the kernels and sets their attributes,
     // neither of which belongs inside a capture); the capture below records the same launches.
     run_step(m, (const unsigned*)m.ids_cur.raw(), B, 1);
@@ -1098,6 +1117,7 @@ int cg_llama_decode(cg_llama* mm, uint64_t steps, uint32_t* out_ids) {
     cudaGraphDestroy(g);
     if (e != cudaSuccess) throw Error(ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
     m.graph_batch = B;
+    m.graph_ctx_bucket = ctx_bucket;
   }
   for (uint64_t i = first; i < steps;) {
     if (use_graph) {

@@ -2,7 +2,8 @@
 //   catgrad-llm-models/src/models/llama.rs:144-385   (forward, attention, mlp, layer)
 //   catgrad-llm-models/src/helpers/tensors.rs        (embeddings, rmsnorm, causal_mask, repeat_kv, squeeze)
 //   catgrad-llm-models/src/helpers/cache.rs:13-103   (functional KV cache, Cache::init)
-//   catgrad-llm-models/src/helpers/rope.rs:65-104,423-451 (default RoPE tables, rotate_half, apply)
+//   catgrad-llm-models/src/helpers/rope.rs:14-60,65-104,232-314,423-451 (table choice, default and llama3 RoPE tables,
+//                                                     rotate_half, apply)
 // Every helper expands inline into primitive edges, as in the reference (no Definition edges).
 // Parameter keys are the safetensors names (`model.layers.0.self_attn.q_proj.weight`, ...), i.e.
 // what `to_load_ops` leaves after stripping the `llama.` prefix (stdlib_definitions.rs:43-54).
@@ -23,6 +24,7 @@ struct G {
   Var add(Var x, Var y) { return map2(b, ScalarOp::Add, x, y); }
   Var mul(Var x, Var y) { return map2(b, ScalarOp::Mul, x, y); }
   Var div(Var x, Var y) { return map2(b, ScalarOp::Div, x, y); }
+  Var sub(Var x, Var y) { return map2(b, ScalarOp::Sub, x, y); }
   Var neg(Var x) { return map1(b, ScalarOp::Neg, x); }
 
   // tensors.rs:27-45 (squeeze / unsqueeze via reshape)
@@ -117,6 +119,52 @@ struct G {
     inv_freq = broadcast(b, sh2, inv_freq);
     Var fac = constant_f32(b, factor, sh2);
     inv_freq = div(inv_freq, fac);
+    Var pos = arange(b, seq_len);
+    pos = cast(b, pos, F32());
+    pos = reshape(b, pack(b, {seq_len, N(1)}), pos);
+    pos = broadcast(b, shape(b, inv_freq), pos);
+    pos = mul(pos, inv_freq);
+    Var c = map1(b, ScalarOp::Cos, pos);
+    Var s = map1(b, ScalarOp::Sin, pos);
+    c = concat(b, N(1), c, c);
+    s = concat(b, N(1), s, s);
+    return {c, s};
+  }
+
+  // rope.rs:232-314: the "llama3" frequency rescaling (long wavelengths divided by `factor`, a smooth blend in between)
+  std::pair<Var, Var> rope_tables_llama3(float theta, Var seq_len, int64_t head_dim) {
+    int64_t half = head_dim / 2;
+    Var f = arange(b, N(half));
+    f = cast(b, f, F32());
+    Var sh = shape(b, f);
+    Var two = constant_f32(b, 2.0f / (float)head_dim, sh);
+    f = mul(f, two);
+    Var th = constant_f32(b, theta, sh);
+    Var freq = map2(b, ScalarOp::Pow, th, f);
+    Var inv_freq = inverse(b, freq);
+    const float orig = (float)cfg.rope_original_max_position;
+    sh = shape(b, inv_freq);
+    Var low_wl = constant_f32(b, orig / cfg.rope_low_freq_factor, sh);
+    Var high_wl = constant_f32(b, orig / cfg.rope_high_freq_factor, sh);
+    Var factor = constant_f32(b, cfg.rope_factor, sh);
+    Var low_ff = constant_f32(b, cfg.rope_low_freq_factor, sh);
+    Var high_ff = constant_f32(b, cfg.rope_high_freq_factor, sh);
+    Var old_len = constant_f32(b, orig, sh);
+    Var pi_2 = constant_f32(b, 2.0f * 3.14159265358979323846f, sh);
+    Var wavelen = div(pi_2, inv_freq);
+    Var low_mask = cast(b, map2(b, ScalarOp::LT, low_wl, wavelen), F32());
+    Var one = constant_f32(b, 1.0f, sh);
+    Var scaled = div(inv_freq, factor);
+    inv_freq = add(mul(low_mask, scaled), mul(sub(one, low_mask), inv_freq));
+    Var high_mask = cast(b, map2(b, ScalarOp::LT, wavelen, high_wl), F32());
+    Var not_high = sub(one, high_mask);
+    Var not_low = sub(one, low_mask);
+    Var mid_mask = mul(not_high, not_low);
+    Var smooth = div(sub(div(old_len, wavelen), low_ff), sub(high_ff, low_ff));
+    Var smoothed = add(mul(smooth, inv_freq), div(mul(sub(one, smooth), inv_freq), factor));
+    inv_freq = add(mul(mid_mask, smoothed), mul(sub(one, mid_mask), inv_freq));
+    Var sh2 = pack(b, {seq_len, N(half)});
+    inv_freq = broadcast(b, sh2, inv_freq);
     Var pos = arange(b, seq_len);
     pos = cast(b, pos, F32());
     pos = reshape(b, pack(b, {seq_len, N(1)}), pos);
@@ -250,7 +298,9 @@ Term build_llama_term(const LlamaConfig& cfg, bool tap_logits) {
   auto kd = unpack(b, shape(b, in_k), 5);
   Var mask = g.causal_mask(bsd[1], kd[3]);
   // forward_embeddings (llama.rs:166-228): Cache::init = RoPE tables + per-layer KV slices
-  auto tables = g.rope_tables_default(cfg.rope_theta, max_positions, cfg.head_dim(), 1.0f);
+  // init_rope_tables (rope.rs:8-60): llama3 scaling when the config carries it, else the default tables
+  auto tables = cfg.rope_scaling_type == 1 ? g.rope_tables_llama3(cfg.rope_theta, max_positions, cfg.head_dim())
+                                           : g.rope_tables_default(cfg.rope_theta, max_positions, cfg.head_dim(), 1.0f);
   g.kv_init(in_k, in_v);
   auto kd2 = unpack(b, shape(b, in_k), 5);
   Var pos = kd2[3];

@@ -1406,13 +1406,34 @@ __global__ void __launch_bounds__(256) add_inplace_kernel(T* __restrict__ x, con
 
 // RoPE tables, the f32 op sequence of rope_tables_default (helpers/rope.rs:65-104):
 // f = i * (2/HD); freq = pow(theta, f); inv = 1/freq; inv = inv / 1.0; ang = pos * inv; cos, sin.
-__global__ void rope_table_kernel(float* cos_t, float* sin_t, int P, int half, float theta, float two_over_d) {
+// With llama3 scaling (rope.rs:232-310) inv is rescaled first, again op for op: wavelengths above
+// original/low_freq_factor are divided by `factor`, those between the two thresholds blend smoothly.
+struct RopeScalingArgs {
+  int type;   // 0 none, 1 llama3
+  float factor, low_freq_factor, high_freq_factor, original_max_position;
+};
+__device__ __forceinline__ float rope_inv_freq(int i, float theta, float two_over_d, const RopeScalingArgs& rs) {
+  const float f = (float)i * two_over_d;
+  float inv = 1.0f / powf(theta, f);
+  if (rs.type == 1) {
+    const float low_wl = rs.original_max_position / rs.low_freq_factor, high_wl = rs.original_max_position / rs.high_freq_factor;
+    const float wavelen = (2.0f * 3.14159265358979323846f) / inv;
+    const float low_mask = low_wl < wavelen ? 1.0f : 0.0f;
+    inv = low_mask * (inv / rs.factor) + (1.0f - low_mask) * inv;
+    const float high_mask = wavelen < high_wl ? 1.0f : 0.0f;
+    const float mid_mask = (1.0f - high_mask) * (1.0f - low_mask);
+    const float smooth = (rs.original_max_position / wavelen - rs.low_freq_factor) / (rs.high_freq_factor - rs.low_freq_factor);
+    const float smoothed = smooth * inv + ((1.0f - smooth) * inv) / rs.factor;
+    inv = mid_mask * smoothed + (1.0f - mid_mask) * inv;
+  } else {
+    inv = inv / 1.0f;
+  }
+  return inv;
+}
+__global__ void rope_table_kernel(float* cos_t, float* sin_t, int P, int half, float theta, float two_over_d, RopeScalingArgs rs) {
   for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < P * half; e += gridDim.x * blockDim.x) {
     int pos = e / half, i = e - pos * half;
-    float f = (float)i * two_over_d;
-    float inv = 1.0f / powf(theta, f);
-    inv = inv / 1.0f;
-    float ang = (float)pos * inv;
+    float ang = (float)pos * rope_inv_freq(i, theta, two_over_d, rs);
     cos_t[e] = cosf(ang);
     sin_t[e] = sinf(ang);
   }

@@ -50,7 +50,9 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(View4 bt, const T* __res
   A += oa;
   B += ob;
   C += (long long)blockIdx.z * M * N;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  // output tiles are flattened onto grid.x (grid.y stops at 65535 tiles: 4 M rows)
+  const int ntn = (N + BN - 1) / BN;
+  const int m0 = (int)(blockIdx.x / ntn) * BM, n0 = (int)(blockIdx.x % ntn) * BN;
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads, each 4 x 4 outputs
   float acc[4][4];
@@ -205,7 +207,7 @@ bool launch_gemv_t(const View4& bt, long long batch, const void* A, const void* 
 template <class T>
 void launch_simt_t(const View4& bt, long long batch, const void* A, const void* B, void* C, int M, int N, int K,
                    long long sam, long long sak, long long sbk, long long sbn, cudaStream_t st) {
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, (unsigned)batch);
+  dim3 grid((unsigned)((long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM)), 1, (unsigned)batch);   // < 2^31 tiles: checked by the caller
   gemm_simt_kernel<T><<<grid, 256, 0, st>>>(bt, (const T*)A, (const T*)B, (T*)C, M, N, K, sam, sak, sbk, sbn);
 }
 }  // namespace

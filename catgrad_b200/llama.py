@@ -31,15 +31,28 @@ class LlamaConfig:
     rope_theta: float = 10000.0
     rms_norm_eps: float = 1e-5
     tie_word_embeddings: bool = False
+    # rope_scaling block of config.json (config.rs:10-18): None, or a dict with rope_type "llama3", factor,
+    # low_freq_factor, high_freq_factor, original_max_position_embeddings (Llama-3.1 / 3.2 checkpoints carry it)
+    rope_scaling: dict = None
 
     @property
     def head_dim(self):
         return self.hidden_size // self.num_attention_heads
 
     def to_struct(self):
+        rs = self.rope_scaling
+        if rs is None:
+            scaling = (0, 1.0, 1.0, 1.0, 0)
+        else:
+            kind = rs.get("rope_type", rs.get("type"))
+            if kind != "llama3":
+                raise ValueError(f"rope_scaling type {kind!r} is not implemented (only 'llama3'; helpers/rope.rs:14-60 also "
+                                 "knows yarn and longrope)")
+            scaling = (1, float(rs["factor"]), float(rs["low_freq_factor"]), float(rs["high_freq_factor"]),
+                       int(rs["original_max_position_embeddings"]))
         return _ffi.LlamaConfigStruct(self.hidden_size, self.intermediate_size, self.num_hidden_layers,
                                       self.num_attention_heads, self.num_key_value_heads, self.vocab_size,
-                                      self.rope_theta, self.rms_norm_eps, int(self.tie_word_embeddings))
+                                      self.rope_theta, self.rms_norm_eps, int(self.tie_word_embeddings), *scaling)
 
     def param_shapes(self):
         """Parameter keys (HF layout [out, in]) in the order the weights are drawn."""

@@ -143,11 +143,17 @@ void cg_term_free(cg_term* t);
 /* counts[0..3] = nodes, edges, tensor-op edges, layers of the parallel SSA order (ssa/mod.rs:24-76) */
 cg_status cg_term_stats(const cg_term* t, uint64_t counts[4]);
 
-/* LlamaConfig (catgrad-llm-models/src/models/llama.rs:9-27), fields the Llama term reads. */
+/* LlamaConfig (catgrad-llm-models/src/models/llama.rs:9-27), fields the Llama term reads; rope_scaling
+ * (config.rs:10-18) selects the RoPE table builder as helpers/rope.rs:8-60 does: absent -> rope_tables_default,
+ * "llama3" -> rope_tables_llama3 (rope.rs:232-310).  Yarn and longrope are not implemented: a config that
+ * carries them must not be passed with rope_scaling_type 0. */
 typedef struct {
   uint64_t hidden_size, intermediate_size, num_hidden_layers, num_attention_heads, num_key_value_heads, vocab_size;
   float rope_theta, rms_norm_eps;
   int tie_word_embeddings;
+  int rope_scaling_type;                 /* 0: no rope_scaling block; 1: "llama3" */
+  float rope_factor, rope_low_freq_factor, rope_high_freq_factor;
+  uint64_t rope_original_max_position;   /* original_max_position_embeddings of the scaling block */
 } cg_llama_config;
 /* The term of LlamaModel::def (llama.rs:393-401): inputs x [B,S] u32, in_k, in_v [L,B,Hkv,T,D],
  * max_positions (nat); outputs ids [B,S,1] u32, out_k, out_v [L,B,Hkv,T+S,D].  tap_logits != 0 adds the

@@ -7,10 +7,26 @@ def rmsnorm(x, g, eps):
     return x / np.sqrt((x * x).mean(-1, keepdims=True) + eps) * g
 
 
-def rope(x, pos0, theta):
+def llama3_inv_freq(inv, scaling):
+    """The frequency rescaling of Llama 3.1 (as published with the model: frequencies whose wavelength exceeds
+    original/low_freq_factor are divided by `factor`, those below original/high_freq_factor are kept, linear blend of
+    the two in between), in float64."""
+    factor, lo, hi = scaling["factor"], scaling["low_freq_factor"], scaling["high_freq_factor"]
+    orig = scaling["original_max_position_embeddings"]
+    wavelen = 2 * np.pi / inv
+    smooth = (orig / wavelen - lo) / (hi - lo)
+    blended = (1 - smooth) * inv / factor + smooth * inv
+    out = np.where(wavelen > orig / lo, inv / factor, inv)
+    mid = (wavelen <= orig / lo) & (wavelen >= orig / hi)
+    return np.where(mid, blended, out)
+
+
+def rope(x, pos0, theta, scaling=None):
     # x [B, h, S, D]; rotate-half convention
     d = x.shape[-1]
     inv = 1.0 / theta ** (np.arange(d // 2, dtype=np.float64) * 2.0 / d)
+    if scaling is not None:
+        inv = llama3_inv_freq(inv, scaling)
     ang = (pos0 + np.arange(x.shape[2], dtype=np.float64))[:, None] * inv[None, :]
     c = np.concatenate([np.cos(ang), np.cos(ang)], -1)
     s = np.concatenate([np.sin(ang), np.sin(ang)], -1)
@@ -32,7 +48,8 @@ def forward(cfg, w, ids, cache=None):
         q = (h @ w[p + "self_attn.q_proj.weight"].T).reshape(b, s, nh, hd).transpose(0, 2, 1, 3)
         k = (h @ w[p + "self_attn.k_proj.weight"].T).reshape(b, s, nkv, hd).transpose(0, 2, 1, 3)
         v = (h @ w[p + "self_attn.v_proj.weight"].T).reshape(b, s, nkv, hd).transpose(0, 2, 1, 3)
-        q, k = rope(q, pos0, cfg.rope_theta), rope(k, pos0, cfg.rope_theta)
+        scaling = getattr(cfg, "rope_scaling", None)
+        q, k = rope(q, pos0, cfg.rope_theta, scaling), rope(k, pos0, cfg.rope_theta, scaling)
         if cache is not None:
             k = np.concatenate([cache[i][0], k], 2)
             v = np.concatenate([cache[i][1], v], 2)

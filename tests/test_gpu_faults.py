@@ -71,3 +71,19 @@ def test_allocator_reuses_blocks_and_reports_oom(gpu):
     assert e.value.status == cb.Status.OOM
     assert capped.to_numpy(small).sum() == 0        # the context survives the refusal
     capped.close()
+
+
+def test_matmul_refuses_dimensions_the_kernels_cannot_index(gpu):
+    """A 2^31-row operand (a broadcast view: no memory behind it) is refused on the host before anything is allocated or
+    launched; a tall product just below the old 65535-row-tile limit of grid.y still computes."""
+    one = gpu.from_numpy(np.ones((1, 8), np.float32))
+    huge = gpu.broadcast(one, (1 << 31, 8))
+    w = gpu.from_numpy(np.ones((8, 4), np.float32))
+    with pytest.raises(cb.BackendError) as ei:
+        gpu.matmul(huge, w)
+    assert ei.value.status == cb.Status.INVALID_ARG
+    tall = gpu.broadcast(one, (70000 * 64, 8))          # 70000 row tiles: beyond what grid.y could hold
+    y = gpu.matmul(gpu.cast(tall, cb.Dtype.F16), gpu.cast(w, cb.Dtype.F16))      # f16 takes the SIMT kernel
+    assert y.shape == (70000 * 64, 4)
+    v = gpu.to_numpy(gpu.slice(y, 0, 70000 * 64 - 3, 3)).astype(np.float32)
+    np.testing.assert_array_equal(v, np.full((3, 4), 8.0, np.float32))

@@ -375,3 +375,24 @@ def test_device_runner_shards_sequences_over_replicas(gpu):
     with pytest.raises(cb.BackendError):
         r.generate(np.zeros((10, 10), np.uint32), 2)     # 4 sequences on a replica sized for 3
     r.close()
+
+
+def test_llama3_rope_scaling_on_the_gpu(oracle, gpu):
+    """rope_scaling "llama3": the fused runner's tables (rope_table_kernel) and the op-by-op term on the GPU against the
+    oracle's term, f32, positions up to 300 where scaled and unscaled tables differ widely."""
+    scaling = {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+               "original_max_position_embeddings": 8192}
+    cfg = cb.LlamaConfig(256, 512, 2, 4, 2, 1024, rope_theta=500000.0, tie_word_embeddings=True, rope_scaling=scaling)
+    w = cb.random_weights(cfg, 5)
+    ids = np.random.default_rng(6).integers(0, cfg.vocab_size, size=(1, 300), dtype=np.uint32)
+    term_o = cb.llama_term(oracle, cfg, tap_logits=True)
+    ref_ids, ref_logits = cb.generate_with_interpreter(oracle, term_o, cb.upload_weights(oracle, w, Dtype.F32), cfg, ids, 3,
+                                                       Dtype.F32, 310, tap=True)
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    runner = cb.LlamaRunner(gpu, cfg, params, Dtype.F32, max_batch=1, max_positions=310)
+    np.testing.assert_array_equal(runner.generate(ids, 3), ref_ids)
+    assert helpers.rel_err(runner.last_logits()[0], ref_logits[2][0, -1]) <= REL_F32
+    term_g = cb.llama_term(gpu, cfg, tap_logits=True)
+    out, logits = cb.generate_with_interpreter(gpu, term_g, params, cfg, ids, 2, Dtype.F32, 310, tap=True)
+    np.testing.assert_array_equal(out, ref_ids[:, :2])
+    assert helpers.rel_err(logits[1][0, -1], ref_logits[1][0, -1]) <= REL_F32

@@ -216,3 +216,33 @@ def test_probe_prints_only_when_asked_and_format_names_dtype_shape_values(oracle
     assert "u32" in oracle.format_tensor(oracle.from_numpy(np.arange(5, dtype=np.uint32)))
     s = oracle.format_tensor(oracle.from_numpy(np.array([0.5, 2.0], np.float32), cb.Dtype.BF16))
     assert "bf16" in s and "0.5" in s and "2" in s
+
+
+LLAMA3_SCALING = {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                  "original_max_position_embeddings": 8192}
+
+
+def test_llama3_rope_scaling_term_equals_textbook_llama(oracle):
+    """rope_scaling "llama3" (helpers/rope.rs:232-310; what Llama-3.1/3.2 checkpoints configure): the term's tables against
+    the published formula in float64.  Head dim 64 with theta 5e5 has frequencies in all three bands (kept, blended,
+    divided by 32), and positions in the hundreds make the difference to unscaled tables large."""
+    cfg = cb.LlamaConfig(128, 256, 2, 2, 1, 512, rope_theta=500000.0, tie_word_embeddings=True, rope_scaling=LLAMA3_SCALING)
+    inv = 1.0 / 500000.0 ** (np.arange(32) * 2.0 / 64)
+    scaled = llama_numpy.llama3_inv_freq(inv, LLAMA3_SCALING)
+    ratio = scaled / inv
+    assert (ratio == 1.0).any() and np.isclose(ratio, 1 / 32).any() and ((ratio > 1 / 32 + 1e-3) & (ratio < 1 - 1e-3)).any()
+    w = cb.random_weights(cfg, 5)
+    ids = np.random.default_rng(6).integers(0, 512, size=(2, 300), dtype=np.uint32)
+    term = cb.llama_term(oracle, cfg, tap_logits=True)
+    params = cb.upload_weights(oracle, w, Dtype.F32)
+    out, logits = cb.generate_with_interpreter(oracle, term, params, cfg, ids, 2, Dtype.F32, 320, tap=True)
+    lg, cache = llama_numpy.forward(cfg, w, ids.astype(np.int64))
+    assert helpers.rel_err(logits[0][:, -1], lg[:, -1]) < 2e-5
+    lg2, _ = llama_numpy.forward(cfg, w, out[:, :1].astype(np.int64), cache)
+    assert helpers.rel_err(logits[1][:, -1], lg2[:, -1]) < 2e-5
+    # and the scaling matters at these positions: the unscaled model is far away
+    plain = cb.LlamaConfig(128, 256, 2, 2, 1, 512, rope_theta=500000.0, tie_word_embeddings=True)
+    lg0, _ = llama_numpy.forward(plain, w, ids.astype(np.int64))
+    assert helpers.rel_err(lg0[:, -1], lg[:, -1]) > 1e-4       # ten times the agreement asked for above
+    with pytest.raises(ValueError):
+        cb.LlamaConfig(128, 256, 2, 2, 1, 512, rope_scaling={"rope_type": "yarn", "factor": 4.0}).to_struct()
