@@ -198,29 +198,36 @@ def ids_digest(ids):
     return rows, hashlib.sha1("".join(rows).encode()).hexdigest()[:16]
 
 
-def interpreter_path_tok_s(be, cfg, params, prompt_len=64, steps=4):
-    """The same model through the op-by-op interpreter (cg_interp_run on the Llama term, the route catgrad's own
-    `interpreter.run(term)` takes): one kernel per IR edge, the KV cache threaded as a value and re-stacked every
-    step (helpers/cache.rs:13-75).  Returns decode tokens/s and launches per step."""
-    term = cb.llama_term(be, cfg)
-    interp = cb.Interpreter(be, params)
+def interpreter_path_tok_s(be, cfg, params, prompt_len=64, steps=8):
+    """The same model through cg_interp_run on the Llama term, the route catgrad's own `interpreter.run(term)` takes,
+    with the KV cache threaded as a value (helpers/cache.rs:13-75), twice: op by op (one kernel per IR edge, the cache
+    re-stacked every step) and with the term recognised and executed as the fused plan (the default)."""
     ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(1, prompt_len), dtype=np.uint32)
-    in_k, in_v = cb.empty_state_cache(be, cfg, 1, cb.Dtype.BF16)
-    x = ids
-    times, launches = [], []
-    for i in range(steps + 2):
-        stats0 = be.stats()[3]
-        t0 = time.perf_counter()
-        r = interp.run(term, [be.ndarray_from_vec_u32(x, x.shape), in_k, in_v, prompt_len + steps + 3])
-        last = be.to_numpy(r[0])[:, -1, 0]
-        times.append(time.perf_counter() - t0)
-        launches.append(be.stats()[3] - stats0)
-        in_k, in_v = r[1], r[2]
-        x = last.reshape(1, 1).astype(np.uint32)
-    dec = times[2:]                                      # skip the prefill call and the first decode call
-    return {"decode_tok_s": len(dec) / sum(dec), "ms_per_step": 1e3 * sum(dec) / len(dec), "launches_per_step": int(launches[-1]),
-            "prompt_len": prompt_len, "steps": steps,
-            "how": "cg_llama_term through cg_interp_run, one kernel per IR edge, KV cache re-stacked per step"}
+    res = {"prompt_len": prompt_len, "steps": steps}
+    for name, planning in (("op_by_op", 0), ("planned", 1)):
+        be._ns.interp_set_planning(planning)
+        try:
+            term = cb.llama_term(be, cfg)
+            interp = cb.Interpreter(be, params)
+            in_k, in_v = cb.empty_state_cache(be, cfg, 1, cb.Dtype.BF16)
+            x = ids
+            times, launches = [], []
+            for i in range(steps + 2):
+                stats0 = be.stats()[3]
+                t0 = time.perf_counter()
+                r = interp.run(term, [be.ndarray_from_vec_u32(x, x.shape), in_k, in_v, prompt_len + steps + 3])
+                last = be.to_numpy(r[0])[:, -1, 0]
+                times.append(time.perf_counter() - t0)
+                launches.append(be.stats()[3] - stats0)
+                in_k, in_v = r[1], r[2]
+                x = last.reshape(1, 1).astype(np.uint32)
+            dec = times[2:]                              # skip the prefill call and the first decode call
+            res[name] = {"decode_tok_s": len(dec) / sum(dec), "ms_per_step": 1e3 * sum(dec) / len(dec),
+                         "backend_calls_per_step": int(launches[-1]), "plan_state": term.plan_state}
+            del in_k, in_v, r, term, interp
+        finally:
+            be._ns.interp_set_planning(1)
+    return res
 
 
 def cpu_baseline_sample(cfg, weights_f32, prompt_len=8, steps=2, batch=1):

@@ -133,6 +133,8 @@ CUDA_ONLY = {
     "llama_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p]),
     "llama_decode": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
     "llama_last_logits": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64]),
+    "term_plan_state": (C.c_int, [C.c_void_p]),
+    "interp_set_planning": (None, [C.c_int]),
     "llama_set_persistent": (C.c_int, [C.c_void_p, C.c_int]),
     "llama_persistent_active": (C.c_int, [C.c_void_p]),
     "llama_context_len": (C.c_uint64, [C.c_void_p]),

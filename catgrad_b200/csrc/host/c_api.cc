@@ -59,6 +59,10 @@ std::string Backend::format_tensor(const Tensor& x) {
 }
 }  // namespace cg
 
+namespace cg {
+PlanHook g_plan_hook = nullptr;
+}
+
 using namespace cg;
 
 namespace {
@@ -407,6 +411,7 @@ int API(params_set)(cg_params* p, const char* path, const cg_tensor* t) {
   CG_API_BEGIN
   CG_CHECK(p && path, ERR_BAD_HANDLE, "null argument");
   p->p[path] = T(t);
+  ++p->version;
   CG_API_END(nullptr)
 }
 
@@ -434,8 +439,11 @@ int API(interp_run)(cg_ctx* c, const cg_term* term, const cg_params* params, con
       default: throw Error(ERR_INVALID_ARG, "bad value kind");
     }
   }
-  Interpreter interp(&BE(c), params ? &params->p : nullptr);
-  std::vector<Value> out = interp.run(term->t, std::move(in));
+  std::vector<Value> out;
+  if (!(g_plan_hook && params && g_plan_hook(c, term, params, in, out))) {
+    Interpreter interp(&BE(c), params ? &params->p : nullptr);
+    out = interp.run(term->t, std::move(in));
+  }
   CG_CHECK((int)out.size() <= cap_outputs, ERR_INVALID_ARG, "output array too small");
   *n_outputs = (int)out.size();
   for (size_t i = 0; i < out.size(); ++i) {

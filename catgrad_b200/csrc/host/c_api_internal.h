@@ -17,6 +17,8 @@ struct cg_tensor {
 };
 struct cg_term {
   cg::Term t;
+  // Slot for a compiled plan of this term (filled by the CUDA library on the term's first run, freed with the term).
+  mutable std::shared_ptr<void> plan;
 };
 struct cg_builder {
   cg::Builder b;
@@ -24,6 +26,7 @@ struct cg_builder {
 };
 struct cg_params {
   cg::Parameters p;
+  uint64_t version = 0;   // bumped by every cg_params_set: plans built from older contents are rebuilt
 };
 
 namespace cg {
@@ -31,6 +34,10 @@ namespace cg {
 Backend* make_backend(int device);
 // Records a failure on the context (or thread-locally when ctx is null) and returns its status.
 int record_error(cg_ctx* ctx, int status, const std::string& msg);
+// Term -> plan hook of cg_interp_run: when set (the CUDA library sets it) it is offered every run first; it returns
+// true after filling `out` if it executed the term as a compiled plan, false to let the op-by-op evaluator run it.
+using PlanHook = bool (*)(cg_ctx*, const cg_term*, const cg_params*, std::vector<Value>& in, std::vector<Value>& out);
+extern PlanHook g_plan_hook;
 }  // namespace cg
 
 // Wraps a C entry point body: exceptions become status codes.

@@ -13,6 +13,7 @@
 // Observable behaviour kept: ids of the last position per sequence; K/V contents; rounding points (see
 // llama_kernels.cuh).  The lm_head runs on the last position of each sequence only: the reference computes it
 // for all S positions (llama.rs:217-225) and its runner reads only the last element.
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -609,6 +610,28 @@ struct Plan {
            (unsigned*)m.ids_cur.raw(), (unsigned*)m.ids_out.raw(), ctx_len, ctx_len + 1, (int)B, (int)S,
            (int)m.out_cap_steps);
     launched("advance");
+  }
+
+  // Greedy ids of ALL M = B*S positions from the residual stream the last step left in x (final norm, lm_head,
+  // argmax per row: llama.rs:204-225 as the term types its output, [B,S,1]); rows are taken 2048 at a time so that the
+  // logits buffer stays at 2048 x vocabulary.
+  void all_position_ids(int64_t M, unsigned* out) {
+    const LlamaConfig& c = m.cfg;
+    const int64_t H = c.hidden_size, V = c.vocab_size, CH = std::min<int64_t>(M, 2048);
+    Tensor xn = m.be->empty({CH, H}, m.dt), lg = m.be->empty({CH, V}, m.dt);
+    Tensor part = m.be->empty({CH * m.argmax_chunks * 2}, Dtype::U32);
+    const T* x = (const T*)m.x.raw();
+    for (int64_t r0 = 0; r0 < M; r0 += CH) {
+      const int64_t rows = std::min(CH, M - r0);
+      rmsnorm(x + r0 * H, m.final_norm, xn.raw(), rows, H, 1, 0);
+      gemm(xn.raw(), H, m.head, lg.raw(), rows, V, H);
+      launch(cgk::argmax_partial_kernel<T>, dim3((unsigned)m.argmax_chunks, (unsigned)rows), dim3(256), 0, (const T*)lg.raw(), (long long)V,
+             (int)V, (unsigned long long*)part.raw());
+      launched("argmax_partial");
+      cgk::ids_from_partials_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const unsigned long long*)part.raw(), m.argmax_chunks, (int)rows,
+                                                                              out + r0);
+      launched("ids_from_partials");
+    }
   }
 
   // round sqrt(hd) through T like `cast(constant(sqrt(hd)), dtype(attn))` (llama.rs:331-332)
@@ -1287,3 +1310,225 @@ int cg_flush_l2(cg_ctx* ctx, uint64_t bytes) {
 }
 
 }  // extern "C"
+
+// ---- term -> plan: the Llama term through cg_interp_run on the fused runner ---------------------------------------
+// catgrad reaches a backend only through `interpreter.run(term, inputs)` per token (examples/llama/main.rs:955-1043;
+// interpreter.rs:29-37), one Backend call per tensor edge.  On the first run of a term, this hook checks whether the
+// term is, edge for edge, the term `LlamaModel` builds (llama_term.cc, i.e. llama.rs:144-401) for the configuration its
+// parameters and constants imply.  If so, this and every later run of the term execute as the fused plan: the KV cache
+// stays in the runner's device buffers and is appended in place; the `out_k`/`out_v` values handed back are strided
+// views of those buffers ([L,B,Hkv,T+S,D] over the [L,B,Hkv,P,D] allocation), and when the caller threads them back
+// in as `in_k`/`in_v` (helpers/cache.rs:13-75) they are recognised by their storage, so nothing is copied or
+// re-stacked.  The ids output has the term's shape [B,S,1] (all positions).  Anything else - a term that differs in a
+// single edge, logits tapped as a fourth output, a cache that is not the runner's own - runs op by op as before.
+namespace {
+
+struct LlamaPlan {
+  bool tried = false, matched = false;
+  LlamaConfig cfg;
+  struct Slot {
+    const cg_params* params = nullptr;
+    uint64_t version = 0;
+    cg_ctx* ctx = nullptr;
+    int64_t batch = 0, positions = 0;
+    cg_llama* model = nullptr;
+  };
+  std::vector<Slot> slots;
+  ~LlamaPlan() {
+    for (auto& s : slots) cg_llama_free(s.model);
+  }
+};
+
+bool same_term(const Term& a, const Term& b) {
+  if (a.nodes != b.nodes || a.sources != b.sources || a.targets != b.targets || a.edges.size() != b.edges.size()) return false;
+  for (size_t i = 0; i < a.edges.size(); ++i) {
+    const Edge &x = a.edges[i], &y = b.edges[i];
+    if (x.sources != y.sources || x.targets != y.targets || x.op.kind != y.op.kind) return false;
+    switch (x.op.kind) {
+      case OpKind::Map: if (x.op.sop != y.op.sop) return false; break;
+      case OpKind::NatConstant: if (x.op.nat != y.op.nat) return false; break;
+      case OpKind::DtypeConstant: if (x.op.dtype != y.op.dtype) return false; break;
+      case OpKind::ScalarF32: if (std::memcmp(&x.op.f32, &y.op.f32, 4) != 0) return false; break;
+      case OpKind::ScalarU32: if (x.op.u32 != y.op.u32) return false; break;
+      case OpKind::Load: case OpKind::Probe: if (x.op.str != y.op.str) return false; break;
+      case OpKind::If: return false;
+      default: break;
+    }
+  }
+  return true;
+}
+
+// The configuration the parameters' shapes and the term's constants imply, verified by rebuilding the term from it.
+bool match_llama(const Term& t, const Parameters& p, LlamaConfig& out) {
+  if (t.sources.size() != 4 || t.targets.size() != 3) return false;
+  auto find = [&](const std::string& k) -> const Tensor* {
+    auto it = p.find(k);
+    return it == p.end() ? nullptr : &it->second;
+  };
+  const Tensor* emb = find("model.embed_tokens.weight");
+  const Tensor* q = find("model.layers.0.self_attn.q_proj.weight");
+  const Tensor* k = find("model.layers.0.self_attn.k_proj.weight");
+  const Tensor* gate = find("model.layers.0.mlp.gate_proj.weight");
+  if (!emb || !q || !k || !gate || emb->rank() != 2 || q->rank() != 2 || k->rank() != 2 || gate->rank() != 2) return false;
+  LlamaConfig c;
+  c.vocab_size = emb->shape[0];
+  c.hidden_size = emb->shape[1];
+  c.intermediate_size = gate->shape[0];
+  while (find("model.layers." + std::to_string(c.num_hidden_layers) + ".self_attn.q_proj.weight")) ++c.num_hidden_layers;
+  c.tie_word_embeddings = find("lm_head.weight") ? 0 : 1;
+  if (q->shape[0] != c.hidden_size) return false;   // head_dim = hidden / heads (llama.rs:54-56): q_proj is square
+  // float constants of the term in edge order: eps is the small positive one, theta the large one; a 2 pi marks
+  // llama3 RoPE scaling, whose six parameters are the constants just before it (rope.rs:252-268)
+  std::vector<float> consts;
+  for (auto& e : t.edges)
+    if (e.op.kind == OpKind::ScalarF32) consts.push_back(e.op.f32);
+  std::vector<float> eps_c, theta_c;
+  for (float v : consts) {
+    if (v > 0.f && v < 1e-3f && std::find(eps_c.begin(), eps_c.end(), v) == eps_c.end()) eps_c.push_back(v);
+    if (v >= 100.f && std::isfinite(v) && std::find(theta_c.begin(), theta_c.end(), v) == theta_c.end()) theta_c.push_back(v);
+  }
+  const float two_pi = 2.0f * 3.14159265358979323846f;
+  size_t pi_at = consts.size();
+  for (size_t i = 0; i < consts.size(); ++i)
+    if (consts[i] == two_pi) { pi_at = i; break; }
+  for (int64_t hd : {64, 128}) {
+    if (c.hidden_size % hd || k->shape[0] % hd) continue;
+    c.num_attention_heads = c.hidden_size / hd;
+    c.num_key_value_heads = k->shape[0] / hd;
+    if (c.num_key_value_heads == 0 || c.num_attention_heads % c.num_key_value_heads) continue;
+    for (float eps : eps_c) {
+      for (float theta : theta_c) {
+        c.rms_norm_eps = eps;
+        c.rope_theta = theta;
+        for (int scaling = 0; scaling < 2; ++scaling) {
+          c.rope_scaling_type = scaling;
+          if (scaling == 1) {
+            if (pi_at < 6 || pi_at >= consts.size()) continue;
+            c.rope_factor = consts[pi_at - 4];
+            c.rope_low_freq_factor = consts[pi_at - 3];
+            c.rope_high_freq_factor = consts[pi_at - 2];
+            c.rope_original_max_position = (int64_t)consts[pi_at - 1];
+            if (!(c.rope_factor > 0.f) || !(c.rope_low_freq_factor > 0.f) || c.rope_high_freq_factor == c.rope_low_freq_factor ||
+                c.rope_original_max_position <= 0)
+              continue;
+          }
+          if (same_term(t, build_llama_term(c, false))) {
+            out = c;
+            return true;
+          }
+        }
+      }
+    }
+  }
+  return false;
+}
+
+std::atomic<bool> g_planning{true};
+
+bool llama_plan_hook(cg_ctx* ctx, const cg_term* term, const cg_params* params, std::vector<Value>& in, std::vector<Value>& out) {
+  if (!g_planning.load() || !ctx || !ctx->be || std::string(ctx->be->name()) != "b200") return false;
+  if (!term->plan) term->plan = std::make_shared<LlamaPlan>();
+  LlamaPlan& plan = *static_cast<LlamaPlan*>(term->plan.get());
+  if (!plan.tried) {
+    plan.tried = true;
+    plan.matched = match_llama(term->t, params->p, plan.cfg);
+  }
+  if (!plan.matched || in.size() != 4) return false;
+  if (in[0].kind != Value::TensorV || in[1].kind != Value::TensorV || in[2].kind != Value::TensorV || in[3].kind != Value::Nat) return false;
+  const Tensor &x = in[0].tensor, &ik = in[1].tensor, &iv = in[2].tensor;
+  const LlamaConfig& c = plan.cfg;
+  const int64_t hd = c.head_dim();
+  if (x.dt != Dtype::U32 || x.rank() != 2 || !x.is_contiguous() || ik.rank() != 5 || iv.rank() != 5 || ik.shape != iv.shape) return false;
+  const int64_t B = x.shape[0], S = x.shape[1], T = ik.shape[3], P = in[3].nat;
+  if (B < 1 || S < 1 || ik.shape[0] != c.num_hidden_layers || ik.shape[1] != B || ik.shape[2] != c.num_key_value_heads ||
+      ik.shape[4] != hd || T + S > P)
+    return false;
+  auto it0 = params->p.find("model.embed_tokens.weight");
+  if (it0 == params->p.end()) return false;
+  const Dtype dt = it0->second.dt;
+  if ((dt != Dtype::F32 && dt != Dtype::BF16) || ik.dt != dt || iv.dt != dt) return false;
+  // the runner for (parameters, batch, positions); rebuilt when the parameters were changed since
+  LlamaPlan::Slot* slot = nullptr;
+  for (auto& s : plan.slots)
+    if (s.params == params && s.ctx == ctx && s.batch == B && s.positions == P) slot = &s;
+  if (slot && slot->version != params->version) {
+    cg_llama_free(slot->model);
+    slot->model = nullptr;
+  }
+  if (!slot) {
+    plan.slots.push_back(LlamaPlan::Slot{params, params->version, ctx, B, P, nullptr});
+    slot = &plan.slots.back();
+  }
+  if (!slot->model) {
+    api_llama_config ac{};
+    ac.hidden_size = (uint64_t)c.hidden_size; ac.intermediate_size = (uint64_t)c.intermediate_size;
+    ac.num_hidden_layers = (uint64_t)c.num_hidden_layers; ac.num_attention_heads = (uint64_t)c.num_attention_heads;
+    ac.num_key_value_heads = (uint64_t)c.num_key_value_heads; ac.vocab_size = (uint64_t)c.vocab_size;
+    ac.rope_theta = c.rope_theta; ac.rms_norm_eps = c.rms_norm_eps; ac.tie_word_embeddings = c.tie_word_embeddings;
+    ac.rope_scaling_type = c.rope_scaling_type; ac.rope_factor = c.rope_factor; ac.rope_low_freq_factor = c.rope_low_freq_factor;
+    ac.rope_high_freq_factor = c.rope_high_freq_factor; ac.rope_original_max_position = (uint64_t)c.rope_original_max_position;
+    cg_llama* mm = nullptr;
+    if (create_runner(ctx, &ac, (int)dt, params, (uint64_t)B, (uint64_t)P, nullptr, 0, &mm) != 0) {
+      plan.matched = false;   // e.g. a parameter with an unexpected layout: leave this term to the evaluator for good
+      return false;
+    }
+    slot->model = mm;
+    slot->version = params->version;
+  }
+  cg_llama& m = *slot->model;
+  // the incoming cache: empty (a new sequence), or the runner's own buffers at its current length
+  if (T == 0) {
+    if (cg_llama_reset(&m, (uint64_t)B) != 0) return false;
+  } else {
+    const bool own = ik.st == m.kc.st && iv.st == m.vc.st && ik.offset == m.kc.offset && iv.offset == m.vc.offset &&
+                     ik.strides == m.kc.strides && iv.strides == m.vc.strides && T == m.host_ctx_len && m.batch == B;
+    if (!own) return false;
+  }
+  m.be->guard();
+  ensure_capacity(m, B, S);
+  if (m.out_cap_steps < 1) {
+    m.ids_out = m.be->zeros({m.max_batch}, Dtype::U32);
+    m.out_cap_steps = 1;
+  }
+  cudaStream_t st = m.be->stream();
+  void* ids_dst = S == 1 ? m.ids_cur.raw() : m.ids_in.raw();
+  CG_CUDA(cudaMemcpyAsync(ids_dst, x.raw(), (size_t)(B * S) * 4, cudaMemcpyDeviceToDevice, st));
+  CG_CUDA(cudaMemsetAsync((int*)m.words.raw() + 1, 0, 4, st));  // step_no = 0
+  run_step(m, (const unsigned*)ids_dst, B, S, /*allow_mega=*/true);
+  Tensor ids = m.be->empty({B, S, 1}, Dtype::U32);
+  if (S == 1) {
+    CG_CUDA(cudaMemcpyAsync(ids.raw(), m.ids_cur.raw(), (size_t)B * 4, cudaMemcpyDeviceToDevice, st));
+  } else if (m.dt == Dtype::BF16) {
+    Plan<__nv_bfloat16>(m).all_position_ids(B * S, (unsigned*)ids.raw());
+  } else {
+    Plan<float>(m).all_position_ids(B * S, (unsigned*)ids.raw());
+  }
+  auto cache_view = [&](const Tensor& full) {
+    Tensor v = full;
+    v.shape = {c.num_hidden_layers, B, c.num_key_value_heads, T + S, hd};
+    return v;   // strides of the [L, Bmax, Hkv, P, D] allocation: a view, nothing moves
+  };
+  out.clear();
+  out.push_back(Value::of_tensor(ids));
+  out.push_back(Value::of_tensor(cache_view(m.kc)));
+  out.push_back(Value::of_tensor(cache_view(m.vc)));
+  return true;
+}
+
+struct PlanHookInstaller {
+  PlanHookInstaller() { cg::g_plan_hook = &llama_plan_hook; }
+} g_plan_hook_installer;
+
+}  // namespace
+
+extern "C" {
+// 0: the term has not been run yet (or planning was off); 1: it was recognised and runs as the fused Llama plan;
+// 2: it was not recognised and runs op by op.
+int cg_term_plan_state(const cg_term* t) {
+  if (!t || !t->plan) return 0;
+  const LlamaPlan& p = *static_cast<const LlamaPlan*>(t->plan.get());
+  return !p.tried ? 0 : (p.matched ? 1 : 2);
+}
+// Process-wide switch of the term -> plan step of cg_interp_run (on by default); off forces op-by-op evaluation.
+void cg_interp_set_planning(int on) { g_planning.store(on != 0); }
+}

@@ -1472,6 +1472,26 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const T* __restrict
   }
 }
 
+// Stage 2 on its own: one warp per row reduces that row's partial keys to the index (used when the ids of ALL
+// positions are wanted, as the term's output is typed: llama.rs:217-225).
+__global__ void __launch_bounds__(256) ids_from_partials_kernel(const unsigned long long* __restrict__ partials, int chunks, int rows,
+                                                                unsigned* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  unsigned long long best = 0ull;
+  for (int c = lane; c < chunks; c += 32) {
+    unsigned long long k = partials[(long long)row * chunks + c];
+    best = k > best ? k : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if (lane == 0) out[row] = (unsigned)(best & 0xffffffffull);
+}
+
 // End of a step: stage 2 of the greedy pick, then the new ids become the next step's input, are recorded for
 // the host, and the context length advances.  One CTA; warp w handles rows w, w+8, ...
 __global__ void __launch_bounds__(256) advance_kernel(const unsigned long long* __restrict__ partials, int chunks,

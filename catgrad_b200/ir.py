@@ -87,6 +87,13 @@ class Term:
     def handle(self):
         return self._h
 
+    @property
+    def plan_state(self):
+        """0: not run yet; 1: cg_interp_run recognised it and runs it as the fused Llama plan; 2: it runs op by op.
+        Always 0 on a backend without the recogniser (the CPU oracle)."""
+        fn = getattr(self._be._ns, "term_plan_state", None)
+        return int(fn(self._h)) if fn is not None else 0
+
     def stats(self):
         """dict(nodes, edges, tensor_ops, layers)"""
         c = (C.c_uint64 * 4)()

@@ -180,6 +180,17 @@ typedef struct {
 cg_status cg_interp_run(cg_ctx*, const cg_term* term, const cg_params* params, const cg_value* inputs, int n_inputs,
                         cg_value* outputs, int cap_outputs, int* n_outputs);
 
+/* Term -> plan (B200 only).  cg_interp_run offers every term to a recogniser first: a term that is, edge for edge, the
+ * Llama term of llama.rs:144-401 for the configuration its parameters and constants imply runs as the fused plan
+ * below instead of one kernel per edge, with the KV cache kept in the runner's device buffers: the out_k / out_v values
+ * are strided views of them, recognised by their storage when the caller threads them back in (helpers/cache.rs:13-75),
+ * so nothing is copied or re-stacked; they stay valid until the term is run again with an empty cache.  Any other term
+ * (one edge of difference is enough), or a cache that is not the runner's own, is evaluated op by op.
+ * cg_term_plan_state: 0 not run yet, 1 runs as the fused plan, 2 runs op by op. */
+int cg_term_plan_state(const cg_term* t);
+/* Process-wide switch of the recogniser (on by default). */
+void cg_interp_set_planning(int on);
+
 /* ---- fused Llama runner (B200 only; not part of the trait) ---------------------------------
  * Executes the Llama term above as a fixed plan of fused kernels with a device-resident KV cache
  * instead of one kernel per IR edge.  It replaces the per-token `run_interpreter` loop of

@@ -396,3 +396,87 @@ def test_llama3_rope_scaling_on_the_gpu(oracle, gpu):
     out, logits = cb.generate_with_interpreter(gpu, term_g, params, cfg, ids, 2, Dtype.F32, 310, tap=True)
     np.testing.assert_array_equal(out, ref_ids[:, :2])
     assert helpers.rel_err(logits[1][0, -1], ref_logits[1][0, -1]) <= REL_F32
+
+
+# ---- term -> plan: the Llama term through cg_interp_run on the fused runner -------------------------------------
+def test_llama_term_through_the_interpreter_entry_point_runs_as_the_fused_plan(gpu, oracle_tiny):
+    """The route catgrad itself takes (interpreter.run(term) per token, the cache threaded as a value): the term is
+    recognised on its first run, ids are those of the oracle and of cg_llama_forward, the cache values handed back are
+    views of the runner's buffers (nothing is re-stacked), and far fewer kernels launch than one per edge."""
+    cfg, w, ids = tiny_inputs()
+    ref_ids, _ = oracle_tiny
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    term = cb.llama_term(gpu, cfg)
+    assert term.plan_state == 0
+    before = gpu.stats()[3]
+    out, _ = cb.generate_with_interpreter(gpu, term, params, cfg, ids, 33, Dtype.F32, 97)
+    assert term.plan_state == 1
+    np.testing.assert_array_equal(out, ref_ids)
+    runner = cb.LlamaRunner(gpu, cfg, params, Dtype.F32, max_batch=1, max_positions=97)
+    np.testing.assert_array_equal(out, runner.generate(ids, 33))
+    # op by op the same loop is ~300 backend calls per token; planned it is a few dozen launches of fused kernels,
+    # none of them through the per-edge entry points counted here
+    assert gpu.stats()[3] - before < 33 * 40
+    # one call by hand: ids of ALL positions come back ([B, S, 1], as the term types them), and the cache is a view
+    interp = cb.Interpreter(gpu, params)
+    k0, v0 = cb.empty_state_cache(gpu, cfg, 1, Dtype.F32)
+    res = interp.run(term, [gpu.ndarray_from_vec_u32(ids, ids.shape), k0, v0, 97])
+    all_ids, k1, v1 = res[0], res[1], res[2]
+    assert all_ids.shape == (1, 64, 1) and k1.shape == (cfg.num_hidden_layers, 1, cfg.num_key_value_heads, 64, cfg.head_dim)
+    assert not k1.is_contiguous and k1.strides[2] == 97 * cfg.head_dim        # [L, B, Hkv, P, D] allocation underneath
+    gpu._ns.interp_set_planning(0)
+    try:
+        slow = cb.Interpreter(gpu, params).run(cb.llama_term(gpu, cfg), [gpu.ndarray_from_vec_u32(ids, ids.shape), k0, v0, 97])
+    finally:
+        gpu._ns.interp_set_planning(1)
+    np.testing.assert_array_equal(gpu.to_numpy(all_ids), gpu.to_numpy(slow[0]))          # every position's id
+    assert helpers.rel_err(gpu.to_numpy(k1), gpu.to_numpy(slow[1])) <= REL_F32
+    assert helpers.rel_err(gpu.to_numpy(v1), gpu.to_numpy(slow[2])) <= REL_F32
+    # threading the views back in continues the same sequence in place
+    nxt = gpu.to_numpy(all_ids)[:, -1, 0].reshape(1, 1).astype(np.uint32)
+    res2 = interp.run(term, [gpu.ndarray_from_vec_u32(nxt, nxt.shape), k1, v1, 97])
+    assert res2[1].shape[3] == 65 and gpu.to_numpy(res2[0])[0, 0, 0] == ref_ids[0, 1]
+
+
+def test_terms_that_are_not_the_llama_term_fall_back_to_op_by_op(gpu, oracle):
+    """One edge of difference is enough: the term with its logits tapped as a fourth output, and a model whose head
+    dimension the fused runner does not support, run op by op and still agree with the oracle.  A cache that is not the
+    runner's own (here: one produced op by op) is also left to the evaluator."""
+    cfg, w, ids = tiny_inputs()
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    tapped = cb.llama_term(gpu, cfg, tap_logits=True)
+    out, logits = cb.generate_with_interpreter(gpu, tapped, params, cfg, ids[:, :20], 3, Dtype.F32, 32, tap=True)
+    assert tapped.plan_state == 2 and len(logits) == 3
+    term_o = cb.llama_term(oracle, cfg)
+    want, _ = cb.generate_with_interpreter(oracle, term_o, cb.upload_weights(oracle, w, Dtype.F32), cfg, ids[:, :20], 3, Dtype.F32, 32)
+    np.testing.assert_array_equal(out, want)
+    odd = cb.LlamaConfig(128, 256, 1, 4, 2, 512, rope_theta=10000.0)           # head_dim 32
+    w2 = cb.random_weights(odd, 2)
+    ids2 = np.random.default_rng(3).integers(0, 512, size=(1, 9), dtype=np.uint32)
+    t2 = cb.llama_term(gpu, odd)
+    got, _ = cb.generate_with_interpreter(gpu, t2, cb.upload_weights(gpu, w2, Dtype.F32), odd, ids2, 3, Dtype.F32, 16)
+    assert t2.plan_state == 2
+    want2, _ = cb.generate_with_interpreter(oracle, cb.llama_term(oracle, odd), cb.upload_weights(oracle, w2, Dtype.F32), odd, ids2, 3,
+                                            Dtype.F32, 16)
+    np.testing.assert_array_equal(got, want2)
+    # a foreign cache: prefill op by op (planning off), then continue with the recognised term
+    term = cb.llama_term(gpu, cfg)
+    k0, v0 = cb.empty_state_cache(gpu, cfg, 1, Dtype.F32)
+    gpu._ns.interp_set_planning(0)
+    try:
+        r1 = cb.Interpreter(gpu, params).run(term, [gpu.ndarray_from_vec_u32(ids[:, :20], (1, 20)), k0, v0, 32])
+    finally:
+        gpu._ns.interp_set_planning(1)
+    tok = gpu.to_numpy(r1[0])[:, -1, 0].reshape(1, 1).astype(np.uint32)
+    r2 = cb.Interpreter(gpu, params).run(term, [gpu.ndarray_from_vec_u32(tok, (1, 1)), r1[1], r1[2], 32])
+    assert gpu.to_numpy(r2[0])[0, 0, 0] == want[0, 1] and r2[1].shape[3] == 21
+
+
+def test_planned_bf16_decode_takes_the_persistent_kernel_and_handles_batches(gpu):
+    cfg, wb, ids = small_bf16_model()
+    pg = cb.upload_weights(gpu, wb, Dtype.BF16)
+    term = cb.llama_term(gpu, cfg)
+    out, _ = cb.generate_with_interpreter(gpu, term, pg, cfg, ids, 6, Dtype.BF16, 64)
+    assert term.plan_state == 1
+    runner = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=2, max_positions=64)
+    np.testing.assert_array_equal(out, runner.generate(ids, 6))
