@@ -462,6 +462,17 @@ Tensor CudaBackend::reduce(int kind, const Tensor& x) {
   int64_t rows = t.size();
   if (rows == 0) return t;
   Shape oshape(x.shape.begin(), x.shape.end() - 1), ostr(x.strides.begin(), x.strides.end() - 1);
+  // a pick over few, long float rows (logits): one CTA per row would leave most SMs idle, so the row is cut into
+  // 4096-element chunks first (two launches, scratch from the allocator)
+  if (kind == cgk::R_ARGMAX && x.dt != Dtype::U32 && x.strides.back() == 1 && n >= 8192 && n < (1ll << 31) && rows <= 65535 &&
+      rows < 4 * (int64_t)sm_count_ && (x.rank() <= 2 || x.is_contiguous())) {
+    const int64_t row_stride = x.rank() == 1 ? n : (x.rank() == 2 ? x.strides[0] : n);
+    const int64_t chunks = (n + 4095) / 4096;
+    Tensor scratch = empty({rows * chunks * 2}, Dtype::U32);
+    cgk::launch_argmax_two_stage((int)x.dt, x.raw(), row_stride, rows, n, scratch.raw(), (unsigned*)t.raw(), stream_);
+    check_launch("argmax");
+    return t;
+  }
   cgk::View4 outer = make_view(oshape, &ostr, nullptr, nullptr, nullptr);
   cgk::launch_reduce(kind, (int)x.dt, outer, rows, n, x.strides.back(), x.raw(), t.raw(), sm_count_, stream_);
   check_launch("reduce");

@@ -26,6 +26,8 @@ void launch_arange(unsigned* o, long long n, int sm_count, cudaStream_t st);
 enum { R_SUM = 0, R_MAX = 1, R_ARGMAX = 2 };
 // Rows of `n` elements: row r starts at a + row_offset(r) where the outer index space is vw (rank-1 dims,
 // strides in vw.sa) and the inner stride is `inner_stride`.  Output is contiguous [rows].
+void launch_argmax_two_stage(int dtype, const void* x, long long row_stride, long long rows, long long n, void* scratch,
+                             unsigned* out, cudaStream_t st);
 void launch_reduce(int kind, int dtype, const View4& outer, long long rows, long long n, long long inner_stride,
                    const void* a, void* o, int sm_count, cudaStream_t st);
 // out = softmax over the last axis of contiguous x [rows, n] (f32, bf16 or f16): the nn::softmax graph in one kernel.

@@ -16,6 +16,7 @@
 
 #include <type_traits>
 
+#include "argmax_two_stage.cuh"
 #include "elementwise.h"
 
 namespace cgk {
@@ -390,6 +391,21 @@ void launch_reduce(int kind, int dtype, const View4& outer, long long rows, long
     case R_MAX: launch_reduce_k<R_MAX>(dtype, outer, rows, n, inner_stride, a, o, sm, st); break;
     case R_ARGMAX: launch_reduce_k<R_ARGMAX>(dtype, outer, rows, n, inner_stride, a, o, sm, st); break;
   }
+}
+
+// Few long rows of a float dtype (rows start `row_stride` elements apart, unit inner stride): the two-stage pick.
+// `scratch` holds rows * ceil(n / 4096) 64-bit keys.
+void launch_argmax_two_stage(int dtype, const void* x, long long row_stride, long long rows, long long n, void* scratch,
+                             unsigned* out, cudaStream_t st) {
+  const unsigned chunks = (unsigned)((n + ARGMAX_STAGE_CHUNK - 1) / ARGMAX_STAGE_CHUNK);
+  dim3 grid(chunks, (unsigned)rows);
+  unsigned long long* part = (unsigned long long*)scratch;
+  switch (dtype) {
+    case DT_F32: argmax_stage1_kernel<float><<<grid, 256, 0, st>>>((const float*)x, row_stride, (int)n, part); break;
+    case DT_BF16: argmax_stage1_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, row_stride, (int)n, part); break;
+    default: argmax_stage1_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, row_stride, (int)n, part); break;
+  }
+  argmax_finish_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(part, (int)chunks, (int)rows, out);
 }
 
 void launch_gather(int elem_size, const void* x, const unsigned* idx, long long idx_stride, void* out, long long outer,
