@@ -324,6 +324,14 @@ def run_op_sweep(be):
         bt = be.transpose(be.from_numpy(np.ascontiguousarray(b_np.transpose(0, 2, 1)), dt), 1, 2)
         add_row("matmul [16,1024,1024]x[16,1024,1024], right operand stored K-contiguous",
                 timed_op(be, lambda: be.matmul(a, bt)), 3 * a_np.size * es, flops=2 * 16 * 1024 ** 3)
+        if name == "bf16":
+            # a compute-bound product in the prefill's layout (x @ W^T, both K-contiguous): 4096 output tiles
+            big_x = be.from_numpy(rng.standard_normal((8192, 4096)).astype(np.float32), dt)
+            big_w = be.transpose(be.from_numpy(rng.standard_normal((8192, 4096)).astype(np.float32), dt), 0, 1)
+            add_row("matmul [8192,4096]x[4096,8192], right operand stored K-contiguous",
+                    timed_op(be, lambda: be.matmul(big_x, big_w)), 3 * 8192 * 4096 * es + 8192 * 8192 * es - 8192 * 4096 * es,
+                    flops=2 * 8192 * 8192 * 4096)
+            del big_x, big_w
         table, idx = be.from_numpy(table_np, dt), be.from_numpy(idx_np)
         add_row("index 4096 rows of [32000,2048]", timed_op(be, lambda: be.index(table, 0, idx)), 2 * 4096 * 2048 * es + 16384)
         am = be.from_numpy(am_np, dt)

@@ -474,6 +474,204 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
   }
 }
 
+
+// ---- persistent variant ------------------------------------------------------------------------------------------
+// Same roles as above, but a CTA (one per SM) walks a static list of output tiles: tile t of CTA b is number
+// b + t * gridDim.x.  TMEM holds TWO accumulators, so the epilogue warps drain tile t (tcgen05.ld, round, store) while
+// the MMA warp is already accumulating tile t + 1; TMEM allocation, barrier set-up and the pipeline fill are paid once
+// per CTA instead of once per tile, and the operand ring keeps streaming across tile boundaries.  Tiles are numbered
+// in bands of 8 row tiles (row tile fastest inside a band) so that the tiles in flight share a few column tiles of B
+// and a band of A in L2.  BATCHED: 3-D tensor maps {K, rows, z}; tile numbers then run over the batch as well.
+// Used when a product has more tiles than SMs (prefill, batched products); K-major right operand only.
+constexpr int PERSIST_GROUP_M = 8;
+
+struct TileCoord {
+  int m0, n0, z;
+};
+template <int BN>
+__device__ __forceinline__ TileCoord tile_coord(long long t, int tiles_m, int tiles_n) {
+  const long long per_z = (long long)tiles_m * tiles_n;
+  TileCoord c;
+  c.z = (int)(t / per_z);
+  const int r = (int)(t - (long long)c.z * per_z);
+  const int band = r / (PERSIST_GROUP_M * tiles_n);
+  const int first_m = band * PERSIST_GROUP_M;
+  const int band_m = tiles_m - first_m < PERSIST_GROUP_M ? tiles_m - first_m : PERSIST_GROUP_M;
+  const int q = r - band * (PERSIST_GROUP_M * tiles_n);
+  c.n0 = (q / band_m) * BN;
+  c.m0 = (first_m + q % band_m) * BM;
+  return c;
+}
+
+template <int BN, int STAGES, bool BATCHED>
+__global__ void __launch_bounds__(192) gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                      const __grid_constant__ CUtensorMap tmB,
+                                                                      __nv_bfloat16* C, int M, int N, int K, int batch,
+                                                                      BatchGeom g, unsigned* err) {
+  using L = SmemLayout<BN>;
+  constexpr int TMEM_COLS = 2 * BN;   // two accumulators; BN is 128 or 256, so this is a power of two <= 512
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;    // [2]
+  uint64_t* tmem_empty = tmem_full + 2;    // [2]
+  uint32_t* tmem_slot = (uint32_t*)(tmem_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const long long total = (long long)tiles_m * tiles_n * batch;
+  const int num_k = (K + BK - 1) / BK;
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);   // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer: one continuous sequence of k-blocks over all tiles of this CTA ----
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    long long it = 0;       // k-blocks issued so far
+    bool ok = true;
+    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      const TileCoord tc = tile_coord<BN>(t, tiles_m, tiles_n);
+      for (int k = 0; k < num_k; ++k, ++it) {
+        const int s = (int)(it % STAGES);
+        const uint32_t par = (uint32_t)((it / STAGES) & 1) ^ 1u;
+        if (!mbar_wait(&empty[s], par, abort_flag)) { ok = false; break; }
+        unsigned char* a_dst = smem + s * L::STAGE_BYTES;
+        mbar_expect_tx(&full[s], L::STAGE_BYTES);
+        if (BATCHED) {
+          tma_load_3d(a_dst, &tmA, &full[s], k * BK, tc.m0, tc.z);
+          tma_load_3d(a_dst + L::A_BYTES, &tmB, &full[s], k * BK, tc.n0, tc.z);
+        } else {
+          tma_load_2d(a_dst, &tmA, &full[s], k * BK, tc.m0);
+          tma_load_2d(a_dst + L::A_BYTES, &tmB, &full[s], k * BK, tc.n0);
+        }
+      }
+    }
+    if (*abort_flag) {
+      // give copies already in flight a bounded time to land before the CTA's shared memory goes away
+      for (long long k = (it > STAGES ? it - STAGES : 0); k < it; ++k) {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&full[k % STAGES], (uint32_t)((k / STAGES) & 1)) && clock64() - t0 < WAIT_CYCLES) {
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ----
+    constexpr uint32_t idesc = make_idesc(BM, BN, false);
+    long long it = 0;
+    bool ok = true;
+    int i = 0;   // this CTA's tile counter
+    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++i) {
+      const int acc = i & 1;
+      // the epilogue must have drained this accumulator (its previous use was tile i - 2)
+      ok = mbar_wait(&tmem_empty[acc], (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+      for (int k = 0; k < num_k && ok; ++k, ++it) {
+        const int s = (int)(it % STAGES);
+        ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const unsigned char* a_tile = smem + s * L::STAGE_BYTES;
+        const uint64_t adesc = make_smem_desc(a_tile);
+        const uint64_t bdesc = make_smem_desc(a_tile + L::A_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk)
+          umma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (k | kk) != 0 ? 1u : 0u);
+        umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+      }
+      if (ok) umma_commit(&tmem_full[acc]);  // accumulator complete
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue: warp w owns TMEM lanes 32*(w%4) .. +31 = rows m0 + 32*(w%4) + lane ----
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int q = warp & 3;
+    const bool vec_ok = (g.ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (((uintptr_t)g.res & 15) == 0) && (g.c_outer % 8 == 0);
+    int i = 0;
+    for (long long t = blockIdx.x; t < total; t += gridDim.x, ++i) {
+      const int acc = i & 1;
+      bool ok = mbar_wait(&tmem_full[acc], (uint32_t)((i >> 1) & 1), abort_flag);
+      ok = __all_sync(0xffffffffu, ok);   // all lanes must agree before the warp-collective tcgen05.ld
+      if (!ok) break;
+      tc_fence_after();
+      const TileCoord tc = tile_coord<BN>(t, tiles_m, tiles_n);
+      const int row = tc.m0 + q * 32 + lane;
+      const long long c_off = (long long)tc.z * g.c_outer;
+      __nv_bfloat16* crow = C + c_off + (long long)row * g.ldc;
+      const __nv_bfloat16* rrow = g.res ? g.res + c_off + (long long)row * g.ldc : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN && tc.m0 + q * 32 < M; c0 += 32) {   // a warp whose 32 rows lie beyond M stores nothing
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+        tmem_ld_wait();
+        if (row < M) {
+          const int col = tc.n0 + c0;
+          if (vec_ok && col + 32 <= N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
+              if (rrow) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + col + v * 8);
+                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  w[j] = add_res2(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]), rw[j]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+                  w[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+              }
+              *reinterpret_cast<uint4*>(crow + col + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col + j < N) {
+                __nv_bfloat16 o = __float2bfloat16_rn(__uint_as_float(r[j]));
+                if (rrow) o = __float2bfloat16_rn(__bfloat162float(rrow[col + j]) + __bfloat162float(o));
+                crow[col + j] = o;
+              }
+          }
+        }
+      }
+      // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tmem_empty[acc])) : "memory");
+    }
+  }
+  if (*abort_flag && threadIdx.x == 0) atomicOr(err, DEV_ERR_WAIT_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+  }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -720,6 +918,34 @@ void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M
   g.early_b = static_b ? 1 : 0;
   launch_g<BN, STAGES, BATCHED ? 1 : 0, B_MN>(ta, tb, C, M, N, K, batch, g, err, st);
 }
+
+// Persistent launch (one CTA per SM): bf16 output, K-major right operand, optional residual.
+template <int BN, int STAGES, bool BATCHED>
+void launch_persistent(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K, long long batch,
+                       unsigned* err, int sm_count, cudaStream_t st, const void* residual) {
+  using L = SmemLayout<BN>;
+  size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 /* alignment slack */ + (2 * STAGES + 4) * 8 + 16;
+  auto kern = gemm_tcgen05_persistent_kernel<BN, STAGES, BATCHED>;
+  static bool attr_set_dev[64] = {false};   // function attributes are per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& attr_set = attr_set_dev[dev & 63];
+  if (!attr_set) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  BatchGeom g;
+  g.heads = 1;
+  g.b_div = 1;
+  g.c_outer = M * N;
+  g.c_inner = 0;
+  g.ldc = (int)N;
+  g.res = (const __nv_bfloat16*)residual;
+  g.early_b = 0;
+  const long long total = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
+  const unsigned grid = (unsigned)(total < sm_count ? total : sm_count);
+  kern<<<grid, 192, smem, st>>>(ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, (int)batch, g, err);
+}
 }  // namespace
 
 bool tcgen05_available();
@@ -794,6 +1020,14 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
   if (bn > N) bn = N >= 256 ? 256 : (N >= 128 ? 128 : (N >= 64 ? 64 : (N >= 32 ? 32 : 16)));
   if (!make_map(&ta, A, K, p.M, lda, p.batch, p.a_bs, BM) || !make_map(&tb, B, K, N, ldb, p.batch, p.b_bs, bn)) return false;
   const bool bt3 = p.batch > 1;
+  // more tiles than SMs: the persistent kernel (epilogue of one tile under the main loop of the next)
+  if ((bn == 256 || bn == 128) && mtiles * ((N + bn - 1) / bn) > sm_count) {
+    if (bn == 256) bt3 ? launch_persistent<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, sm_count, st, residual)
+                       : launch_persistent<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, sm_count, st, residual);
+    else bt3 ? launch_persistent<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, sm_count, st, residual)
+             : launch_persistent<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, sm_count, st, residual);
+    return true;
+  }
   switch (bn) {
     case 256: bt3 ? launch_t<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual, static_b) : launch_t<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, st, residual, static_b); break;
     case 128: bt3 ? launch_t<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, st, residual, static_b) : launch_t<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, st, residual, static_b); break;

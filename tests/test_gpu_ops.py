@@ -374,7 +374,8 @@ def _bf16_round(a):
 
 @pytest.mark.parametrize("mnk", [(128, 128, 64), (300, 200, 264), (17, 2048, 512), (512, 384, 2048), (1000, 136, 72),
                                  (129, 257, 1032), (64, 16, 16), (128, 4096, 256), (100, 8200, 128), (32, 40, 64),
-                                 (2048, 2048, 512)], ids=str)
+                                 (2048, 2048, 512), (2048, 4096, 512), (1000, 8200, 264), (2500, 1160, 136),
+                                 (4100, 4104, 72)], ids=str)
 def test_tensor_core_gemm_against_f32_path(gpu, mnk):
     """bf16 `x @ W^T` products (both operands K-contiguous) run on the tcgen05 kernel; the same bf16-rounded
     operands multiplied by the exact-f32 SIMT kernel give the reference.  Only the accumulation order differs, so
@@ -428,6 +429,27 @@ def test_tensor_core_gemm_row_major_right_operand(gpu, mnk):
     assert helpers.rel_err(got, ref) < 6e-3
     ref64 = x[-8:].astype(np.float64) @ w[:, :8].astype(np.float64)
     np.testing.assert_allclose(got[-8:, :8], ref64, rtol=1e-2, atol=1e-2)
+
+
+def test_tensor_core_gemm_more_tiles_than_sms(gpu):
+    """Products with more output tiles than SMs run on the persistent kernel (a CTA walks several tiles, two
+    accumulators in tensor memory).  Every output element is checked against a float64 product, for a batched K-major
+    product with ragged row tiles and for a product with a fused residual in the Llama runner's shapes."""
+    rng = np.random.default_rng(77)
+    q = _bf16_round(rng.standard_normal((8, 900, 64)).astype(np.float32))
+    kk = _bf16_round(rng.standard_normal((8, 1024, 64)).astype(np.float32))
+    got = gpu.to_f32(gpu.matmul(gpu.from_numpy(q, Dtype.BF16), gpu.transpose(gpu.from_numpy(kk, Dtype.BF16), 1, 2)))
+    ref64 = np.einsum("bmk,bnk->bmn", q.astype(np.float64), kk.astype(np.float64))
+    np.testing.assert_allclose(got, ref64, rtol=2e-2, atol=8e-2)
+    # every tile must land where it belongs: compare the position of the largest element of each row
+    assert (got.argmax(-1) == _bf16_round(ref64.astype(np.float32)).argmax(-1)).mean() > 0.98
+    # many launches in a row on the same buffers: barrier phases and accumulator hand-over start afresh each time
+    x = _bf16_round(rng.standard_normal((1536, 320)).astype(np.float32))
+    w = _bf16_round((rng.standard_normal((6400, 320)) / 18).astype(np.float32))
+    X, Wt = gpu.from_numpy(x, Dtype.BF16), gpu.transpose(gpu.from_numpy(w, Dtype.BF16), 0, 1)
+    ref64 = x.astype(np.float64) @ w.astype(np.float64).T
+    for _ in range(3):
+        np.testing.assert_allclose(gpu.to_f32(gpu.matmul(X, Wt)), ref64, rtol=2e-2, atol=2e-2)
 
 
 def test_tensor_core_gemm_row_major_batched(gpu):
