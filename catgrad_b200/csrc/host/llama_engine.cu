@@ -38,6 +38,10 @@ struct LayerW {
   const void *qkv = nullptr, *gate_up = nullptr;
 };
 
+// Row interleave of the stacked [gate; up] weight: 32 gate rows, then the 32 up rows of the same features, so that a
+// 64-column block of the product holds both halves of 32 outputs and SiLU(gate) * up can ride in the GEMM epilogue.
+constexpr int64_t GU_BLOCK = 32;
+
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace
@@ -57,6 +61,7 @@ struct cg_llama {
   int64_t max_batch = 0, P = 0;
   std::vector<Tensor> keep;  // parameter tensors kept alive
   std::vector<Tensor> stacked;  // [q; k; v] and [gate; up] per layer (GEMM path only)
+  bool gu_interleaved = false;  // [gate; up] rows alternate in blocks of GU_BLOCK (FFN width a multiple of it)
   std::vector<LayerW> layers;
   const void *embed = nullptr, *final_norm = nullptr, *head = nullptr;
 
@@ -188,20 +193,25 @@ struct Plan {
   // (batch-256 decode, prefill) but -18 % on a batch-32 decode step, whose cluster launches it delays.
   // With `res`: res[M,N] += T(xin @ W^T) (the residual add of a block), through `scratch` when the add cannot ride
   // in the GEMM epilogue.
-  void gemm(const void* xin, int64_t ldx, const void* W, void* out, int64_t M, int64_t N, int64_t K, void* res = nullptr) {
+  // `silu_pairs`: W is the block-interleaved [gate; up] weight and out is [M, N / 2] (see launch_tcgen05_gemm);
+  // returns false, with nothing launched, when the tensor-core kernel cannot take that product.
+  bool gemm(const void* xin, int64_t ldx, const void* W, void* out, int64_t M, int64_t N, int64_t K, void* res = nullptr,
+            bool silu_pairs = false) {
     cgk::View4 bt;
     std::memset(&bt, 0, sizeof(bt));
     bt.rank = 0;
     bt.total = 1;
     if (std::is_same<T, __nv_bfloat16>::value && cgk::tcgen05_gemm_applicable(bt, 1, xin, W, M, N, K, ldx, 1, 1, K) &&
         cgk::launch_tcgen05_gemm(bt, 1, xin, W, res ? res : out, M, N, K, ldx, K, m.be->dev_err(), sm, st, false, res,
-                                 /*static_b=*/m.use_pdl && M >= 256)) {
+                                 /*static_b=*/m.use_pdl && M >= 256, silu_pairs)) {
       launched("gemm(tcgen05)");
-      return;
+      return true;
     }
+    if (silu_pairs) return false;
     cgk::launch_matmul((int)m.dt, bt, 1, xin, W, out, M, N, K, ldx, 1, 1, K, sm, st);
     launched("gemm");
     if (res) add_inplace(res, out, M * N);
+    return true;
   }
 
   int grid_for(long long items) {
@@ -571,10 +581,15 @@ struct Plan {
         gemv(cgk::PRO_NORM, cgk::EPI_SILU_MUL, a);
       } else {
         rmsnorm(x, w.post_norm, m.xn.raw(), M, H, 1, 0);
-        gemm(m.xn.raw(), H, w.gate_up, m.g.raw(), M, 2 * F, H);   // one product over the stacked [gate; up]
-        launch(cgk::silu_mul_packed_kernel<T>, dim3((unsigned)grid_for(M * F / (16 / sizeof(T)))), dim3(256), 0,
-               (const T*)m.g.raw(), hbuf, (long long)M, (int)F);
-        launched("silu_mul");
+        // one product over the interleaved [gate; up] with SiLU(gate) * up in its epilogue; where the tensor-core
+        // kernel cannot take it (f32, odd sizes) the two halves are multiplied out and combined by a second kernel
+        if (!(m.gu_interleaved && gemm(m.xn.raw(), H, w.gate_up, hbuf, M, 2 * F, H, nullptr, true))) {
+          if (!m.g.defined() || m.g.size() < M * 2 * F) m.g = m.be->empty({M, 2 * F}, m.dt);
+          gemm(m.xn.raw(), H, w.gate_up, m.g.raw(), M, 2 * F, H);
+          launch(cgk::silu_mul_packed_kernel<T>, dim3((unsigned)grid_for(M * F / (16 / sizeof(T)))), dim3(256), 0,
+                 (const T*)m.g.raw(), hbuf, (long long)M, (int)F, m.gu_interleaved ? (int)GU_BLOCK : 0);
+          launched("silu_mul");
+        }
       }
       if (gemv_ok(M, F)) {
         cgk::GemvArgs a{};
@@ -755,8 +770,15 @@ void ensure_stacked_weights(cg_llama& m) {
     CG_CUDA(cudaMemcpyAsync(p + (size_t)NQ * H * m.es, w.k, (size_t)NKV * H * m.es, cudaMemcpyDeviceToDevice, st));
     CG_CUDA(cudaMemcpyAsync(p + (size_t)(NQ + NKV) * H * m.es, w.v, (size_t)NKV * H * m.es, cudaMemcpyDeviceToDevice, st));
     unsigned char* g = (unsigned char*)gu.raw();
-    CG_CUDA(cudaMemcpyAsync(g, w.gate, (size_t)F * H * m.es, cudaMemcpyDeviceToDevice, st));
-    CG_CUDA(cudaMemcpyAsync(g + (size_t)F * H * m.es, w.up, (size_t)F * H * m.es, cudaMemcpyDeviceToDevice, st));
+    m.gu_interleaved = F % GU_BLOCK == 0;
+    if (m.gu_interleaved) {
+      const size_t blk = (size_t)GU_BLOCK * H * m.es;   // one block of rows
+      CG_CUDA(cudaMemcpy2DAsync(g, 2 * blk, w.gate, blk, blk, (size_t)(F / GU_BLOCK), cudaMemcpyDeviceToDevice, st));
+      CG_CUDA(cudaMemcpy2DAsync(g + blk, 2 * blk, w.up, blk, blk, (size_t)(F / GU_BLOCK), cudaMemcpyDeviceToDevice, st));
+    } else {
+      CG_CUDA(cudaMemcpyAsync(g, w.gate, (size_t)F * H * m.es, cudaMemcpyDeviceToDevice, st));
+      CG_CUDA(cudaMemcpyAsync(g + (size_t)F * H * m.es, w.up, (size_t)F * H * m.es, cudaMemcpyDeviceToDevice, st));
+    }
     w.qkv = qkv.raw();
     w.gate_up = gu.raw();
     m.stacked.push_back(qkv);
@@ -807,9 +829,14 @@ void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
     } else {
       m.tmp = m.be->empty({M, H}, m.dt);
     }
-    if (M > 16 || (size_t)16 * H * m.es > 160 * 1024) {  // gate | up buffer of the GEMM path
-      m.g = m.be->empty({M, 2 * F}, m.dt);
+    if (M > 16 || (size_t)16 * H * m.es > 160 * 1024) {  // GEMM path
       ensure_stacked_weights(m);
+      // gate | up buffer: only where SiLU(gate) * up cannot ride in the tensor-core GEMM's epilogue
+      // (the fused epilogue is taken only by products with several tiles per SM, where it runs under the next
+      // tile's main loop; with one tile per SM - a decode step of a few hundred sequences - its exponentials would
+      // be exposed and the separate, fully parallel SiLU kernel is faster)
+      if (M <= 1024 || !(m.gu_interleaved && m.dt == Dtype::BF16 && cgk::tcgen05_available()))
+        m.g = m.be->empty({M, 2 * F}, m.dt);
     }
     m.ids_in = m.be->empty({M}, Dtype::U32);
     m.cap_tokens = M;

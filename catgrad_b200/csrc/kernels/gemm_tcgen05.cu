@@ -191,7 +191,35 @@ struct BatchGeom {
   // BMODE 0 with a right operand that no earlier kernel of the stream writes (a weight): the kernel was launched
   // with programmatic stream serialization and may fetch its first B tiles before the preceding kernel has finished
   int early_b;
+  // columns come in blocks of 64 = 32 `gate` columns followed by the 32 `up` columns of the same features (the
+  // interleaved [gate; up] weight of an MLP): the epilogue writes bf16(bf16(g * sigmoid(g)) * u), 32 values per block,
+  // to a C that is half as wide (ldc = N / 2).  bf16 output, no residual, N a multiple of 64; persistent kernel only.
+  int silu = 0;
 };
+
+// One 64-column block of gate|up accumulators of one row -> 32 bf16 outputs (64 bytes).  The products are rounded
+// to bf16 first, as a stand-alone GEMM would have stored them, then combined like `silu_mul_packed_kernel`.
+__device__ __forceinline__ void store_silu_block(__nv_bfloat16* dst, const uint32_t (&rg)[32], const uint32_t (&ru)[32]) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float o[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float gf = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rg[v * 8 + 2 * j + e])));
+        const float uf = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ru[v * 8 + 2 * j + e])));
+        const float sg = 1.f / (1.f + expf(-gf));
+        const float si = __bfloat162float(__float2bfloat16_rn(gf * sg));
+        o[e] = si * uf;
+      }
+      __nv_bfloat162 h = __floats2bfloat162_rn(o[0], o[1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
 
 // bf16(r + bf16(a)) for two neighbouring elements
 __device__ __forceinline__ uint32_t add_res2(float a0, float a1, uint32_t r) {
@@ -482,7 +510,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
 // per CTA instead of once per tile, and the operand ring keeps streaming across tile boundaries.  Tiles are numbered
 // in bands of 8 row tiles (row tile fastest inside a band) so that the tiles in flight share a few column tiles of B
 // and a band of A in L2.  BATCHED: 3-D tensor maps {K, rows, z}; tile numbers then run over the batch as well.
-// Used when a product has more tiles than SMs (prefill, batched products); K-major right operand only.
+// Used when a product has more tiles than SMs (prefill, batched products).
 constexpr int PERSIST_GROUP_M = 8;
 
 struct TileCoord {
@@ -503,7 +531,7 @@ __device__ __forceinline__ TileCoord tile_coord(long long t, int tiles_m, int ti
   return c;
 }
 
-template <int BN, int STAGES, bool BATCHED>
+template <int BN, int STAGES, bool BATCHED, bool B_MN>
 __global__ void __launch_bounds__(192) gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                       const __grid_constant__ CUtensorMap tmB,
                                                                       __nv_bfloat16* C, int M, int N, int K, int batch,
@@ -560,12 +588,19 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_persistent_kernel(const __gr
         if (!mbar_wait(&empty[s], par, abort_flag)) { ok = false; break; }
         unsigned char* a_dst = smem + s * L::STAGE_BYTES;
         mbar_expect_tx(&full[s], L::STAGE_BYTES);
-        if (BATCHED) {
-          tma_load_3d(a_dst, &tmA, &full[s], k * BK, tc.m0, tc.z);
-          tma_load_3d(a_dst + L::A_BYTES, &tmB, &full[s], k * BK, tc.n0, tc.z);
+        unsigned char* b_dst = a_dst + L::A_BYTES;
+        if (BATCHED) tma_load_3d(a_dst, &tmA, &full[s], k * BK, tc.m0, tc.z);
+        else tma_load_2d(a_dst, &tmA, &full[s], k * BK, tc.m0);
+        if (B_MN) {
+          // row-major [K, N] right operand: one 64-column x BK-row box per 64 columns of the tile
+#pragma unroll
+          for (int nb = 0; nb < BN / 64; ++nb) {
+            if (BATCHED) tma_load_3d(b_dst + nb * (BK * 128), &tmB, &full[s], tc.n0 + nb * 64, k * BK, tc.z);
+            else tma_load_2d(b_dst + nb * (BK * 128), &tmB, &full[s], tc.n0 + nb * 64, k * BK);
+          }
         } else {
-          tma_load_2d(a_dst, &tmA, &full[s], k * BK, tc.m0);
-          tma_load_2d(a_dst + L::A_BYTES, &tmB, &full[s], k * BK, tc.n0);
+          if (BATCHED) tma_load_3d(b_dst, &tmB, &full[s], k * BK, tc.n0, tc.z);
+          else tma_load_2d(b_dst, &tmB, &full[s], k * BK, tc.n0);
         }
       }
     }
@@ -579,7 +614,7 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_persistent_kernel(const __gr
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
-    constexpr uint32_t idesc = make_idesc(BM, BN, false);
+    constexpr uint32_t idesc = make_idesc(BM, BN, B_MN);
     long long it = 0;
     bool ok = true;
     int i = 0;   // this CTA's tile counter
@@ -597,10 +632,12 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_persistent_kernel(const __gr
         tc_fence_after();
         const unsigned char* a_tile = smem + s * L::STAGE_BYTES;
         const uint64_t adesc = make_smem_desc(a_tile);
-        const uint64_t bdesc = make_smem_desc(a_tile + L::A_BYTES);
+        const uint64_t bdesc = B_MN ? make_smem_desc_mn(a_tile + L::A_BYTES) : make_smem_desc(a_tile + L::A_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < BK / UMMA_K; ++kk)
-          umma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (k | kk) != 0 ? 1u : 0u);
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          const uint64_t bstep = B_MN ? (uint64_t)(kk * (UMMA_K * 128 / 16)) : (uint64_t)(kk * 2);
+          umma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + bstep, idesc, (k | kk) != 0 ? 1u : 0u);
+        }
         umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
       }
       if (ok) umma_commit(&tmem_full[acc]);  // accumulator complete
@@ -622,6 +659,16 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_persistent_kernel(const __gr
       const long long c_off = (long long)tc.z * g.c_outer;
       __nv_bfloat16* crow = C + c_off + (long long)row * g.ldc;
       const __nv_bfloat16* rrow = g.res ? g.res + c_off + (long long)row * g.ldc : nullptr;
+      if (g.silu) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN && tc.m0 + q * 32 < M; c0 += 64) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), rg);
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0 + 32), ru);
+          tmem_ld_wait();
+          if (row < M && tc.n0 + c0 + 64 <= N) store_silu_block(crow + ((tc.n0 + c0) >> 1), rg, ru);
+        }
+      } else
 #pragma unroll 1
       for (int c0 = 0; c0 < BN && tc.m0 + q * 32 < M; c0 += 32) {   // a warp whose 32 rows lie beyond M stores nothing
         uint32_t r[32];
@@ -919,13 +966,13 @@ void launch_t(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M
   launch_g<BN, STAGES, BATCHED ? 1 : 0, B_MN>(ta, tb, C, M, N, K, batch, g, err, st);
 }
 
-// Persistent launch (one CTA per SM): bf16 output, K-major right operand, optional residual.
-template <int BN, int STAGES, bool BATCHED>
+// Persistent launch (one CTA per SM): bf16 output, optional residual.
+template <int BN, int STAGES, bool BATCHED, bool B_MN = false>
 void launch_persistent(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long long M, long long N, long long K, long long batch,
-                       unsigned* err, int sm_count, cudaStream_t st, const void* residual) {
+                       unsigned* err, int sm_count, cudaStream_t st, const void* residual, bool silu = false) {
   using L = SmemLayout<BN>;
   size_t smem = (size_t)STAGES * L::STAGE_BYTES + 1024 /* alignment slack */ + (2 * STAGES + 4) * 8 + 16;
-  auto kern = gemm_tcgen05_persistent_kernel<BN, STAGES, BATCHED>;
+  auto kern = gemm_tcgen05_persistent_kernel<BN, STAGES, BATCHED, B_MN>;
   static bool attr_set_dev[64] = {false};   // function attributes are per device
   int dev = 0;
   cudaGetDevice(&dev);
@@ -937,11 +984,12 @@ void launch_persistent(const CUtensorMap& ta, const CUtensorMap& tb, void* C, lo
   BatchGeom g;
   g.heads = 1;
   g.b_div = 1;
-  g.c_outer = M * N;
+  g.c_outer = silu ? M * N / 2 : M * N;
   g.c_inner = 0;
-  g.ldc = (int)N;
+  g.ldc = (int)(silu ? N / 2 : N);
   g.res = (const __nv_bfloat16*)residual;
   g.early_b = 0;
+  g.silu = silu ? 1 : 0;
   const long long total = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
   const unsigned grid = (unsigned)(total < sm_count ? total : sm_count);
   kern<<<grid, 192, smem, st>>>(ta, tb, (__nv_bfloat16*)C, (int)M, (int)N, (int)K, (int)batch, g, err);
@@ -959,7 +1007,8 @@ bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, co
 
 bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
                          long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
-                         cudaStream_t st, bool b_n_contiguous, const void* residual, bool static_b) {
+                         cudaStream_t st, bool b_n_contiguous, const void* residual, bool static_b, bool silu_pairs) {
+  if (silu_pairs && (b_n_contiguous || residual || batch != 1 || N % 64 != 0)) return false;
   Problem p = b_n_contiguous ? analyse(bt, batch, A, B, M, N, K, lda, 1, ldb, 1) : analyse(bt, batch, A, B, M, N, K, lda, 1, 1, ldb);
   if (!p.ok) return false;
   CUtensorMap ta, tb;
@@ -967,7 +1016,7 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
   // columns) keep all SMs streaming W when M fits one row tile (decode of a batch).
   const long long mtiles = ((p.M + BM - 1) / BM) * p.batch;
   const bool streaming = mtiles <= 2;                 // one or two row tiles: a pass over W, HBM-bound
-  const int min_bn = streaming ? 16 : 64;             // compute-bound products keep the MMA reasonably wide
+  const int min_bn = streaming && !silu_pairs ? 16 : 64;   // compute-bound products keep the MMA reasonably wide
   // enough tiles to occupy ~60 % of the SMs, but do not cut tiles finer than that: a second wave of CTAs costs more
   // than narrower tiles gain
   const long long want = streaming ? (3ll * sm_count) / 5 : (3ll * sm_count) / 4;
@@ -978,6 +1027,13 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
     if (bn < 64) bn = 64;
     if (!make_map(&ta, A, K, p.M, lda, p.batch, p.a_bs, BM) || !make_map_mn(&tb, B, K, N, ldb, p.batch, p.b_bs)) return false;
     const bool b3 = p.batch > 1;
+    if ((bn == 256 || bn == 128) && mtiles * ((N + bn - 1) / bn) > sm_count) {
+      if (bn == 256) b3 ? launch_persistent<256, 4, true, true>(ta, tb, C, p.M, N, K, p.batch, err, sm_count, st, nullptr)
+                        : launch_persistent<256, 4, false, true>(ta, tb, C, p.M, N, K, 1, err, sm_count, st, nullptr);
+      else b3 ? launch_persistent<128, 6, true, true>(ta, tb, C, p.M, N, K, p.batch, err, sm_count, st, nullptr)
+              : launch_persistent<128, 6, false, true>(ta, tb, C, p.M, N, K, 1, err, sm_count, st, nullptr);
+      return true;
+    }
     switch (bn) {
       case 256: b3 ? launch_t<256, 4, true, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<256, 4, false, true>(ta, tb, C, p.M, N, K, 1, err, st); break;
       case 128: b3 ? launch_t<128, 6, true, true>(ta, tb, C, p.M, N, K, p.batch, err, st) : launch_t<128, 6, false, true>(ta, tb, C, p.M, N, K, 1, err, st); break;
@@ -987,7 +1043,7 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
   }
   // One or two row tiles and too few 128-wide column tiles to fill the GPU: split K over a cluster instead of
   // cutting the columns finer (narrow tiles re-read the activations once per tile).
-  if (streaming && p.batch == 1 && N >= 64) {
+  if (streaming && p.batch == 1 && N >= 64 && !silu_pairs) {
     const long long num_k = (K + BK - 1) / BK;
     // candidates: column tiles of 128 or 64, 2/4/8-way split; keep the one that occupies the most SMs in ONE wave
     // of clusters (ties: wider tiles, then fewer splits)
@@ -1021,11 +1077,15 @@ bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const 
   if (!make_map(&ta, A, K, p.M, lda, p.batch, p.a_bs, BM) || !make_map(&tb, B, K, N, ldb, p.batch, p.b_bs, bn)) return false;
   const bool bt3 = p.batch > 1;
   // more tiles than SMs: the persistent kernel (epilogue of one tile under the main loop of the next)
-  if ((bn == 256 || bn == 128) && mtiles * ((N + bn - 1) / bn) > sm_count) {
+  const bool persistent = (bn == 256 || bn == 128) && mtiles * ((N + bn - 1) / bn) > sm_count;
+  // SiLU(gate) * up costs the four epilogue warps a few microseconds per tile: worth fusing only where that runs under
+  // the next tile's MMAs
+  if (silu_pairs && !persistent) return false;
+  if (persistent) {
     if (bn == 256) bt3 ? launch_persistent<256, 4, true>(ta, tb, C, p.M, N, K, p.batch, err, sm_count, st, residual)
-                       : launch_persistent<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, sm_count, st, residual);
+                       : launch_persistent<256, 4, false>(ta, tb, C, p.M, N, K, 1, err, sm_count, st, residual, silu_pairs);
     else bt3 ? launch_persistent<128, 6, true>(ta, tb, C, p.M, N, K, p.batch, err, sm_count, st, residual)
-             : launch_persistent<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, sm_count, st, residual);
+             : launch_persistent<128, 6, false>(ta, tb, C, p.M, N, K, 1, err, sm_count, st, residual, silu_pairs);
     return true;
   }
   switch (bn) {

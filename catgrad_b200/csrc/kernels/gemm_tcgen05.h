@@ -14,10 +14,14 @@ bool tcgen05_gemm_applicable(const View4& bt, long long batch, const void* A, co
 // residual (optional, C's layout, may alias C; K-major B and a single product only): C = bf16(residual + bf16(A x B)).
 // static_b: no earlier kernel of the stream writes B (it is a weight); the kernel is then launched with programmatic
 // stream serialization and fetches its first B tiles while the preceding kernel drains.
+// silu_pairs: B's rows come in blocks of 64 = 32 `gate` rows then the 32 `up` rows of the same features; C is then
+// [M, N / 2] = bf16(bf16(g * sigmoid(g)) * u) with g, u the bf16-rounded products (the MLP's SiLU-and-multiply in the
+// epilogue).  K-major B, single product, no residual, N a multiple of 64, more output tiles than SMs (the persistent
+// kernel, where the epilogue's exponentials run under the next tile's MMAs); otherwise nothing is launched.
 bool launch_tcgen05_gemm(const View4& bt, long long batch, const void* A, const void* B, void* C, long long M,
                          long long N, long long K, long long lda, long long ldb, unsigned* err, int sm_count,
                          cudaStream_t st, bool b_n_contiguous = false, const void* residual = nullptr,
-                         bool static_b = false);
+                         bool static_b = false, bool silu_pairs = false);
 // C[batch, M, N] (contiguous f32) = A[batch, M, K] x B[batch, N, K]^T with bf16 operands (both K-contiguous, rows K
 // apart, batch strides a_bs / b_bs in elements) and the f32 accumulator stored unrounded.
 bool launch_tcgen05_gemm_f32out(const void* A, const void* B, float* C, long long M, long long N, long long K,

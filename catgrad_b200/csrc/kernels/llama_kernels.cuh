@@ -746,7 +746,6 @@ __global__ void __launch_bounds__(128) attn_decode_group_kernel(AttnArgs a, unsi
   T* vc = (T*)a.vc + ((long long)b * a.nkv + kvh) * a.P * HD;
   const float* ct = a.cos_t + (long long)pos * half;
   const float* st = a.sin_t + (long long)pos * half;
-
   // RoPE of the group's query heads and of the new key; the new value row is copied
   for (int i = lane; i < REP * half; i += 32) {
     const int h = i / half, j = i - h * half;
@@ -1368,7 +1367,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gat
 // gate = gu[r, 0:F], up = gu[r, F:2F]; out is [rows, F].  F is a multiple of 16 bytes.
 template <class T>
 __global__ void __launch_bounds__(256) silu_mul_packed_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows,
-                                                              int F) {
+                                                              int F, int block) {
   constexpr int VEC = 16 / sizeof(T);
   pdl_launch_dependents();   // the down projection that follows may start fetching its weight tiles
   pdl_wait();
@@ -1377,8 +1376,11 @@ __global__ void __launch_bounds__(256) silu_mul_packed_kernel(const T* __restric
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
     const long long r = t / per;
     const int c = (int)(t - r * per) * VEC;
-    VecT<T, VEC> g = *reinterpret_cast<const VecT<T, VEC>*>(gu + r * 2 * F + c);
-    VecT<T, VEC> u = *reinterpret_cast<const VecT<T, VEC>*>(gu + r * 2 * F + F + c);
+    // block == 0: row = gate[F] | up[F]; otherwise blocks of `block` gate columns alternate with their up columns
+    const long long gi = block ? r * 2 * F + (long long)(c / block) * 2 * block + c % block : r * 2 * F + c;
+    const long long ui = block ? gi + block : gi + F;
+    VecT<T, VEC> g = *reinterpret_cast<const VecT<T, VEC>*>(gu + gi);
+    VecT<T, VEC> u = *reinterpret_cast<const VecT<T, VEC>*>(gu + ui);
     VecT<T, VEC> o;
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
