@@ -554,6 +554,10 @@ def main():
                                    "traffic": None if r3["persistent"] else TRAFFIC_PER_STEP_B1}}
         if not args.no_interpreter_path:
             line["c3"]["interpreter_path"] = interpreter_path_tok_s(be, cfg, params)
+        # the same two figures in the reference benchmark mode's own table (stderr: stdout carries the one JSON line)
+        for row in cb.bench_table("llama-3.2-1b shape (synthetic weights)", cfg.num_params() * 2 / 2 ** 30, cfg.num_params() / 1e6,
+                                  "b200", 512, r3["prefill_ms"] / 1e3, c3_steps, r3["ms"] / 1e3):
+            print(row, file=sys.stderr)
     if tensor_parallel:
         del comm
     if single and workload == "c3" and not args.skip_c4:

@@ -6,6 +6,6 @@ catgrad's `Backend` trait, of its term builder/interpreter and of the Llama gene
 """
 from .backend import Backend, BackendError, Dtype, Status, Tensor, bf16_bits_to_f32, f32_to_bf16_bits  # noqa: F401
 from .ir import Interpreter, NodeType, OpKind, Parameters, ScalarOp, Term, TermBuilder  # noqa: F401
-from .llama import (LLAMA_1B, LLAMA_8B, TINY, LlamaConfig, LlamaRunner, empty_state_cache,  # noqa: F401
+from .llama import (LLAMA_1B, LLAMA_8B, TINY, LlamaConfig, LlamaRunner, bench_table, empty_state_cache,  # noqa: F401
                     generate_with_interpreter, llama_term, random_weights, upload_weights)
 from . import safetensors, tp  # noqa: F401,E402

@@ -21,6 +21,7 @@
 #include "../kernels/elementwise.h"
 #include "../kernels/gemm_tcgen05.h"
 #include "../kernels/llama_kernels.cuh"
+#include "../kernels/attn_prefill_fused.cuh"
 #include "../kernels/llama_persist.cuh"
 #include "../kernels/matmul.h"
 #include "c_api_internal.h"
@@ -667,10 +668,29 @@ struct Plan {
     const LlamaConfig& c = m.cfg;
     const int64_t nh = c.num_attention_heads, nkv = c.num_key_value_heads, hd = m.hd, rep = nh / nkv;
     const int64_t T0 = m.host_ctx_len, Tt = T0 + S;
-    const int64_t Tp = score_pitch(Tt);  // row pitch of the score matrix
-    T* scores = (T*)m.scores.raw();
     const float scale = cgk_host_round((float)std::sqrt((float)hd));
     unsigned* err = m.be->dev_err();
+    if (fused_prefill_ok(m, Tt)) {
+      // one kernel: scores, mask, softmax and P x V per 64-query tile, the score rows never leave shared memory
+      cgk::PrefillAttnArgs a{};
+      a.q = (const __nv_bfloat16*)q; a.q_row = qs; a.kc = (const __nv_bfloat16*)kcl; a.vc = (const __nv_bfloat16*)vcl;
+      a.out = (__nv_bfloat16*)attn_out; a.S = (int)S; a.T0 = (int)T0; a.P = (int)m.P; a.nh = (int)nh; a.nkv = (int)nkv;
+      a.scale = scale;
+      a.pp = (int)((Tt + cgk::PA_KEYS - 1) / cgk::PA_KEYS * cgk::PA_KEYS + 8);
+      const size_t smem = cgk::prefill_attn_smem((int)hd, (int)Tt);
+      auto kern = hd == 64 ? cgk::attn_prefill_fused_kernel<64> : cgk::attn_prefill_fused_kernel<128>;
+      static size_t smem_set_dev[64][2] = {};
+      size_t& smem_set = smem_set_dev[m.be->device() & 63][hd == 64 ? 0 : 1];
+      if (smem > smem_set) {
+        CG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        smem_set = smem;
+      }
+      kern<<<dim3((unsigned)((S + cgk::PA_ROWS - 1) / cgk::PA_ROWS), (unsigned)nh, (unsigned)B), 128, smem, st>>>(a);
+      launched("attention(prefill, fused)");
+      return;
+    }
+    const int64_t Tp = score_pitch(Tt);  // row pitch of the score matrix
+    T* scores = (T*)m.scores.raw();
     bool tc = false;
     if (std::is_same<T, __nv_bfloat16>::value) {
       // tensor cores: scores[b, h] = Q[b, :, h, :] x K[b, h / rep]^T over 4-D tensor maps
@@ -736,6 +756,12 @@ struct Plan {
     cgk::bhsd_to_bshd_kernel<T><<<grid_for(B * nh * S * (hd / (16 / sizeof(T)))), 256, 0, st>>>(obhsd, attn_out, (int)B,
                                                                                               (int)nh, (int)S, (int)hd);
     launched("bhsd_to_bshd");
+  }
+
+  // bf16, head dimension 64 or 128, at most 1024 keys (the score rows of a 64-query tile stay in shared memory)
+  static bool fused_prefill_ok(const cg_llama& m, int64_t Tt) {
+    return std::is_same<T, __nv_bfloat16>::value && (m.hd == 64 || m.hd == 128) && Tt <= cgk::PA_MAX_KEYS &&
+           m.max_batch <= 65535 && m.cfg.num_attention_heads <= 65535;   // grid.y = heads, grid.z = sequences
   }
 
   // bf16 score rows are padded to a multiple of 16 bytes so that they can be tensor-map rows
@@ -848,7 +874,8 @@ void ensure_capacity(cg_llama& m, int64_t B, int64_t S) {
     m.attn_partial = m.be->empty({m.max_batch * nh * chunks_max * hd}, Dtype::F32);
     m.attn_counters = m.be->zeros({m.max_batch * c.num_key_value_heads}, Dtype::U32);
   }
-  if (S > 1) {
+  const bool fused_prefill = m.dt == Dtype::BF16 && Plan<__nv_bfloat16>::fused_prefill_ok(m, m.host_ctx_len + S);
+  if (S > 1 && !fused_prefill) {   // score matrix and [B, nh, S, hd] staging of the unfused prefill attention
     int64_t Tt = m.host_ctx_len + S;
     int64_t need = B * nh * S * ((Tt + 7) / 8 * 8);
     if (!m.scores.defined() || m.scores.size() < need) m.scores = m.be->empty({need}, m.dt);

@@ -149,6 +149,20 @@ def generate_with_interpreter(backend, term, params, cfg, prompt_ids, steps, dty
     return out_ids, logits
 
 
+def bench_table(model_name, size_gib, params_m, backend, pp, elapsed_pp_s, tg, elapsed_tg_s):
+    """The prompt-processing / token-generation table of the reference's benchmark mode, column for column
+    (catgrad-llm/src/utils/mod.rs:528-566): two rows, `pp<prompt tokens>` and `tg<generated tokens>`, tokens per second
+    to two decimals.  Returns the four lines."""
+    head = ("| model                                    | size       | params     | backend    |            test |"
+            "                  t/s |")
+    rule = ("| ---------------------------------------- | ---------- | ---------- | ---------- | --------------- |"
+            " -------------------- |")
+    rows = []
+    for label, n, secs in ((f"pp{pp}", pp, elapsed_pp_s), (f"tg{tg}", tg, elapsed_tg_s)):
+        rows.append(f"| {model_name:<40} | {size_gib:>6.2f} GiB | {params_m:>8.2f} M | {backend:<10} | {label:>15} | {n / secs:>20.2f} |")
+    return [head, rule] + rows
+
+
 class LlamaRunner:
     """Fused Llama plan with a device-resident KV cache (`cg_llama_*`)."""
 

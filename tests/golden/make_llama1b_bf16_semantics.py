@@ -3,13 +3,16 @@ how far the reference's own bf16 semantics (every op output rounded to bf16, can
 CPU oracle in bf16 mode) lands from the f32 evaluation of the same model (weights rounded to bf16 first), on the
 inputs tests/test_gpu_full_dims.py uses:
   1b   : Llama-3.2-1B shape, seed-0 weights, a 16-token prompt from seed 1, two decode steps fed with the f32 run's ids;
-  8b2l : Llama-3-8B dimensions at two layers, seed-3 weights, an 8-token prompt from seed 5, one decode step.
+  8b2l : Llama-3-8B dimensions at two layers, seed-3 weights, an 8-token prompt from seed 5, one decode step;
+  8b2l_tp : the same model on the inputs of the tensor-parallel worker (tests/tp_worker.py): rows 0 and 1 of its
+         32 x 16 prompt matrix (seed 21), three decode steps; per call the larger max-abs and the mean of the mean-abs of
+         the two sequences.
 
 The bf16 kernels are held to the f32 oracle with a bar derived from these figures, because at these sizes the 2e-2
 max-abs bar that holds for small models is out of reach for the reference semantics themselves.
 
 Run from the repository root (about 10 minutes of CPU, ~12 GB of RAM):
-    python tests/golden/make_llama1b_bf16_semantics.py [8b2l]
+    python tests/golden/make_llama1b_bf16_semantics.py [8b2l | 8b2l_tp]
 """
 import ctypes
 import gc
@@ -53,10 +56,13 @@ def main():
     so = os.path.join(ROOT, "oracle", "_build", "libndarray_ref.so")
     oracle = cb.Backend(_cdll=ctypes.CDLL(so), _prefix="ref_")
     which = sys.argv[1] if len(sys.argv) > 1 else "1b"
-    if which == "8b2l":
+    rows = 1
+    if which in ("8b2l", "8b2l_tp"):
         cfg = cb.LlamaConfig(4096, 14336, 2, 32, 8, 128256, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
         wseed, pseed, PROMPT, DECODE = 3, 5, 8, 1
         name, out_name = "Llama-3-8B dimensions, 2 layers", "llama8b2l_bf16_semantics.json"
+        if which == "8b2l_tp":
+            pseed, PROMPT, DECODE, rows, out_name = 21, 16, 3, 2, "llama8b2l_tp_bf16_semantics.json"
     else:
         cfg = cb.LLAMA_1B
         wseed, pseed = 0, 1
@@ -64,6 +70,28 @@ def main():
     w = cb.random_weights(cfg, seed=wseed)
     wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
     del w
+    if rows > 1:
+        # the worker draws a [32, PROMPT] matrix; its first `rows` rows are evaluated one sequence at a time
+        all_ids = np.random.default_rng(pseed).integers(0, cfg.vocab_size, size=(32, PROMPT), dtype=np.uint32)
+        per = []
+        for r in range(rows):
+            ids = all_ids[r:r + 1]
+            ids32, l32 = run(oracle, cfg, wb, Dtype.F32, ids, None)
+            ids16, l16 = run(oracle, cfg, wb, Dtype.BF16, ids, ids32)
+            per.append((ids32, ids16, l32, np.abs(l16 - l32)))
+        out = {
+            "model": f"{name}, seed-{wseed} N(0, 0.02) weights rounded to bf16, norm gains 1",
+            "prompt_seed": pseed, "prompt_len": PROMPT, "decode_steps": DECODE, "sequences": rows,
+            "f32_ids": [p[0] for p in per], "bf16_ids": [p[1] for p in per],
+            "logit_absmax": [float(max(np.abs(p[2][i]).max() for p in per)) for i in range(1 + DECODE)],
+            "bf16_vs_f32_max_abs": [float(max(p[3][i].max() for p in per)) for i in range(1 + DECODE)],
+            "bf16_vs_f32_mean_abs": [float(np.mean([p[3][i].mean() for p in per])) for i in range(1 + DECODE)],
+            "bf16_vs_f32_mean_abs_each": [[float(p[3][i].mean()) for i in range(1 + DECODE)] for p in per],
+        }
+        with open(os.path.join(ROOT, "tests", "golden", out_name), "w") as f:
+            json.dump(out, f, indent=1)
+        print(json.dumps(out, indent=1))
+        return
     ids = np.random.default_rng(pseed).integers(0, cfg.vocab_size, size=(1, PROMPT), dtype=np.uint32)
     ids32, l32 = run(oracle, cfg, wb, Dtype.F32, ids, None)
     ids16, l16 = run(oracle, cfg, wb, Dtype.BF16, ids, ids32)

@@ -480,3 +480,32 @@ def test_planned_bf16_decode_takes_the_persistent_kernel_and_handles_batches(gpu
     assert term.plan_state == 1
     runner = cb.LlamaRunner(gpu, cfg, pg, Dtype.BF16, max_batch=2, max_positions=64)
     np.testing.assert_array_equal(out, runner.generate(ids, 6))
+
+
+def test_safetensors_checkpoint_loads_onto_the_gpu(tmp_path, oracle, gpu):
+    """The loader (utils/mod.rs:321-449, dense-model part) feeding the CUDA backend: a sharded bf16 checkpoint is read
+    into device tensors (values exact), and the loaded model generates, through the fused runner and through the Llama
+    term in the interpreter, the ids the CPU oracle generates from the in-memory weights."""
+    from catgrad_b200 import safetensors as st
+    cfg = cb.TINY
+    w = cb.random_weights(cfg, seed=0)
+    keys = sorted(w)
+    half = len(keys) // 2
+    st.save_file(tmp_path / "model-00001-of-00002.safetensors", {k: w[k] for k in keys[:half]}, bf16=True)
+    st.save_file(tmp_path / "model-00002-of-00002.safetensors", {k: w[k] for k in keys[half:]}, bf16=True)
+    files = [str(tmp_path / f"model-0000{i}-of-00002.safetensors") for i in (1, 2)]
+    loaded, n = st.load_parameters(gpu, files, Dtype.F32)            # BF16 file -> f32 model: exact widening
+    assert n == cfg.num_params() and sorted(loaded.keys()) == keys
+    wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+    for k in keys:
+        np.testing.assert_array_equal(gpu.to_numpy(loaded[k]), wb[k])
+    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, size=(2, 8), dtype=np.uint32)
+    want = cb.generate_with_interpreter(oracle, cb.llama_term(oracle, cfg), cb.upload_weights(oracle, wb, Dtype.F32), cfg,
+                                        ids, 4, Dtype.F32, 16)[0]
+    runner = cb.LlamaRunner(gpu, cfg, loaded, Dtype.F32, max_batch=2, max_positions=16)
+    np.testing.assert_array_equal(runner.generate(ids, 4), want)
+    got = cb.generate_with_interpreter(gpu, cb.llama_term(gpu, cfg), loaded, cfg, ids, 4, Dtype.F32, 16)[0]
+    np.testing.assert_array_equal(got, want)
+    l16, _ = st.load_parameters(gpu, files, Dtype.BF16)              # kept as bf16 on the device
+    assert all(l16[k].dtype == Dtype.BF16 for k in keys)
+    np.testing.assert_array_equal(gpu.to_f32(l16[keys[0]]), wb[keys[0]])

@@ -246,3 +246,14 @@ def test_llama3_rope_scaling_term_equals_textbook_llama(oracle):
     assert helpers.rel_err(lg0[:, -1], lg[:, -1]) > 1e-4       # ten times the agreement asked for above
     with pytest.raises(ValueError):
         cb.LlamaConfig(128, 256, 2, 2, 1, 512, rope_scaling={"rope_type": "yarn", "factor": 4.0}).to_struct()
+
+
+def test_bench_table_has_the_reference_layout():
+    """print_bench_table (catgrad-llm/src/utils/mod.rs:528-566): header, rule, a pp row and a tg row; widths and
+    precision as the reference formats them."""
+    lines = cb.bench_table("llama-3.2-1b", 2.30, 1235.81, "b200", 512, 0.004, 128, 0.1)
+    assert len(lines) == 4 and len({len(x) for x in lines}) == 1
+    assert lines[0].startswith("| model ") and lines[0].endswith("t/s |") and set(lines[1]) <= set("| -")
+    cells = [c.strip() for c in lines[2].split("|")[1:-1]]
+    assert cells == ["llama-3.2-1b", "2.30 GiB", "1235.81 M", "b200", "pp512", "128000.00"]
+    assert [c.strip() for c in lines[3].split("|")[1:-1]][-2:] == ["tg128", "1280.00"]
