@@ -117,6 +117,44 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ in, 
   }
 }
 
+// Same with one warp per row and the row in registers (NV 16-byte vectors per lane, H = 32 * NV * (16 / sizeof(T))):
+// one pass over the row, every load of a lane in flight at once, no block-level synchronisation.
+template <class T, int NV>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const T* __restrict__ in, const T* __restrict__ gain,
+                                                           T* __restrict__ out, long long rows, float eps, long long row_mul,
+                                                           long long row_off) {
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int H = 32 * NV * VEC;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* x = in + (row * row_mul + row_off) * H;
+  T* y = out + row * H;
+  VecT<T, VEC> xv[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) xv[j] = *reinterpret_cast<const VecT<T, VEC>*>(x + (j * 32 + lane) * VEC);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const float v = Elem<T>::load(xv[j].v[i]);
+      ss += v * v;
+    }
+  ss = warp_sum(ss);
+  const float rms = sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const VecT<T, VEC> g = *reinterpret_cast<const VecT<T, VEC>*>(gain + (j * 32 + lane) * VEC);
+    VecT<T, VEC> o;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o.v[i] = Elem<T>::store(rt<T>(Elem<T>::load(xv[j].v[i]) / rms) * Elem<T>::load(g.v[i]));
+    *reinterpret_cast<VecT<T, VEC>*>(y + (j * 32 + lane) * VEC) = o;
+  }
+}
+
 // ---- weight-streaming GEMV with fused prologue/epilogue --------------------------------------------
 // out[m, n] = epilogue( sum_k xin[m, k] * W[n, k] ),  m < M <= MT, W rows K-contiguous (the [out,in] layout of
 // every linear layer, nn/mod.rs:182-204: x @ transpose(W) without ever forming the transpose or its broadcast).
@@ -827,7 +865,7 @@ __global__ void __launch_bounds__(128) attn_decode_group_kernel(AttnArgs a, unsi
   for (int h = 0; h < REP; ++h)
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[h][i] = 0.f;
-#pragma unroll 4
+#pragma unroll 16
   for (int t = g; t < pos; t += KG) {
     const uint4 vv = *reinterpret_cast<const uint4*>(vc + (long long)t * HD + c * 8);
     const T* e = reinterpret_cast<const T*>(&vv);
@@ -1456,10 +1494,30 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const T* __restrict
   const T* x = logits + (long long)row * row_stride;
   const int lo = chunk * ARGMAX_CHUNK, hi = min(n, lo + ARGMAX_CHUNK);
   unsigned long long best = 0ull;
-  for (int i = lo + threadIdx.x; i < hi; i += 256) {
-    unsigned hiw = (unsigned)total_key(Elem<T>::load(x[i])) ^ 0x80000000u;
-    unsigned long long key = ((unsigned long long)hiw << 32) | (unsigned)i;
-    best = key > best ? key : best;
+  constexpr int VEC = 16 / sizeof(T);
+  if (((uintptr_t)logits & 15) == 0 && row_stride % VEC == 0) {
+    // 16-byte loads over the whole vectors of the chunk (chunk starts are multiples of 4096 elements)
+    const int nvec = (hi - lo) / VEC;
+    for (int v = threadIdx.x; v < nvec; v += 256) {
+      const VecT<T, VEC> in = *reinterpret_cast<const VecT<T, VEC>*>(x + lo + v * VEC);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        unsigned hiw = (unsigned)total_key(Elem<T>::load(in.v[e])) ^ 0x80000000u;
+        unsigned long long key = ((unsigned long long)hiw << 32) | (unsigned)(lo + v * VEC + e);
+        best = key > best ? key : best;
+      }
+    }
+    for (int i = lo + nvec * VEC + threadIdx.x; i < hi; i += 256) {
+      unsigned hiw = (unsigned)total_key(Elem<T>::load(x[i])) ^ 0x80000000u;
+      unsigned long long key = ((unsigned long long)hiw << 32) | (unsigned)i;
+      best = key > best ? key : best;
+    }
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += 256) {
+      unsigned hiw = (unsigned)total_key(Elem<T>::load(x[i])) ^ 0x80000000u;
+      unsigned long long key = ((unsigned long long)hiw << 32) | (unsigned)i;
+      best = key > best ? key : best;
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -1495,29 +1553,41 @@ __global__ void __launch_bounds__(256) ids_from_partials_kernel(const unsigned l
 }
 
 // End of a step: stage 2 of the greedy pick, then the new ids become the next step's input, are recorded for
-// the host, and the context length advances.  One CTA; warp w handles rows w, w+8, ...
-__global__ void __launch_bounds__(256) advance_kernel(const unsigned long long* __restrict__ partials, int chunks,
-                                                      unsigned* __restrict__ cur_ids, unsigned* __restrict__ out_ids,
-                                                      int* ctx_len, int* step_no, int B, int S, int out_cap_steps) {
+// the host, and the context length advances.  One CTA of 32 warps (one writer of the two step counters); a warp takes
+// rows in groups of eight and issues the loads of a whole group before it reduces any of them, so the kernel costs a
+// few dependent memory round trips however many rows there are.
+constexpr int ADVANCE_THREADS = 1024;
+__global__ void __launch_bounds__(ADVANCE_THREADS) advance_kernel(const unsigned long long* __restrict__ partials, int chunks,
+                                                                  unsigned* __restrict__ cur_ids, unsigned* __restrict__ out_ids,
+                                                                  int* ctx_len, int* step_no, int B, int S, int out_cap_steps) {
   pdl_launch_dependents();
   pdl_wait();
   const int step = *step_no;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int b = warp; b < B; b += 8) {
-    unsigned long long best = 0ull;
-    for (int c = lane; c < chunks; c += 32) {
-      unsigned long long k = partials[(long long)b * chunks + c];
-      best = k > best ? k : best;
+  constexpr int WARPS = ADVANCE_THREADS / 32, GROUP = 8;
+  for (int b0 = warp * GROUP; b0 < B; b0 += WARPS * GROUP) {
+    unsigned long long best[GROUP];
+#pragma unroll
+    for (int j = 0; j < GROUP; ++j) {
+      best[j] = 0ull;
+      if (b0 + j < B)
+        for (int c = lane; c < chunks; c += 32) {
+          unsigned long long k = partials[(long long)(b0 + j) * chunks + c];
+          best[j] = k > best[j] ? k : best[j];
+        }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
-      best = other > best ? other : best;
-    }
-    if (lane == 0) {
-      unsigned id = (unsigned)(best & 0xffffffffull);
-      cur_ids[b] = id;
-      if (step < out_cap_steps) out_ids[(long long)step * B + b] = id;
+    for (int j = 0; j < GROUP; ++j) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        unsigned long long other = __shfl_xor_sync(0xffffffffu, best[j], o);
+        best[j] = other > best[j] ? other : best[j];
+      }
+      if (lane == 0 && b0 + j < B) {
+        unsigned id = (unsigned)(best[j] & 0xffffffffull);
+        cur_ids[b0 + j] = id;
+        if (step < out_cap_steps) out_ids[(long long)step * B + b0 + j] = id;
+      }
     }
   }
   __syncthreads();
