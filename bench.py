@@ -46,6 +46,8 @@ HBM_NOMINAL_GBS = 8000.0
 # DRAM bytes per step from ncu captures (constants, not measured in this run).  Batch 1, kernel-per-sub-graph plan:
 # (8.44 + 67.18 + 33.62 + 12.66) MB x 16 layers + 525.3 MB lm_head, measured per launch.
 TRAFFIC_PER_STEP_B1 = int((8.44e6 + 67.18e6 + 33.62e6 + 12.66e6) * 16 + 525.3e6)
+# batch 1, persistent kernel: one captured launch of 4 steps at context ~520 read 9 964 379 904 B and wrote 77 484 544 B
+TRAFFIC_PER_STEP_B1_PERSISTENT = (9964379904 + 77484544) // 4
 # batch 256 on one GPU: per layer [q;k;v] 12.73 + o_proj 8.67 + down_proj 34.23 MB (ncu, split-K summary), [gate;up]
 # 67.11 MB and lm_head 525.3 MB (not captured: their weight bytes), attention 70.1 MB (ncu, context ~135)
 TRAFFIC_PER_STEP_C4 = int((12.73e6 + 8.67e6 + 34.23e6 + 67.11e6 + 70.1e6) * 16 + 525.3e6)
@@ -499,7 +501,8 @@ def main():
         kernel = "one decode step = 65 gemv_fused_kernel launches (79 % of the device time) + attention + greedy pick"
     else:
         kernel = "one decode step = 64 gemm_tcgen05 launches (62 % of the device time) + attention + norms + greedy pick"
-    traffic = (TRAFFIC_PER_STEP_B1 if (batch_total == 1 and workload == "c3" and not r["persistent"]) else
+    traffic = ((TRAFFIC_PER_STEP_B1_PERSISTENT if r["persistent"] else TRAFFIC_PER_STEP_B1)
+               if (batch_total == 1 and workload == "c3" and not args.prompt) else
                TRAFFIC_PER_STEP_C4 if (workload == "c4" and batch == 256 and not args.prompt) else None)
     line = {
         "metric": "decode tokens/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
@@ -551,7 +554,9 @@ def main():
                                    "achieved": a3, "peak": hbm_peak,
                                    "unit": "GB/s", "frac": a3 / hbm_peak, "peak_source": peak_src,
                                    "frac_of_8TBs_nominal": a3 / HBM_NOMINAL_GBS, "bytes_per_step": b3,
-                                   "traffic": None if r3["persistent"] else TRAFFIC_PER_STEP_B1}}
+                                   "traffic": TRAFFIC_PER_STEP_B1_PERSISTENT if r3["persistent"] else TRAFFIC_PER_STEP_B1,
+                                   "traffic_how": "constant from one ncu capture of this kernel (dram__bytes_read.sum + "
+                                                  "dram__bytes_write.sum per step); not measured in this run"}}
         if not args.no_interpreter_path:
             line["c3"]["interpreter_path"] = interpreter_path_tok_s(be, cfg, params)
         # the same two figures in the reference benchmark mode's own table (stderr: stdout carries the one JSON line)
