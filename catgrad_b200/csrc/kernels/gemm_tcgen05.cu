@@ -230,6 +230,71 @@ __device__ __forceinline__ uint32_t add_res2(float a0, float a1, uint32_t r) {
   return *reinterpret_cast<const uint32_t*>(&o);
 }
 
+// Split-K reduction of one CTA's share of a tile: rows [z * rows_per, (z + 1) * rows_per) of the f32 partial tiles that
+// the Z CTAs of the cluster parked in their shared memory (row r at r * (BN + 4) floats), summed in rank order, rounded
+// once, residual added, stored.  128 threads (warps 2..5); U items (4 columns each) per thread are in flight at once.
+struct ReduceArgs {
+  __nv_bfloat16* C;
+  const __nv_bfloat16* res;
+  int ldc, M, N, m0, n0, z, rows_valid, rows_per;
+};
+template <int BN, int Z, int U>
+__device__ __forceinline__ void splitk_reduce(const ReduceArgs& a, const float* park) {
+  const int t = threadIdx.x - 64;  // 0..127
+  const bool vec_ok = (a.ldc % 4 == 0) && (((uintptr_t)a.C & 7) == 0) && (((uintptr_t)a.res & 7) == 0);
+  const int items = a.rows_per * (BN / 4);
+  for (int base = t; base < items; base += 128 * U) {
+    float4 part[U][Z];
+    uint2 rv[U];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int item = base + u * 128;
+      const int rr = a.z * a.rows_per + item / (BN / 4), c4 = (item % (BN / 4)) * 4;
+      live[u] = item < items && rr < a.rows_valid;
+      rv[u] = make_uint2(0u, 0u);
+      if (live[u]) {
+        const float* src = park + (size_t)rr * (BN + 4) + c4;
+#pragma unroll
+        for (int pz = 0; pz < Z; ++pz) part[u][pz] = ld_cluster_f4(src, (unsigned)pz);
+        const int row = a.m0 + rr, col = a.n0 + c4;
+        if (a.res && vec_ok && row < a.M && col + 4 <= a.N)
+          rv[u] = *reinterpret_cast<const uint2*>(a.res + (long long)row * a.ldc + col);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!live[u]) continue;
+      const int item = base + u * 128;
+      const int rr = a.z * a.rows_per + item / (BN / 4), c4 = (item % (BN / 4)) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int pz = 0; pz < Z; ++pz) { acc.x += part[u][pz].x; acc.y += part[u][pz].y; acc.z += part[u][pz].z; acc.w += part[u][pz].w; }
+      const int row = a.m0 + rr, col = a.n0 + c4;
+      if (row < a.M && col < a.N) {
+        __nv_bfloat16* dst = a.C + (long long)row * a.ldc + col;
+        const __nv_bfloat16* rsrc = a.res ? a.res + (long long)row * a.ldc + col : nullptr;
+        if (vec_ok && col + 4 <= a.N) {
+          if (rsrc) {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(add_res2(acc.x, acc.y, rv[u].x), add_res2(acc.z, acc.w, rv[u].y));
+          } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          }
+        } else {
+          const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+          for (int j = 0; j < 4; ++j)
+            if (col + j < a.N) {
+              __nv_bfloat16 o = __float2bfloat16_rn(a4[j]);
+              if (rsrc) o = __float2bfloat16_rn(__bfloat162float(rsrc[j]) + __bfloat162float(o));
+              dst[j] = o;
+            }
+        }
+      }
+    }
+  }
+}
+
 // grid: (ceil(N/BN), ceil(M/BM), batch).  BMODE: 0 = one product, 1/2 = see BatchGeom.  B_MN: the right
 // operand is stored [K, N] with N contiguous (tensor map dims {N, K}); otherwise [N, K] with K contiguous.
 // SPLITK (BMODE 0 only): launched as clusters of gridDim.z CTAs along z; CTA z of a cluster accumulates k-blocks
@@ -457,43 +522,13 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
     const int rows_valid = M - m0 < BM ? M - m0 : BM;   // rows of this tile that exist
     const int rows_per = (rows_valid + Z - 1) / Z;      // CTA z reduces rows [z * rows_per, (z + 1) * rows_per)
     if (warp >= 2 && !*abort_flag) {
-      const int t = threadIdx.x - 64;  // 0..127
-      const bool vec_ok = (g.ldc % 4 == 0) && (((uintptr_t)C & 7) == 0);
-      for (int item = t; item < rows_per * (BN / 4); item += 128) {
-        const int rr = bz * rows_per + item / (BN / 4), c4 = (item % (BN / 4)) * 4;
-        if (rr >= rows_valid) break;
-        const float* src = reinterpret_cast<const float*>(smem) + (size_t)rr * (BN + 4) + c4;
-        float4 part[8];
-#pragma unroll
-        for (int pz = 0; pz < 8; ++pz)
-          if (pz < Z) part[pz] = ld_cluster_f4(src, (unsigned)pz);   // all loads issued before the first use
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int pz = 0; pz < 8; ++pz)
-          if (pz < Z) { acc.x += part[pz].x; acc.y += part[pz].y; acc.z += part[pz].z; acc.w += part[pz].w; }
-        const int row = m0 + rr, col = n0 + c4;
-        if (row < M && col < N) {
-          __nv_bfloat16* dst = C + (long long)row * g.ldc + col;
-          const __nv_bfloat16* rsrc = g.res ? g.res + (long long)row * g.ldc + col : nullptr;
-          if (vec_ok && col + 4 <= N && (((uintptr_t)g.res & 7) == 0)) {
-            if (rsrc) {
-              const uint2 rv = *reinterpret_cast<const uint2*>(rsrc);
-              *reinterpret_cast<uint2*>(dst) = make_uint2(add_res2(acc.x, acc.y, rv.x), add_res2(acc.z, acc.w, rv.y));
-            } else {
-              __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-              *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-            }
-          } else {
-            const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
-            for (int j = 0; j < 4; ++j)
-              if (col + j < N) {
-                __nv_bfloat16 o = __float2bfloat16_rn(a4[j]);
-                if (rsrc) o = __float2bfloat16_rn(__bfloat162float(rsrc[j]) + __bfloat162float(o));
-                dst[j] = o;
-              }
-          }
-        }
-      }
+      // each loop iteration costs a distributed-shared-memory round trip plus a global one (the residual): several
+      // items are kept in flight per thread, as many as fit 16 float4 of partials
+      const ReduceArgs ra{C, g.res, g.ldc, M, N, m0, n0, bz, rows_valid, rows_per};
+      const float* park = reinterpret_cast<const float*>(smem);
+      if (Z == 2) splitk_reduce<BN, 2, 8>(ra, park);
+      else if (Z == 4) splitk_reduce<BN, 4, 4>(ra, park);
+      else splitk_reduce<BN, 8, 2>(ra, park);
     }
     cluster_sync_all();  // peers may still be reading this CTA's partial tile
   }
