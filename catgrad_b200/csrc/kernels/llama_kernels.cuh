@@ -750,6 +750,100 @@ __global__ void __launch_bounds__(256) attn_decode_warp_kernel(AttnArgs a, unsig
   *reinterpret_cast<VecT<T, DPL>*>((T*)a.out + (long long)b * a.out_row_stride + h * HD + d0) = ov;
 }
 
+// ---- decode-attention scores on the tensor cores ------------------------------------------------------------------
+// scores[h, t] = T(T(q[h] . k[t]) / scale) for the REP (<= 8) query heads of one kv head and the cached keys of the
+// 32-key blocks blk0, blk0 + blk_step, ... below `pos`, written to p_s[h * pp + t]; the running maximum per head comes
+// back in mx.  mma.sync.m16n8k16: the query heads are rows 0..REP-1 of the A operand (rows up to 15 are zero), eight
+// keys are the columns of B, whose fragments are read straight from the key rows in global memory with 16-byte loads.
+// The key of the current position (k_new, still in shared memory) is dotted by the whole warp when
+// `owns_new`.  Against the FMA form this takes a fifth of the issue slots and has no dependent 64-long FMA chains.
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <int HD, int REP>
+__device__ __forceinline__ void decode_scores_mma(const float* q_s, const __nv_bfloat16* kc, const __nv_bfloat16* k_new, int pos,
+                                                  int blk0, int blk_step, bool owns_new, float* p_s, int pp, float scale,
+                                                  float (&mx)[REP]) {
+  static_assert(REP <= 8, "the query heads of a group are rows 0..7 of the A fragment");
+  using T = __nv_bfloat16;
+  constexpr int KS = HD / 16;
+  constexpr int NBU = HD <= 64 ? 4 : 2;   // 8-key column blocks whose loads are in flight together
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  // A dot product does not care in which order the head dimension is walked, as long as both operands agree: lane t of
+  // a quad takes the 16-byte chunks t, t + 4, ... of a key row (two 16-byte loads per 64 elements instead of eight
+  // 4-byte ones, whole sectors per request), and k-step ks multiplies words 2ks and 2ks + 1 of what it holds.  The
+  // query fragment is packed from the same elements: word m = 4j + i of lane t is elements 8t + 32j + 2i, + 1.
+  uint32_t qa0[KS], qa2[KS];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    qa0[ks] = 0u;
+    qa2[ks] = 0u;
+    if (g < REP) {   // q_s holds values already rounded to T: the packing is exact
+      const float* qrow = q_s + g * HD + 8 * t + 32 * (ks / 2) + 4 * (ks % 2);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(qrow[0], qrow[1]), hi = __floats2bfloat162_rn(qrow[2], qrow[3]);
+      qa0[ks] = *reinterpret_cast<uint32_t*>(&lo);
+      qa2[ks] = *reinterpret_cast<uint32_t*>(&hi);
+    }
+  }
+  float mxl = -FLT_MAX;
+  for (int blk = blk0; blk * 32 < pos; blk += blk_step) {
+#pragma unroll
+    for (int nb0 = 0; nb0 < 4; nb0 += NBU) {
+      uint32_t bf[NBU][KS][2];
+#pragma unroll
+      for (int u = 0; u < NBU; ++u) {
+        const int key = blk * 32 + (nb0 + u) * 8 + g;
+        const bool valid = key < pos;
+        const uint4* row = reinterpret_cast<const uint4*>(kc + (long long)(valid ? key : 0) * HD);
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) {
+          const uint4 w = valid ? row[t + 4 * j] : make_uint4(0u, 0u, 0u, 0u);
+          bf[u][2 * j][0] = w.x;
+          bf[u][2 * j][1] = w.y;
+          bf[u][2 * j + 1][0] = w.z;
+          bf[u][2 * j + 1][1] = w.w;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < NBU; ++u) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) mma_bf16_16816(c, qa0[ks], 0u, qa2[ks], 0u, bf[u][ks][0], bf[u][ks][1]);
+        if (g < REP) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = blk * 32 + (nb0 + u) * 8 + t * 2 + e;
+            if (key < pos) {
+              const float sres = rt<T>(rt<T>(c[e]) / scale);
+              p_s[g * pp + key] = sres;
+              mxl = fmaxf(mxl, sres);
+            }
+          }
+        }
+      }
+    }
+  }
+  mxl = fmaxf(mxl, __shfl_xor_sync(0xffffffffu, mxl, 1));
+  mxl = fmaxf(mxl, __shfl_xor_sync(0xffffffffu, mxl, 2));
+#pragma unroll
+  for (int h = 0; h < REP; ++h) mx[h] = g == h ? mxl : -FLT_MAX;
+  if (owns_new) {
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      float d = 0.f;
+      for (int i = lane; i < HD; i += 32) d = fmaf(q_s[h * HD + i], __bfloat162float(k_new[i]), d);
+      d = warp_sum(d);
+      const float sres = rt<T>(rt<T>(d) / scale);
+      if (lane == 0) p_s[h * pp + pos] = sres;
+      mx[h] = fmaxf(mx[h], sres);
+    }
+  }
+  __syncwarp();   // the scores were written by other lanes than those that read them next
+}
+
 // ---- decode attention for very many sequences: one warp per (kv head, sequence), all its query heads --------
 // Same sub-graph and rounding points again.  Each K row is loaded once into registers and dotted with the REP query
 // heads of the group; in the P.v pass a lane owns 8 head-dim elements of every (32 / (HD/8))-th key, so every load
@@ -813,37 +907,9 @@ __global__ void __launch_bounds__(128) attn_decode_group_kernel(AttnArgs a, unsi
   }
   __syncwarp();
 
-  // scores: lane = key; the row stays in registers for all REP heads
+  // scores on the tensor cores (all cached keys, then the new one)
   float mx[REP];
-#pragma unroll
-  for (int h = 0; h < REP; ++h) mx[h] = -FLT_MAX;
-  for (int t = lane; t < total; t += 32) {
-    const uint4* krow = reinterpret_cast<const uint4*>(t == pos ? k_new : kc + (long long)t * HD);
-    uint4 kr[CH];
-#pragma unroll
-    for (int c = 0; c < CH; ++c) kr[c] = krow[c];
-#pragma unroll
-    for (int h = 0; h < REP; ++h) {
-      float d = 0.f;
-#pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        const T* e = reinterpret_cast<const T*>(&kr[c]);
-        const float4 qa = *reinterpret_cast<const float4*>(q_s + h * HD + c * 8);
-        const float4 qb = *reinterpret_cast<const float4*>(q_s + h * HD + c * 8 + 4);
-        d = fmaf(qa.x, Elem<T>::load(e[0]), d);
-        d = fmaf(qa.y, Elem<T>::load(e[1]), d);
-        d = fmaf(qa.z, Elem<T>::load(e[2]), d);
-        d = fmaf(qa.w, Elem<T>::load(e[3]), d);
-        d = fmaf(qb.x, Elem<T>::load(e[4]), d);
-        d = fmaf(qb.y, Elem<T>::load(e[5]), d);
-        d = fmaf(qb.z, Elem<T>::load(e[6]), d);
-        d = fmaf(qb.w, Elem<T>::load(e[7]), d);
-      }
-      const float sres = rt<T>(rt<T>(d) / a.scale);
-      p_s[h * pp + t] = sres;
-      mx[h] = fmaxf(mx[h], sres);
-    }
-  }
+  decode_scores_mma<HD, REP>(q_s, kc, k_new, pos, 0, 1, true, p_s, pp, a.scale, mx);
 #pragma unroll
   for (int h = 0; h < REP; ++h) {
     const float m = warp_max(mx[h]);
@@ -971,37 +1037,9 @@ __global__ void __launch_bounds__(128) attn_decode_pair_kernel(AttnArgs a, unsig
     }
   }
   pair_barrier(pair);
-  // scores: lane = key, keys pl, pl + 64, ...
+  // scores on the tensor cores: this warp's 32-key blocks hw, hw + 2, ...; the new key goes to the warp whose block holds it
   float mx[REP];
-#pragma unroll
-  for (int h = 0; h < REP; ++h) mx[h] = -FLT_MAX;
-  for (int t = pl; t < total; t += 64) {
-    const uint4* krow = reinterpret_cast<const uint4*>(t == pos ? k_new : kc + (long long)t * HD);
-    uint4 kr[CH];
-#pragma unroll
-    for (int c = 0; c < CH; ++c) kr[c] = krow[c];
-#pragma unroll
-    for (int h = 0; h < REP; ++h) {
-      float d = 0.f;
-#pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        const T* e = reinterpret_cast<const T*>(&kr[c]);
-        const float4 qa = *reinterpret_cast<const float4*>(q_s + h * HD + c * 8);
-        const float4 qb = *reinterpret_cast<const float4*>(q_s + h * HD + c * 8 + 4);
-        d = fmaf(qa.x, Elem<T>::load(e[0]), d);
-        d = fmaf(qa.y, Elem<T>::load(e[1]), d);
-        d = fmaf(qa.z, Elem<T>::load(e[2]), d);
-        d = fmaf(qa.w, Elem<T>::load(e[3]), d);
-        d = fmaf(qb.x, Elem<T>::load(e[4]), d);
-        d = fmaf(qb.y, Elem<T>::load(e[5]), d);
-        d = fmaf(qb.z, Elem<T>::load(e[6]), d);
-        d = fmaf(qb.w, Elem<T>::load(e[7]), d);
-      }
-      const float sres = rt<T>(rt<T>(d) / a.scale);
-      p_s[h * pp + t] = sres;
-      mx[h] = fmaxf(mx[h], sres);
-    }
-  }
+  decode_scores_mma<HD, REP>(q_s, kc, k_new, pos, hw, 2, ((pos >> 5) & 1) == hw, p_s, pp, a.scale, mx);
 #pragma unroll
   for (int h = 0; h < REP; ++h) {
     const float m = warp_max(mx[h]);
