@@ -763,7 +763,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-template <int HD, int REP>
+template <int HD, int REP, int BLKS>
 __device__ __forceinline__ void decode_scores_mma(const float* q_s, const __nv_bfloat16* kc, const __nv_bfloat16* k_new, int pos,
                                                   int blk0, int blk_step, bool owns_new, float* p_s, int pp, float scale,
                                                   float (&mx)[REP]) {
@@ -789,41 +789,48 @@ __device__ __forceinline__ void decode_scores_mma(const float* q_s, const __nv_b
     }
   }
   float mxl = -FLT_MAX;
-  for (int blk = blk0; blk * 32 < pos; blk += blk_step) {
+  // BLKS blocks of 32 keys per round, the 16-byte loads of a whole round issued before its first product: the phase
+  // is bound by the number of dependent memory round trips, not by arithmetic (measured at 256 sequences, context
+  // ~140: two blocks per round -3.5 % of the step with one warp per pair; no gain with two warps per pair)
+  for (int blk = blk0; blk * 32 < pos; blk += BLKS * blk_step) {
 #pragma unroll
     for (int nb0 = 0; nb0 < 4; nb0 += NBU) {
-      uint32_t bf[NBU][KS][2];
+      uint32_t bf[BLKS][NBU][KS][2];
 #pragma unroll
-      for (int u = 0; u < NBU; ++u) {
-        const int key = blk * 32 + (nb0 + u) * 8 + g;
-        const bool valid = key < pos;
-        const uint4* row = reinterpret_cast<const uint4*>(kc + (long long)(valid ? key : 0) * HD);
+      for (int sb = 0; sb < BLKS; ++sb)
 #pragma unroll
-        for (int j = 0; j < HD / 32; ++j) {
-          const uint4 w = valid ? row[t + 4 * j] : make_uint4(0u, 0u, 0u, 0u);
-          bf[u][2 * j][0] = w.x;
-          bf[u][2 * j][1] = w.y;
-          bf[u][2 * j + 1][0] = w.z;
-          bf[u][2 * j + 1][1] = w.w;
+        for (int u = 0; u < NBU; ++u) {
+          const int key = (blk + sb * blk_step) * 32 + (nb0 + u) * 8 + g;
+          const bool valid = key < pos;
+          const uint4* row = reinterpret_cast<const uint4*>(kc + (long long)(valid ? key : 0) * HD);
+#pragma unroll
+          for (int j = 0; j < HD / 32; ++j) {
+            const uint4 w = valid ? row[t + 4 * j] : make_uint4(0u, 0u, 0u, 0u);
+            bf[sb][u][2 * j][0] = w.x;
+            bf[sb][u][2 * j][1] = w.y;
+            bf[sb][u][2 * j + 1][0] = w.z;
+            bf[sb][u][2 * j + 1][1] = w.w;
+          }
         }
-      }
 #pragma unroll
-      for (int u = 0; u < NBU; ++u) {
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int sb = 0; sb < BLKS; ++sb)
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) mma_bf16_16816(c, qa0[ks], 0u, qa2[ks], 0u, bf[u][ks][0], bf[u][ks][1]);
-        if (g < REP) {
+        for (int u = 0; u < NBU; ++u) {
+          float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int key = blk * 32 + (nb0 + u) * 8 + t * 2 + e;
-            if (key < pos) {
-              const float sres = rt<T>(rt<T>(c[e]) / scale);
-              p_s[g * pp + key] = sres;
-              mxl = fmaxf(mxl, sres);
+          for (int ks = 0; ks < KS; ++ks) mma_bf16_16816(c, qa0[ks], 0u, qa2[ks], 0u, bf[sb][u][ks][0], bf[sb][u][ks][1]);
+          if (g < REP) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int key = (blk + sb * blk_step) * 32 + (nb0 + u) * 8 + t * 2 + e;
+              if (key < pos) {
+                const float sres = rt<T>(rt<T>(c[e]) / scale);
+                p_s[g * pp + key] = sres;
+                mxl = fmaxf(mxl, sres);
+              }
             }
           }
         }
-      }
     }
   }
   mxl = fmaxf(mxl, __shfl_xor_sync(0xffffffffu, mxl, 1));
@@ -909,7 +916,7 @@ __global__ void __launch_bounds__(128) attn_decode_group_kernel(AttnArgs a, unsi
 
   // scores on the tensor cores (all cached keys, then the new one)
   float mx[REP];
-  decode_scores_mma<HD, REP>(q_s, kc, k_new, pos, 0, 1, true, p_s, pp, a.scale, mx);
+  decode_scores_mma<HD, REP, (HD <= 64 ? 2 : 1)>(q_s, kc, k_new, pos, 0, 1, true, p_s, pp, a.scale, mx);
 #pragma unroll
   for (int h = 0; h < REP; ++h) {
     const float m = warp_max(mx[h]);
@@ -1039,7 +1046,7 @@ __global__ void __launch_bounds__(128) attn_decode_pair_kernel(AttnArgs a, unsig
   pair_barrier(pair);
   // scores on the tensor cores: this warp's 32-key blocks hw, hw + 2, ...; the new key goes to the warp whose block holds it
   float mx[REP];
-  decode_scores_mma<HD, REP>(q_s, kc, k_new, pos, hw, 2, ((pos >> 5) & 1) == hw, p_s, pp, a.scale, mx);
+  decode_scores_mma<HD, REP, 1>(q_s, kc, k_new, pos, hw, 2, ((pos >> 5) & 1) == hw, p_s, pp, a.scale, mx);
 #pragma unroll
   for (int h = 0; h < REP; ++h) {
     const float m = warp_max(mx[h]);
