@@ -240,6 +240,10 @@ struct Plan {
         case 8: rmsnorm_rows<8>(in, gain, out, rows, row_mul, row_off); break;
         default: rmsnorm_rows<16>(in, gain, out, rows, row_mul, row_off); break;
       }
+    } else if (aligned && H % (16 / (int64_t)sizeof(T)) == 0 && H / (16 / (int64_t)sizeof(T)) <= 1024) {
+      // one CTA per row, the row in registers, 16-byte accesses
+      launch(cgk::rmsnorm_vec_kernel<T>, dim3((unsigned)rows), dim3(256), 0, (const T*)in, (const T*)gain, (T*)out, (int)H,
+             m.cfg.rms_norm_eps, (long long)row_mul, (long long)row_off);
     } else {
       launch(cgk::rmsnorm_kernel<T>, dim3((unsigned)rows), dim3(256), 0, (const T*)in, (const T*)gain, (T*)out, (int)H,
              m.cfg.rms_norm_eps, (long long)row_mul, (long long)row_off);

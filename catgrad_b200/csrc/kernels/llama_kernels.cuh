@@ -117,6 +117,48 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ in, 
   }
 }
 
+// Same with the row in registers and 16-byte accesses: thread t of the CTA owns vectors t, t + 256, ... (at most four:
+// rows of up to 1024 vectors), one load and one store per vector instead of two passes of scalar loads.
+template <class T>
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const T* __restrict__ in, const T* __restrict__ gain,
+                                                          T* __restrict__ out, int H, float eps, long long row_mul,
+                                                          long long row_off) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ float scratch[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const T* x = in + ((long long)blockIdx.x * row_mul + row_off) * H;
+  T* y = out + (long long)blockIdx.x * H;
+  const int nvec = H / VEC;
+  VecT<T, VEC> xv[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int v = threadIdx.x + j * 256;
+    if (v < nvec) {
+      xv[j] = *reinterpret_cast<const VecT<T, VEC>*>(x + v * VEC);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float f = Elem<T>::load(xv[j].v[i]);
+        ss += f * f;
+      }
+    }
+  }
+  ss = block_sum_256(ss, scratch);
+  const float rms = sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int v = threadIdx.x + j * 256;
+    if (v < nvec) {
+      const VecT<T, VEC> g = *reinterpret_cast<const VecT<T, VEC>*>(gain + v * VEC);
+      VecT<T, VEC> o;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o.v[i] = Elem<T>::store(rt<T>(Elem<T>::load(xv[j].v[i]) / rms) * Elem<T>::load(g.v[i]));
+      *reinterpret_cast<VecT<T, VEC>*>(y + v * VEC) = o;
+    }
+  }
+}
+
 // Same with one warp per row and the row in registers (NV 16-byte vectors per lane, H = 32 * NV * (16 / sizeof(T))):
 // one pass over the row, every load of a lane in flight at once, no block-level synchronisation.
 template <class T, int NV>
