@@ -39,6 +39,40 @@ class LlamaConfig:
     def head_dim(self):
         return self.hidden_size // self.num_attention_heads
 
+    @classmethod
+    def from_hf_config(cls, config):
+        """From a checkpoint's config.json (a path or the parsed dict), the fields the reference deserialises for Llama
+        (catgrad-llm-models/src/models/llama.rs:9-27, config.rs:10-49).  Features of that struct the Llama term here does
+        not implement are refused rather than ignored: NoPE layer intervals, partial rotary factors other than 1,
+        yarn / longrope scaling, quantised checkpoints."""
+        import json
+        if not isinstance(config, dict):
+            with open(config) as f:
+                config = json.load(f)
+        if config.get("no_rope_layer_interval", 0):
+            raise ValueError("no_rope_layer_interval is not implemented")
+        if float(config.get("partial_rotary_factor", 1.0)) != 1.0:
+            raise ValueError("partial_rotary_factor other than 1.0 is not implemented")
+        if config.get("quantization_config"):
+            raise ValueError("quantised checkpoints are not implemented")
+        scaling = config.get("rope_scaling")
+        if scaling is not None:
+            kind = scaling.get("rope_type", scaling.get("type"))
+            if kind != "llama3":
+                raise ValueError(f"rope_scaling type {kind!r} is not implemented (only 'llama3')")
+            scaling = {k: scaling[k] for k in ("factor", "low_freq_factor", "high_freq_factor",
+                                               "original_max_position_embeddings")}
+            scaling["rope_type"] = "llama3"
+        heads = int(config["num_attention_heads"])
+        cfg = cls(hidden_size=int(config["hidden_size"]), intermediate_size=int(config["intermediate_size"]),
+                  num_hidden_layers=int(config["num_hidden_layers"]), num_attention_heads=heads,
+                  num_key_value_heads=int(config.get("num_key_value_heads", heads)), vocab_size=int(config["vocab_size"]),
+                  rope_theta=float(config.get("rope_theta", 10000.0)), rms_norm_eps=float(config["rms_norm_eps"]),
+                  tie_word_embeddings=bool(config.get("tie_word_embeddings", False)), rope_scaling=scaling)
+        if "head_dim" in config and int(config["head_dim"]) != cfg.head_dim:
+            raise ValueError("head_dim other than hidden_size / num_attention_heads is not implemented")
+        return cfg
+
     def to_struct(self):
         rs = self.rope_scaling
         if rs is None:

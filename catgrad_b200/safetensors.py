@@ -91,6 +91,24 @@ def load_parameters(backend, paths, dtype):
     return params, total
 
 
+def load_model(backend, directory, dtype):
+    """A checkpoint directory in the Hugging Face layout (config.json + *.safetensors, sharded or not) ->
+    (LlamaConfig, Parameters, element count): what `get_model_files` + `load_model` hand the runner
+    (catgrad-llm/src/utils/mod.rs:321-470), for the dense Llama family."""
+    import glob
+    import os
+    from .llama import LlamaConfig
+    cfg = LlamaConfig.from_hf_config(os.path.join(directory, "config.json"))
+    files = sorted(glob.glob(os.path.join(directory, "*.safetensors")))
+    if not files:
+        raise SafetensorsError(f"no .safetensors file in {directory}")
+    params, n = load_parameters(backend, files, dtype)
+    missing = [k for k, _ in cfg.param_shapes() if k not in params.keys()]
+    if missing:
+        raise SafetensorsError(f"checkpoint lacks {len(missing)} tensors of the configured model, e.g. {missing[0]}")
+    return cfg, params, n
+
+
 def save_file(path, tensors, bf16=False):
     """Writes float32 arrays as F32 (or, with bf16=True, rounded to BF16): used by tests and for exporting synthetic
     models."""
