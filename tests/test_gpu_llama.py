@@ -509,3 +509,32 @@ def test_safetensors_checkpoint_loads_onto_the_gpu(tmp_path, oracle, gpu):
     l16, _ = st.load_parameters(gpu, files, Dtype.BF16)              # kept as bf16 on the device
     assert all(l16[k].dtype == Dtype.BF16 for k in keys)
     np.testing.assert_array_equal(gpu.to_f32(l16[keys[0]]), wb[keys[0]])
+
+
+@pytest.mark.parametrize("heads,kv_heads", [(8, 2), (4, 4)], ids=["hd64", "hd128"])
+def test_fused_prefill_attention_with_a_cached_prefix(gpu, heads, kv_heads):
+    """A prompt fed in two calls (100 tokens, then 90 more on top of the cache): the fused prefill attention then runs
+    with a non-empty prefix (keys 0..99 from the cache, causal mask offset by 100, ragged last query and key tiles).
+    bf16 against the f32 runner driven the same way, and against the bf16 one-call prefill of all 190 tokens."""
+    cfg = cb.LlamaConfig(512, 1536, 2, heads, kv_heads, 4096, rope_theta=500000.0, rms_norm_eps=1e-5,
+                         tie_word_embeddings=True)
+    w = cb.random_weights(cfg, seed=4)
+    wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+    B = 3
+    ids = np.random.default_rng(31).integers(0, cfg.vocab_size, size=(B, 190), dtype=np.uint32)
+    p16 = cb.upload_weights(gpu, wb, Dtype.BF16)
+    r16 = cb.LlamaRunner(gpu, cfg, p16, Dtype.BF16, max_batch=B, max_positions=256)
+    r32 = cb.LlamaRunner(gpu, cfg, cb.upload_weights(gpu, wb, Dtype.F32), Dtype.F32, max_batch=B, max_positions=256)
+    for r in (r16, r32):
+        r.reset(B)
+        r.forward(ids[:, :100])
+        r.forward(ids[:, 100:])
+    two_calls = r16.last_logits().copy()
+    assert np.abs(two_calls - r32.last_logits()).max() <= ABS_BF16
+    tok = r16.forward(ids[:, :1] * 0 + 7)          # one decode step on top: the cache rows of both calls are in place
+    r32.forward(ids[:, :1] * 0 + 7)
+    assert np.abs(r16.last_logits() - r32.last_logits()).max() <= ABS_BF16
+    one = cb.LlamaRunner(gpu, cfg, p16, Dtype.BF16, max_batch=B, max_positions=256)
+    one.reset(B)
+    one.forward(ids)
+    assert np.abs(one.last_logits() - two_calls).max() <= ABS_BF16
