@@ -538,3 +538,26 @@ def test_fused_prefill_attention_with_a_cached_prefix(gpu, heads, kv_heads):
     one.reset(B)
     one.forward(ids)
     assert np.abs(one.last_logits() - two_calls).max() <= ABS_BF16
+
+
+def test_prefill_with_ragged_row_tiles_on_the_persistent_gemm(gpu):
+    """5 x 333 = 1665 prompt tokens: 13 full row tiles and one of a single row, more output tiles than SMs in the
+    [gate;up] product (persistent kernel, SiLU(gate)*up in the epilogue) and in the other projections (residual in the
+    epilogue); bf16 against the f32 runner on the same weights, then two decode steps."""
+    cfg = cb.LlamaConfig(512, 4096, 2, 8, 2, 4096, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=True)
+    w = cb.random_weights(cfg, seed=6)
+    wb = {k: cb.bf16_bits_to_f32(cb.f32_to_bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+    B, S = 5, 333
+    ids = np.random.default_rng(41).integers(0, cfg.vocab_size, size=(B, S), dtype=np.uint32)
+    r16 = cb.LlamaRunner(gpu, cfg, cb.upload_weights(gpu, wb, Dtype.BF16), Dtype.BF16, max_batch=B, max_positions=S + 8)
+    r32 = cb.LlamaRunner(gpu, cfg, cb.upload_weights(gpu, wb, Dtype.F32), Dtype.F32, max_batch=B, max_positions=S + 8)
+    r16.reset(B)
+    r32.reset(B)
+    tok = r16.forward(ids)
+    r32.forward(ids)
+    assert np.abs(r16.last_logits() - r32.last_logits()).max() <= ABS_BF16
+    for _ in range(2):
+        nxt = r16.forward(tok.reshape(B, 1))
+        r32.forward(tok.reshape(B, 1))
+        assert np.abs(r16.last_logits() - r32.last_logits()).max() <= ABS_BF16
+        tok = nxt
