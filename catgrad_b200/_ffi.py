@@ -104,6 +104,9 @@ CORE = {
     "params_set": (C.c_int, [C.c_void_p, C.c_char_p, _T]),
     "interp_run": (C.c_int, [_CTX, C.c_void_p, C.c_void_p, C.POINTER(ValueStruct), C.c_int, C.POINTER(ValueStruct),
                              C.c_int, intp]),
+    "op_stats_set_mode": (None, [C.c_int]),
+    "op_stats_reset": (None, []),
+    "op_stats": (C.c_int, [C.c_char_p, C.c_uint64, C.POINTER(C.c_uint64)]),
 }
 for _name in ("add", "sub", "mul", "div", "pow", "lt", "gt", "gte", "lte", "eq"):
     CORE[_name] = (C.c_int, [_CTX, _T, _T, c_void_pp])

@@ -170,6 +170,21 @@ class Backend:
         self._check(fn(self._ctx, *args, C.byref(out)))
         return Tensor(self, out)
 
+    def op_stats(self, mode=None, reset=False):
+        """Per-operation counters of the evaluator behind `cg_interp_run` (`cg_op_stats*`): with `mode` (0 off, 1 count and
+        dispatch time, 2 synchronised time) sets the mode, with `reset` clears them; returns {op: {"count", "ms"}}."""
+        import json
+        if mode is not None:
+            self._ns.op_stats_set_mode(int(mode))
+        if reset:
+            self._ns.op_stats_reset()
+        need = C.c_uint64(0)
+        self._ns.op_stats(None, 0, C.byref(need))
+        buf = C.create_string_buffer(int(need.value) + 16)
+        if self._ns.op_stats(buf, len(buf), C.byref(need)) != 0:
+            raise BackendError(Status.INVALID_ARG, "cg_op_stats failed")
+        return json.loads(buf.value.decode())
+
     def stats(self):
         """(live bytes, cached bytes, cudaMalloc calls, kernel launches) of the context (`cg_ctx_stats`)."""
         out = (C.c_uint64 * 4)()

@@ -464,4 +464,19 @@ int API(interp_run)(cg_ctx* c, const cg_term* term, const cg_params* params, con
   CG_API_END(c)
 }
 
+// ---- per-operation counters of the evaluator (interp.cc) ----
+void API(op_stats_set_mode)(int mode) { OpStats::set_mode(mode); }
+void API(op_stats_reset)(void) { OpStats::reset(); }
+int API(op_stats)(char* buf, uint64_t cap, uint64_t* needed) {
+  try {
+    const std::string js = OpStats::json();
+    if (needed) *needed = js.size() + 1;
+    if (buf == nullptr || cap < js.size() + 1) return (int)ERR_INVALID_ARG;
+    std::memcpy(buf, js.c_str(), js.size() + 1);
+    return 0;
+  } catch (...) {
+    return (int)ERR_INVALID_ARG;
+  }
+}
+
 }  // extern "C"

@@ -1,5 +1,8 @@
 // Builder, scheduler and evaluator for the restated core IR (see ir.h).
 #include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <mutex>
 #include <cstdio>
 #include <cstdlib>
 
@@ -140,6 +143,55 @@ void arity(const std::vector<Value>& a, size_t n, int edge_id) {
   CG_CHECK(a.size() == n, ERR_INTERP, edge_msg("ArityError", edge_id));
 }
 }  // namespace
+
+// ---- per-operation counters ----------------------------------------------------------------------
+namespace {
+std::mutex g_stats_mu;
+std::map<std::string, OpStats::Entry> g_stats;
+std::atomic<int> g_stats_mode{[] {
+  const char* e = std::getenv("CATGRAD_OP_STATS");   // "1" or "sync"
+  return e == nullptr ? 0 : (std::string(e) == "sync" || std::string(e) == "2" ? 2 : 1);
+}()};
+}  // namespace
+void OpStats::set_mode(int mode) { g_stats_mode.store(mode < 0 ? 0 : (mode > 2 ? 2 : mode)); }
+int OpStats::mode() { return g_stats_mode.load(); }
+void OpStats::reset() {
+  std::lock_guard<std::mutex> lk(g_stats_mu);
+  g_stats.clear();
+}
+void OpStats::add(const std::string& op, double seconds) {
+  std::lock_guard<std::mutex> lk(g_stats_mu);
+  Entry& e = g_stats[op];
+  e.count += 1;
+  e.seconds += seconds;
+}
+std::string OpStats::json() {
+  std::lock_guard<std::mutex> lk(g_stats_mu);
+  std::string out = "{";
+  bool first = true;
+  for (const auto& kv : g_stats) {
+    char buf[96];
+    std::snprintf(buf, sizeof(buf), "{\"count\": %llu, \"ms\": %.6f}", (unsigned long long)kv.second.count, kv.second.seconds * 1e3);
+    out += (first ? "\"" : ", \"") + kv.first + "\": " + buf;
+    first = false;
+  }
+  return out + "}";
+}
+std::string op_label(const Operation& op) {
+  static const char* kinds[] = {"TypePack", "TypeUnpack", "TypeShape", "TypeDtype", "NatConstant", "NatMul", "NatAdd",
+                                "DtypeConstant", "Map", "NatToU32", "Cast", "MatMul", "ScalarF32", "ScalarU32", "Sum", "Max",
+                                "Argmax", "TopK", "Probe", "Broadcast", "Reshape", "Transpose", "Slice", "Concat", "Arange",
+                                "Index", "If", "Copy", "Load"};
+  static const char* sops[] = {"Add", "Sub", "Mul", "Div", "Neg", "Pow", "LT", "GT", "GTE", "LTE", "EQ", "Cos", "Sin", "Exp",
+                               "Log", "Floor", "Round", "Where"};
+  const int k = (int)op.kind;
+  if (k < 0 || k >= (int)(sizeof(kinds) / sizeof(kinds[0]))) return "?";
+  if (op.kind == OpKind::Map) {
+    const int so = (int)op.sop;
+    return std::string("Map.") + (so >= 0 && so < (int)(sizeof(sops) / sizeof(sops[0])) ? sops[so] : "?");
+  }
+  return kinds[k];
+}
 
 std::vector<Value> Interpreter::apply(const Edge& e, int id, std::vector<Value>& a) const {
   const Operation& op = e.op;
@@ -302,7 +354,16 @@ std::vector<Value> Interpreter::run(const Term& term, std::vector<Value> inputs)
         args.push_back(std::move(state[s]));
         state[s] = Value();
       }
-      std::vector<Value> res = apply(e, eid, args);
+      std::vector<Value> res;
+      if (const int stats = OpStats::mode()) {
+        const auto t0 = std::chrono::steady_clock::now();
+        res = apply(e, eid, args);
+        if (stats == 2 && e.op.kind != OpKind::If) be_->synchronize();   // an If is charged to the edges of its branch
+        if (e.op.kind != OpKind::If)
+          OpStats::add(op_label(e.op), std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count());
+      } else {
+        res = apply(e, eid, args);
+      }
       CG_CHECK(res.size() == e.targets.size(), ERR_INTERP, edge_msg("ArityError: result count", eid));
       for (size_t i = 0; i < res.size(); ++i) {
         CG_CHECK(state[e.targets[i]].kind == Value::None, ERR_INTERP,

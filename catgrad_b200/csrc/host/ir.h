@@ -82,6 +82,19 @@ struct Value {
 using Parameters = std::map<std::string, Tensor>;
 
 // Evaluator (interp.cc).  `Interpreter::run` = catgrad/src/interpreter/interpreter.rs:29-37.
+// Per-operation counters of the evaluator (tracing aid; off by default): how many edges of each kind were evaluated and
+// the host time spent in them.  Mode 1 times the dispatch only (device work is asynchronous), mode 2 synchronises the
+// backend after every edge so that the time is the operation's own.  Process-wide, guarded by a mutex.
+struct OpStats {
+  struct Entry { uint64_t count = 0; double seconds = 0.0; };
+  static void set_mode(int mode);   // 0 off, 1 count + dispatch time, 2 count + synchronised time
+  static int mode();
+  static void reset();
+  static void add(const std::string& op, double seconds);
+  static std::string json();        // {"op name": {"count": n, "ms": t}, ...} sorted by name
+};
+std::string op_label(const Operation& op);   // "MatMul", "Map.Add", "Load", ...
+
 class Interpreter {
  public:
   Interpreter(Backend* be, const Parameters* params) : be_(be), params_(params) {}

@@ -276,6 +276,17 @@ cg_status cg_runner_generate(cg_runner* r, const uint32_t* prompts, uint64_t n_s
 const char* cg_runner_last_error(const cg_runner* r);
 void cg_runner_free(cg_runner* r);
 
+/* ---- per-operation counters of cg_interp_run (tracing aid, off by default; the reference has Probe and wall clocks only:
+ * tensor_op.rs:121-136, main.rs:914-917) ------------------------------------------------------------------------------
+ * mode 0 off, 1 count every evaluated edge by operation and time its dispatch on the host, 2 also synchronise after every
+ * edge so that the time is the operation's own (slow).  The environment variable CATGRAD_OP_STATS=1|sync sets the
+ * initial mode.  Process-wide.  cg_op_stats writes a JSON object {"MatMul": {"count": n, "ms": t}, "Map.Add": ...};
+ * `needed` receives the size to pass when `cap` was too small (CG_ERR_INVALID_ARG).  A term that runs as the fused plan
+ * evaluates no edges and leaves the counters untouched. */
+void cg_op_stats_set_mode(int mode);
+void cg_op_stats_reset(void);
+cg_status cg_op_stats(char* buf, uint64_t cap, uint64_t* needed);
+
 /* ---- timing and allocator introspection ---------------------------------------------------- */
 /* CUDA events on the context's stream (the stream every kernel of this library is launched on). */
 cg_status cg_event_record(cg_ctx*, int slot /* 0..63 */);

@@ -561,3 +561,26 @@ def test_prefill_with_ragged_row_tiles_on_the_persistent_gemm(gpu):
         r32.forward(tok.reshape(B, 1))
         assert np.abs(r16.last_logits() - r32.last_logits()).max() <= ABS_BF16
         tok = nxt
+
+
+def test_operation_counters_see_the_op_by_op_route_only(gpu):
+    """cg_op_stats on the CUDA backend: a Llama term that runs as the fused plan evaluates no edge and records nothing; the
+    same term op by op records every edge (synchronised timing mode)."""
+    cfg, w, _ = tiny_inputs()
+    params = cb.upload_weights(gpu, w, Dtype.F32)
+    ids = np.random.default_rng(2).integers(0, cfg.vocab_size, size=(1, 6), dtype=np.uint32)
+    try:
+        gpu.op_stats(mode=2, reset=True)
+        term = cb.llama_term(gpu, cfg)
+        planned = cb.generate_with_interpreter(gpu, term, params, cfg, ids, 2, Dtype.F32, 12)[0]
+        assert term.plan_state == 1 and gpu.op_stats() == {}
+        gpu._ns.interp_set_planning(0)
+        term2 = cb.llama_term(gpu, cfg)
+        stepwise = cb.generate_with_interpreter(gpu, term2, params, cfg, ids, 2, Dtype.F32, 12)[0]
+        st = gpu.op_stats()
+    finally:
+        gpu._ns.interp_set_planning(1)
+        gpu.op_stats(mode=0, reset=True)
+    np.testing.assert_array_equal(planned, stepwise)
+    assert st["MatMul"]["count"] == 2 * (9 * cfg.num_hidden_layers + 1) and st["Argmax"]["count"] == 2
+    assert sum(v["ms"] for v in st.values()) > 0.0

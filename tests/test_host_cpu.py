@@ -257,3 +257,31 @@ def test_bench_table_has_the_reference_layout():
     cells = [c.strip() for c in lines[2].split("|")[1:-1]]
     assert cells == ["llama-3.2-1b", "2.30 GiB", "1235.81 M", "b200", "pp512", "128000.00"]
     assert [c.strip() for c in lines[3].split("|")[1:-1]][-2:] == ["tg128", "1280.00"]
+
+
+def test_per_operation_counters_of_the_evaluator(oracle):
+    """cg_op_stats*: off by default; when on, every evaluated edge of a term is counted under its operation's name (the
+    Llama term: 7 linear layers per layer + the head as MatMul, one Argmax, one Load per parameter) and timed; a reset
+    clears them; the mode is process-wide, so it is switched off again here."""
+    cfg = cb.TINY
+    w = cb.random_weights(cfg, seed=0)
+    params = cb.upload_weights(oracle, w, cb.Dtype.F32)
+    term = cb.llama_term(oracle, cfg)
+    ids = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(1, 5), dtype=np.uint32)
+    assert oracle.op_stats(mode=0, reset=True) == {}
+    cb.generate_with_interpreter(oracle, term, params, cfg, ids, 1, cb.Dtype.F32, 8)
+    assert oracle.op_stats() == {}                      # off: nothing recorded
+    try:
+        oracle.op_stats(mode=2)
+        cb.generate_with_interpreter(oracle, term, params, cfg, ids, 1, cb.Dtype.F32, 8)
+        st = oracle.op_stats()
+    finally:
+        oracle.op_stats(mode=0)
+    L = cfg.num_hidden_layers
+    # q, k, v, o, gate, up, down per layer, the head, and the two attention products per layer
+    assert st["MatMul"]["count"] == 9 * L + 1
+    assert st["Argmax"]["count"] == 1
+    assert st["Load"]["count"] == len(cfg.param_shapes())
+    assert all(v["count"] > 0 and v["ms"] >= 0.0 for v in st.values())
+    assert any(k.startswith("Map.") for k in st) and "Concat" in st and "Broadcast" in st
+    assert oracle.op_stats(reset=True) == {}
