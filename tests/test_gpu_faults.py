@@ -87,3 +87,21 @@ def test_matmul_refuses_dimensions_the_kernels_cannot_index(gpu):
     assert y.shape == (70000 * 64, 4)
     v = gpu.to_numpy(gpu.slice(y, 0, 70000 * 64 - 3, 3)).astype(np.float32)
     np.testing.assert_array_equal(v, np.full((3, 4), 8.0, np.float32))
+
+
+def test_allocator_size_classes_absorb_slowly_growing_tensors(gpu):
+    """A tensor that grows by a row per step (the KV cache an op-by-op evaluation re-concatenates per token) must not
+    reach cudaMalloc at every step: sizes fall into four classes per power of two, and a freed block of the class is
+    reused."""
+    import ctypes as C
+    stats = (C.c_uint64 * 4)()
+    rows = lambda n: gpu.zeros((n, 512), Dtype.F32)          # 2 KiB per row
+    t = rows(100)
+    del t
+    gpu._check(gpu._ns.ctx_stats(gpu._ctx, stats))
+    before = stats[2]
+    for n in range(100, 228):                                # 200 KiB .. 456 KiB in steps of 2 KiB: 128 distinct sizes
+        t = rows(n)
+        del t
+    gpu._check(gpu._ns.ctx_stats(gpu._ctx, stats))
+    assert stats[2] - before <= 6                            # classes of 32 / 64 KiB: a handful of new blocks, not 128
